@@ -1,0 +1,443 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4] [--impl ours|reference]
+
+One "step" is one pass over the workload's list of linears on one batch of
+synthetic input (x ~ N(0,1) bf16, W ~ N(0,0.02) quantised per output channel to
+e4m3, bias ~ N(0,0.01), static activation scale from a seeded calibration draw).
+The default workload "c2" is the W8A8-static 3B-scale sweep
+(M,K,N) in {(1,2048,2048), (16,2048,11008), (256,11008,2048), (1024,2048,11008)}.
+Weights are cycled over several distinct copies so that no weight byte is
+L2-resident when it is read again.
+
+Prints ONE JSON line (rank 0).  `value` is aggregate TFLOP/s (2*M*K*N summed
+over the pass / step time) with inputs resident in HBM and the step replayed
+from a CUDA graph; `e2e` is the same metric through the public layer API with
+host buffers (pinned H2D of x and D2H of y inside the timed region); `shapes`
+lists per-(M,K,N) microseconds and roofline fractions; `roofline` describes the
+dominant kernel; `cpu_baseline` is the reference's torch dequant-then-matmul
+formula timed on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (scheme, [(label, M, K, N, parallel kind)])
+    "c1": ("fp8_w8a16", [("up_proj", 16, 2048, 11008, "col")]),
+    "c2": ("fp8_w8a8_static", [("q_proj", 1, 2048, 2048, "col"), ("up_proj", 16, 2048, 11008, "col"),
+                               ("down_proj", 256, 11008, 2048, "row"), ("up_proj", 1024, 2048, 11008, "col")]),
+}
+for _m in (1, 4, 16, 64):
+    for _s, _tag in (("fp8_w8a8_static", "w8a8"), ("fp8_w8a16", "w8a16")):
+        WORKLOADS[f"c3_{_tag}_m{_m}"] = (_s, [("qkv", _m, 3584, 4608, "col"), ("o_proj", _m, 3584, 3584, "row"),
+                                              ("gate_up", _m, 3584, 37888, "col"), ("down", _m, 18944, 3584, "row")])
+for _m in (4096, 16384, 32640):
+    WORKLOADS[f"c4_m{_m}"] = ("fp8_w8a8_static", [("qkv", _m, 3584, 4608, "col"), ("o_proj", _m, 3584, 3584, "row"),
+                                                  ("gate_up", _m, 3584, 37888, "col"), ("down", _m, 18944, 3584, "row")])
+
+L2_BYTES = 126 * 1024 * 1024
+SEED = 20260519
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def algorithmic_bytes(m, k, n, bias=True):
+    """x bf16 + W e4m3 + scale f32 + bias bf16 + input scale + y bf16 (no credit for scratch)."""
+    return 2 * m * k + k * n + 4 * n + (2 * n if bias else 0) + 4 + 2 * m * n
+
+
+def shard_shape(k, n, kind, tp):
+    if tp == 1:
+        return k, n
+    return (k, n // tp) if kind == "col" else (k // tp, n)
+
+
+# --------------------------------------------------------------------------- data
+def make_weights(k, n, seed, device):
+    """Seeded W ~ N(0, 0.02) quantised per output channel (same rule as the exporter)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn((n, k), generator=g, device=device, dtype=torch.float32) * 0.02
+    scale = w.abs().amax(dim=1).clamp(min=1e-8) / 448.0
+    q = (w / scale[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    return q.contiguous(), scale.contiguous()
+
+
+def make_inputs(m, k, n, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn((m, k), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    bias = (torch.randn((n,), generator=g, device=device, dtype=torch.float32) * 0.01).to(torch.bfloat16)
+    calib = torch.randn((4096, k), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    in_scale = (calib.float().abs().amax().clamp(min=1e-8) / 448.0).reshape(())
+    return x, bias, in_scale.to(torch.float32)
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- reference arm (CPU)
+def cpu_tensors(ops):
+    out = []
+    for i, (_, m, k, n, _) in enumerate(ops):
+        q, s = make_weights(k, n, SEED + 10 * i, "cpu")
+        x, _, _ = make_inputs(m, k, n, SEED + 10 * i + 1, "cpu")
+        out.append((x, q, s))
+    return out
+
+
+def time_cpu(ops, steps, warmup, budget_s=25.0):
+    """Reference formula on the host cores (the one place the bench executes oracle/)."""
+    from oracle import torch_ref
+    times, _ = torch_ref.time_passes(cpu_tensors(ops), steps, warmup, budget_s)
+    return times
+
+
+def run_reference_arm(args, scheme, ops, flops):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = time_cpu(ops, args.steps, args.warmup, budget_s=120.0)
+    sec = sum(times) / len(times)
+    val = flops / sec / 1e12
+    line = {
+        "impl": "reference", "metric": "fp8_linear_throughput", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (cpu dequant-then-matmul)", "data": "synthetic",
+        "config": {"workload": args.workload, "scheme": scheme, "shapes": [[m, k, n] for _, m, k, n, _ in ops]},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{len(times)} full passes of the workload on the host cores"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- our arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    scheme, ops = WORKLOADS[args.workload]
+    flops = sum(2 * m * k * n for _, m, k, n, _ in ops)
+    if args.impl == "reference":
+        run_reference_arm(args, scheme, ops, flops)
+        return
+
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback; use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    tp = world
+
+    pkg = importlib.import_module("nano-vllm-moe_b200")
+    Kn = importlib.import_module("nano-vllm-moe_b200.quantization.kernels")
+    lib = pkg._lib
+    scheme_id = lib.W8A8_STATIC if scheme == "fp8_w8a8_static" else lib.W8A16
+    peaks = load_peaks()
+
+    # ---- layers: real layer classes, loaded through their weight loaders ----------------------
+    weight_bytes = sum(k * n for _, _, k, n, _ in ops) // tp
+    copies = max(2, -(-2 * L2_BYTES // max(weight_bytes, 1)))
+    copies = min(copies, 28)
+    cfg = pkg.Fp8Config(scheme)
+    layers = []   # [copy][op] -> layer
+    inputs = []   # [op] -> (x_local, x_host_pinned)
+    for c in range(copies):
+        row = []
+        for i, (label, m, k, n, kind) in enumerate(ops):
+            q, s = make_weights(k, n, SEED + 1000 * c + 10 * i, dev)
+            x, bias, in_scale = make_inputs(m, k, n, SEED + 10 * i + 1, dev)
+            cls = pkg.ColumnParallelLinear if kind == "col" else pkg.RowParallelLinear
+            lay = cls(k, n, bias=True, quant_method=cfg.get_quant_method(None, label))
+            lay = lay.to(dev)
+            lay.qweight.weight_loader(lay.qweight, q)
+            lay.weight_scale.weight_loader(lay.weight_scale, s)
+            if scheme == "fp8_w8a8_static":
+                lay.input_scale.weight_loader(lay.input_scale, in_scale)
+            lay.bias.data = torch.empty_like(lay.bias.data, dtype=torch.bfloat16)
+            lay.bias.weight_loader(lay.bias, bias)
+            pkg.process_weights_after_loading(lay)
+            row.append(lay)
+            del q, s
+            if c == 0:
+                xl = x if (kind == "col" or tp == 1) else x[:, rank * (k // tp):(rank + 1) * (k // tp)].contiguous()
+                inputs.append((xl, xl.cpu().pin_memory()))
+        layers.append(row)
+    torch.cuda.synchronize()
+
+    def run_pass(c, xs):
+        outs = []
+        for lay, x in zip(layers[c % copies], xs):
+            outs.append(lay(x))
+        return outs
+
+    xs_dev = [x for x, _ in inputs]
+    # warm every (shape, scratch size) once eagerly so that graph capture sees no allocation
+    for c in range(copies):
+        run_pass(c, xs_dev)
+    torch.cuda.synchronize()
+    kernels_per_pass = sum(2 if Kn.variant_name(scheme_id, m, *shard_shape(k, n, kind, tp)).startswith("umma") else 1
+                           for _, m, k, n, kind in ops)
+
+    # ---- device-resident timing: one CUDA graph per weight copy --------------------------------
+    graphs = []
+    use_graph = not args.no_graph
+    side = torch.cuda.Stream(dev)
+    if use_graph:
+        try:
+            with torch.cuda.stream(side):
+                run_pass(0, xs_dev)          # scratch for the capture stream
+                torch.cuda.synchronize()
+                for c in range(copies):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        run_pass(c, xs_dev)
+                    graphs.append(g)
+        except Exception as e:  # noqa: BLE001  (capture is an optimisation of the measurement only)
+            print(f"[bench] CUDA graph capture failed ({e!r}); timing eager launches", file=sys.stderr)
+            graphs, use_graph = [], False
+    torch.cuda.synchronize()
+
+    def step(i):
+        if use_graph:
+            graphs[i % copies].replay()
+        else:
+            run_pass(i, xs_dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = flops / (ms_step * 1e-3) / 1e12
+
+    # ---- per-shape microseconds and roofline (graph of 20 launches per weight copy) ----------------
+    shapes = []
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    for i, (label, m, k, n, kind) in enumerate(ops):
+        kl, nl = shard_shape(k, n, kind, tp)
+        x = xs_dev[i]
+        reps = 5
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.stream(side):
+                layers[0][i](x)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g, stream=side):
+                    for r in range(reps):
+                        for c in range(copies):
+                            layers[c][i](x)
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(4):
+                g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / (4 * reps * copies)
+        except Exception as e:  # noqa: BLE001
+            print(f"[bench] per-shape graph failed for {label}: {e!r}", file=sys.stderr)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for r in range(reps):
+                for c in range(copies):
+                    layers[c][i](x)
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / (reps * copies)
+        fl = 2.0 * m * kl * nl
+        by = algorithmic_bytes(m, kl, nl)
+        t_hbm = by / (peaks["hbm_gbs"] * 1e9)
+        t_tc = fl / (fp8_peak * 1e12)
+        bound = "hbm" if t_hbm >= t_tc else "tensor"
+        shapes.append({
+            "layer": label, "m": m, "k": kl, "n": nl, "variant": Kn.variant_name(scheme_id, m, kl, nl),
+            "us": us, "tflops": fl / us / 1e6, "gbs": by / us / 1e3, "bound": bound,
+            "frac": (by / us / 1e3) / peaks["hbm_gbs"] if bound == "hbm" else (fl / us / 1e6) / fp8_peak,
+        })
+    dom = max(shapes, key=lambda s: s["us"])
+    if dom["bound"] == "hbm":
+        roofline = {"bound": "hbm", "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": dom["gbs"] / peaks["hbm_gbs"], "traffic": None}
+    else:
+        roofline = {"bound": "tensor", "achieved": dom["tflops"], "peak": fp8_peak, "unit": "TFLOP/s",
+                    "frac": dom["tflops"] / fp8_peak, "traffic": None}
+    roofline["kernel"] = dom["variant"]
+    roofline["shape"] = [dom["m"], dom["k"], dom["n"]]
+    roofline["peak_source"] = (f"{peaks['source']}: HBM copy {peaks['hbm_gbs']} GB/s; dense-FP8 peak taken as 2 x "
+                               f"{peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s")
+
+    # ---- end to end through the layer API with host buffers ------------------------------------------
+    host_out = [torch.empty((m, shard_shape(k, n, kind, tp)[1]), dtype=torch.bfloat16).pin_memory()
+                for _, m, k, n, kind in ops]
+    dev_in = [torch.empty_like(x) for x in xs_dev]
+    h2d = sum(h.numel() * 2 for _, h in inputs)
+    d2h = sum(h.numel() * 2 for h in host_out)
+
+    def e2e_step(i):
+        for d, (_, h) in zip(dev_in, inputs):
+            d.copy_(h, non_blocking=True)
+        outs = run_pass(i, dev_in)
+        for h, o in zip(host_out, outs):
+            h.copy_(o, non_blocking=True)
+
+    e2e_steps = max(10, min(args.steps, 50))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = flops / (e2e_ms * 1e-3) / 1e12
+    status = Kn.read_status(dev)
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            times = time_cpu(ops, steps=60, warmup=3, budget_s=20.0)
+            sec = sum(times) / len(times)
+            cpu = {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                   "ms_per_pass": sec * 1e3,
+                   "sample": f"{len(times)} full passes of the same workload (torch dequant-then-matmul on the host)"}
+        line = {
+            "metric": "fp8_linear_throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 -> bf16"
+            if scheme == "fp8_w8a8_static" else "fp8_e4m3 weights, f16 MMA -> fp32 -> bf16",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "scheme": scheme,
+                       "shapes": [[m, k, n] for _, m, k, n, _ in ops],
+                       "parallelism": f"tp{tp}" if tp > 1 else "single",
+                       "l2": f"weights cycled over {copies} distinct copies per shape "
+                             f"({copies * weight_bytes / 1e6:.0f} MB > 126 MB L2)",
+                       "launch": "cuda-graph replay" if use_graph else "eager"},
+            "clocks": clocks, "shapes": shapes, "roofline": roofline,
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": kernels_per_pass * args.steps, "device_status": status,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,117 @@
+/*
+ * fp8lin — C ABI of the B200 (sm_100a) FP8 quantized-linear engine.
+ *
+ * Drop-in for the kernel launchers behind nano-vllm-moe's FP8 linear backend
+ * (nanovllm/quantization/fp8.py, Fp8LinearMethod.apply).  Every pointer is a
+ * CUDA device pointer unless stated otherwise; `stream` is a cudaStream_t
+ * passed as void*.  All calls are asynchronous on `stream`, allocate nothing
+ * on the device, never synchronise the host (except fp8lin_read_status) and
+ * are safe to capture in a CUDA graph.  The library owns no tensor: every
+ * buffer, including scratch, belongs to the caller.
+ *
+ * Number formats
+ *   activations x, bias, outputs y : bfloat16, row-major, row strides ldx/ldy in ELEMENTS
+ *   weights                        : e4m3 (torch.float8_e4m3fn) bytes
+ *   scales                         : float32
+ *
+ * Weight layouts
+ *   "kn"  : [K][N], N contiguous — the layout of the reference's `qweight`
+ *           buffer (fp8.py:80-83) after its loaders ran.
+ *   "nk"  : [N][K], K contiguous — the layout every kernel here streams
+ *           (it is also the checkpoint's own layout, quantize.py:56).
+ *           Produce it once per layer with fp8lin_prepack_weight.
+ *
+ * Return value: 0 on success, otherwise one of the FP8LIN_ERR_* codes;
+ * fp8lin_last_error() returns a thread-local description of the last failure.
+ */
+#ifndef FP8LIN_H
+#define FP8LIN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FP8LIN_VERSION 1
+
+enum {
+    FP8LIN_OK = 0,
+    FP8LIN_ERR_NULL = 1,       /* a required pointer is NULL */
+    FP8LIN_ERR_SHAPE = 2,      /* M/K/N/ld out of range or K not a multiple of 16 */
+    FP8LIN_ERR_ALIGN = 3,      /* pointer or stride not 16-byte aligned */
+    FP8LIN_ERR_WORKSPACE = 4,  /* workspace missing or smaller than fp8lin_workspace_bytes */
+    FP8LIN_ERR_ARCH = 5,       /* device is not sm_100 */
+    FP8LIN_ERR_LAUNCH = 6,     /* CUDA reported a launch/driver error */
+    FP8LIN_ERR_DEVICE = 7,     /* a kernel recorded a bounded-wait timeout (fp8lin_read_status) */
+    FP8LIN_ERR_ARG = 8         /* unknown enum value / unsupported combination */
+};
+
+/* scheme ids; names follow the reference's `quantization_type` (fp8.py:20). */
+enum { FP8LIN_W8A16 = 0, FP8LIN_W8A8_STATIC = 1 };
+
+int fp8lin_version(void);
+const char* fp8lin_last_error(void);
+
+/* ---- weight prepack -------------------------------------------------------
+ * Replaces the derived copies the reference builds in
+ * Fp8LinearMethod.process_weights_after_loading (fp8.py:106-111).
+ * qweight_kn: u8 [K][N]  ->  w_nk: u8 [N][K].  K % 16 == 0. */
+size_t fp8lin_packed_bytes(int64_t K, int64_t N);
+int fp8lin_prepack_weight(const void* qweight_kn, void* w_nk, int64_t K, int64_t N, void* stream);
+
+/* ---- scratch --------------------------------------------------------------
+ * Bytes of caller-owned scratch a linear call of this shape needs (split-K
+ * partial sums, quantised activations, tile counters).  Scratch must be
+ * 256-byte aligned, ZERO-FILLED ONCE after allocation (the first
+ * FP8LIN_WS_HEADER_BYTES hold counters that every kernel leaves at zero), and
+ * must not be shared by calls that can run concurrently (one per stream). */
+#define FP8LIN_WS_HEADER_BYTES 65536
+size_t fp8lin_workspace_bytes(int scheme, int64_t M, int64_t K, int64_t N);
+
+/* ---- the linears ----------------------------------------------------------
+ * y[M,N] = bf16( (x . W^T) * w_scale[n] + bias[n] )
+ * Replaces launch_w8a16_gemm (nanovllm/quantization/kernels/fp8.py:79-109) and
+ * w8a16_cuda_forward (nanovllm/quantization/csrc/w8a16_ext.cpp:3-11).
+ * bias may be NULL. */
+int fp8lin_w8a16(const void* x, int64_t ldx, const void* w_nk, const float* w_scale,
+                 const void* bias, void* y, int64_t ldy,
+                 int64_t M, int64_t K, int64_t N,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* xq = e4m3(clamp(x / max(*input_scale,1e-12), +-448));
+ * y[M,N] = bf16( (xq . W^T) * max(*input_scale,1e-12) * w_scale[n] + bias[n] )
+ * Replaces launch_w8a8_cuda_ptx_jit (nanovllm/quantization/w8a8_jit.py:521-542),
+ * launch_w8a8_cutlass_gemm (nanovllm/quantization/cuda_ext.py:84-106 ->
+ * csrc/w8a8_cutlass_kernel.cu:460-497) and launch_scaled_mm_w8a8
+ * (kernels/fp8.py:376-396).  w_scale is per output channel ([N]); pass a
+ * broadcast copy for a per-tensor scale.  input_scale points to ONE float on
+ * the device. */
+int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_scale,
+                const float* input_scale, const void* bias, void* y, int64_t ldy,
+                int64_t M, int64_t K, int64_t N,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* Stand-alone activation quantiser; replaces quantize_activation_kernel
+ * (csrc/w8a8_cutlass_kernel.cu:406-430) / act_quant_fp8_kernel (kernels/fp8.py:232-249).
+ * xq: u8 [M][K] contiguous. */
+int fp8lin_quantize_activation(const void* x, int64_t ldx, const float* input_scale,
+                               void* xq, int64_t M, int64_t K, void* stream);
+
+/* Which kernel variant a shape is routed to ("stream_mma_w8a8_m16", "umma_w8a8_128x256", ...),
+ * for labelling bench rows and ncu captures.  Host-only, returns a static string. */
+const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);
+
+/* Bench/ncu studies only: force a tuning knob ("stream_splits", "stream_max_m",
+ * "umma_bn", "umma_splits", ...; value < 0 restores the default).  Not thread safe. */
+int fp8lin_set_tuning(const char* knob, int value);
+
+/* Blocking: copies the device status word out of `workspace` (after syncing
+ * `stream`) and clears it.  0 = no kernel gave up a bounded wait. */
+int fp8lin_read_status(void* workspace, void* stream, int* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP8LIN_H */

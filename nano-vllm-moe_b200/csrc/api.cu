@@ -1,0 +1,206 @@
+// extern "C" surface of libfp8lin.so (declared in include/fp8lin.h).
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace fp8lin;
+
+namespace {
+
+thread_local char g_err[256] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+struct Tuning {
+    int stream_splits = -1;   // force split-K factor of the streaming kernel
+    int stream_max_m = -1;    // largest M routed to the streaming kernel (W8A8)
+    int umma_bn = -1;         // force tile width of the tcgen05 kernel
+    int umma_splits = -1;     // force split-K factor of the tcgen05 kernel
+} g_tune;
+
+constexpr int kDefaultStreamMaxM = 64;
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int check_arch() {
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    int dev = 0;
+    cudaDeviceProp prop;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return cached = 0;
+    return cached = (prop.major == 10) ? 1 : 0;
+}
+
+int validate_common(const void* x, int64_t ldx, const void* w, const float* w_scale, const void* bias, void* y,
+                    int64_t ldy, int64_t M, int64_t K, int64_t N) {
+    if (M < 0 || K <= 0 || N <= 0) return fail(FP8LIN_ERR_SHAPE, "bad shape M=%lld K=%lld N=%lld", (long long)M, (long long)K, (long long)N);
+    if (M > (1ll << 30) || K > (1ll << 30) || N > (1ll << 30)) return fail(FP8LIN_ERR_SHAPE, "dimension too large");
+    if (K % 16 != 0) return fail(FP8LIN_ERR_SHAPE, "K=%lld must be a multiple of 16", (long long)K);
+    if (M == 0) return FP8LIN_OK;
+    if (!x || !w || !w_scale || !y) return fail(FP8LIN_ERR_NULL, "x, w_nk, w_scale and y must not be NULL");
+    if (ldx < K || ldy < N) return fail(FP8LIN_ERR_SHAPE, "ldx=%lld < K or ldy=%lld < N", (long long)ldx, (long long)ldy);
+    if (ldx % 8 != 0) return fail(FP8LIN_ERR_ALIGN, "ldx=%lld must be a multiple of 8 elements", (long long)ldx);
+    if (!aligned16(x) || !aligned16(w) || !aligned16(w_scale) || (bias && !aligned16(bias)))
+        return fail(FP8LIN_ERR_ALIGN, "x, w_nk, w_scale and bias must be 16-byte aligned");
+    if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
+    return FP8LIN_OK;
+}
+
+bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
+    const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
+    return M > max_m && N % 8 == 0 && ldy % 8 == 0 && aligned16(y);
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp8lin_version(void) { return FP8LIN_VERSION; }
+const char* fp8lin_last_error(void) { return g_err; }
+
+size_t fp8lin_packed_bytes(int64_t K, int64_t N) { return (K > 0 && N > 0) ? (size_t)K * (size_t)N : 0; }
+
+int fp8lin_prepack_weight(const void* qweight_kn, void* w_nk, int64_t K, int64_t N, void* stream) {
+    if (K <= 0 || N <= 0) return fail(FP8LIN_ERR_SHAPE, "bad shape K=%lld N=%lld", (long long)K, (long long)N);
+    if (K % 16 != 0) return fail(FP8LIN_ERR_SHAPE, "K=%lld must be a multiple of 16", (long long)K);
+    if (!qweight_kn || !w_nk) return fail(FP8LIN_ERR_NULL, "qweight_kn and w_nk must not be NULL");
+    cudaError_t e = launch_transpose_u8((const unsigned char*)qweight_kn, (unsigned char*)w_nk, K, N, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "prepack launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+size_t fp8lin_workspace_bytes(int scheme, int64_t M, int64_t K, int64_t N) {
+    if (M <= 0 || K <= 0 || N <= 0) return FP8LIN_WS_HEADER_BYTES;
+    size_t body = 0;
+    // streaming route (any M for W8A16; M <= 64 or odd shapes for W8A8)
+    StreamPlan sp = plan_stream(scheme, M, K, N, g_tune.stream_splits);
+    body = sp.partial_bytes;
+    if (scheme == FP8LIN_W8A8_STATIC) {
+        UmmaPlan up = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
+        size_t u = align_up((size_t)M * K, 256) + up.partial_bytes;
+        if (u > body) body = u;
+    }
+    return FP8LIN_WS_HEADER_BYTES + align_up(body, 256);
+}
+
+static int run_stream(int scheme, const void* x, int64_t ldx, const void* w, const float* w_scale,
+                      const float* input_scale, const void* bias, void* y, int64_t ldy, int64_t M, int64_t K,
+                      int64_t N, void* workspace, size_t ws_bytes, cudaStream_t stream) {
+    StreamPlan pl = plan_stream(scheme, M, K, N, g_tune.stream_splits);
+    WsView ws = ws_view(workspace, ws_bytes);
+    if (pl.splits > 1) {
+        if (!workspace || ws.body_bytes < pl.partial_bytes)
+            return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes", FP8LIN_WS_HEADER_BYTES + pl.partial_bytes);
+    }
+    StreamArgs a;
+    a.x = (const __nv_bfloat16*)x; a.w = (const unsigned char*)w; a.w_scale = w_scale; a.input_scale = input_scale;
+    a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y;
+    a.partial = workspace ? (float*)ws.body : nullptr; a.counters = workspace ? ws.counters : nullptr;
+    a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldx = (int)ldx; a.ldy = (int)ldy; a.k_per_split = pl.k_per_split;
+    cudaError_t e = launch_stream(scheme, pl, a, stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "stream kernel launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+int fp8lin_w8a16(const void* x, int64_t ldx, const void* w_nk, const float* w_scale, const void* bias, void* y,
+                 int64_t ldy, int64_t M, int64_t K, int64_t N, void* workspace, size_t workspace_bytes,
+                 void* stream) {
+    int rc = validate_common(x, ldx, w_nk, w_scale, bias, y, ldy, M, K, N);
+    if (rc != FP8LIN_OK || M == 0) return rc;
+    return run_stream(FP8LIN_W8A16, x, ldx, w_nk, w_scale, nullptr, bias, y, ldy, M, K, N, workspace,
+                      workspace_bytes, (cudaStream_t)stream);
+}
+
+int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_scale, const float* input_scale,
+                const void* bias, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N, void* workspace,
+                size_t workspace_bytes, void* stream) {
+    int rc = validate_common(x, ldx, w_nk, w_scale, bias, y, ldy, M, K, N);
+    if (rc != FP8LIN_OK || M == 0) return rc;
+    if (!input_scale) return fail(FP8LIN_ERR_NULL, "input_scale must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!umma_eligible(M, N, ldy, y))
+        return run_stream(FP8LIN_W8A8_STATIC, x, ldx, w_nk, w_scale, input_scale, bias, y, ldy, M, K, N, workspace,
+                          workspace_bytes, st);
+
+    UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
+    WsView ws = ws_view(workspace, workspace_bytes);
+    const size_t xq_bytes = align_up((size_t)M * K, 256);
+    if (!workspace || ws.body_bytes < xq_bytes + pl.partial_bytes)
+        return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes",
+                    FP8LIN_WS_HEADER_BYTES + xq_bytes + pl.partial_bytes);
+    unsigned char* xq = ws.body;
+    cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, xq, M, K, st);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
+    UmmaArgs a;
+    a.xq = xq; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
+    a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y;
+    a.partial = (float*)(ws.body + xq_bytes); a.counters = ws.counters; a.status = ws.status;
+    a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ldy;
+    const char* why = nullptr;
+    e = launch_umma_w8a8(pl, a, st, &why);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+    return FP8LIN_OK;
+}
+
+int fp8lin_quantize_activation(const void* x, int64_t ldx, const float* input_scale, void* xq, int64_t M, int64_t K,
+                               void* stream) {
+    if (M < 0 || K <= 0 || K % 16 != 0) return fail(FP8LIN_ERR_SHAPE, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
+    if (M == 0) return FP8LIN_OK;
+    if (!x || !input_scale || !xq) return fail(FP8LIN_ERR_NULL, "x, input_scale and xq must not be NULL");
+    if (ldx < K || ldx % 8 != 0 || !aligned16(x) || !aligned16(xq)) return fail(FP8LIN_ERR_ALIGN, "x/xq alignment or ldx");
+    cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, (unsigned char*)xq, M, K, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
+    static thread_local char buf[64];
+    if (M <= 0 || K <= 0 || N <= 0) return "none";
+    const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
+    if (scheme == FP8LIN_W8A8_STATIC && M > max_m && N % 8 == 0) {
+        UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
+        snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s%d", pl.bn, pl.splits);
+        return buf;
+    }
+    StreamPlan sp = plan_stream(scheme, M, K, N, g_tune.stream_splits);
+    snprintf(buf, sizeof(buf), "stream_mma_%s_m%d_s%d", scheme == FP8LIN_W8A16 ? "w8a16" : "w8a8", sp.mt * 8, sp.splits);
+    return buf;
+}
+
+int fp8lin_set_tuning(const char* knob, int value) {
+    if (!knob) return fail(FP8LIN_ERR_NULL, "knob is NULL");
+    if (!strcmp(knob, "stream_splits")) g_tune.stream_splits = value;
+    else if (!strcmp(knob, "stream_max_m")) g_tune.stream_max_m = value;
+    else if (!strcmp(knob, "umma_bn")) g_tune.umma_bn = value;
+    else if (!strcmp(knob, "umma_splits")) g_tune.umma_splits = value;
+    else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
+    return FP8LIN_OK;
+}
+
+int fp8lin_read_status(void* workspace, void* stream, int* status_out) {
+    if (!workspace || !status_out) return fail(FP8LIN_ERR_NULL, "workspace and status_out must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    int v = 0;
+    cudaError_t e = cudaMemcpyAsync(&v, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "status read: %s", cudaGetErrorString(e));
+    *status_out = v;
+    if (v != 0) {
+        cudaMemsetAsync(workspace, 0, sizeof(int), st);
+        cudaStreamSynchronize(st);
+        return fail(FP8LIN_ERR_DEVICE, "a kernel gave up a bounded wait (device status 0x%x)", v);
+    }
+    return FP8LIN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,99 @@
+// Shared device helpers for the fp8lin kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fp8lin.h"
+
+namespace fp8lin {
+
+// ---- scratch header ---------------------------------------------------------
+// The first FP8LIN_WS_HEADER_BYTES of the caller's scratch.  Everything in it
+// is zero between calls: counters are reset by the CTA that consumes them.
+constexpr int kWsStatusWords = 64;                                  // word 0 = device status
+constexpr int kWsMaxCounters = FP8LIN_WS_HEADER_BYTES / 4 - kWsStatusWords;
+
+struct WsView {
+    int* status;          // device status word (0 = ok)
+    int* counters;        // kWsMaxCounters split-K arrival counters
+    unsigned char* body;  // shape-dependent area, 256-byte aligned
+    size_t body_bytes;
+};
+
+__host__ __device__ inline WsView ws_view(void* ws, size_t bytes) {
+    WsView v;
+    v.status = reinterpret_cast<int*>(ws);
+    v.counters = reinterpret_cast<int*>(ws) + kWsStatusWords;
+    v.body = reinterpret_cast<unsigned char*>(ws) + FP8LIN_WS_HEADER_BYTES;
+    v.body_bytes = bytes > FP8LIN_WS_HEADER_BYTES ? bytes - FP8LIN_WS_HEADER_BYTES : 0;
+    return v;
+}
+
+// device status codes written by kernels that gave up a bounded wait
+enum : int { kDevOk = 0, kDevTimeoutFull = 0x101, kDevTimeoutEmpty = 0x102, kDevTimeoutTmemFull = 0x103,
+             kDevTimeoutTmemEmpty = 0x104 };
+
+// ---- small numeric helpers ----------------------------------------------------
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+
+// Two floats -> two e4m3 bytes (lo in bits 0-7), RNE, saturating to +-448.
+__device__ __forceinline__ uint16_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Two e4m3 bytes -> packed f16x2 (exact).
+__device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint16_t v) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+    return r;
+}
+
+// Static activation quantiser for 8 bf16 values (one 16-byte word) -> 8 e4m3 bytes.
+// True IEEE division so the codes equal the reference's torch path bit for bit.
+__device__ __forceinline__ uint2 quant8_e4m3(uint4 v, float s) {
+    uint2 r;
+    uint32_t a = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.x), s), __fdiv_rn(bf16_hi(v.x), s));
+    uint32_t b = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.y), s), __fdiv_rn(bf16_hi(v.y), s));
+    uint32_t c = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.z), s), __fdiv_rn(bf16_hi(v.z), s));
+    uint32_t d = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.w), s), __fdiv_rn(bf16_hi(v.w), s));
+    r.x = a | (b << 16);
+    r.y = c | (d << 16);
+    return r;
+}
+
+// 8 bf16 -> 8 f16 (RNE; exact for every bf16 inside the f16 normal range).
+__device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v) {
+    uint4 r;
+    __half2 h;
+    h = __floats2half2_rn(bf16_lo(v.x), bf16_hi(v.x)); r.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(bf16_lo(v.y), bf16_hi(v.y)); r.y = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(bf16_lo(v.z), bf16_hi(v.z)); r.z = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(bf16_lo(v.w), bf16_hi(v.w)); r.w = *reinterpret_cast<uint32_t*>(&h);
+    return r;
+}
+
+// Streaming 16-byte load that does not pollute L1 (weights are read once).
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ uint4 ld_cached16(const void* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+}  // namespace fp8lin

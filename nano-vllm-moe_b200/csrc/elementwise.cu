@@ -1,0 +1,67 @@
+// HBM-bound helpers: static activation quantiser and the one-off weight transpose.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fp8lin {
+
+// xq[m][k] = e4m3(clamp(x[m][k] / max(s, 1e-12), +-448)).  3 bytes of traffic per
+// element (2 read + 1 written); each thread converts 16 elements per iteration
+// (two 16-byte loads, one 16-byte store), grid-stride over [M][K/16].
+__global__ void __launch_bounds__(256)
+act_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ input_scale,
+                 unsigned char* __restrict__ xq, int64_t M, int64_t K) {
+    const float s = fmaxf(__ldg(input_scale), 1e-12f);
+    const int64_t vec_per_row = K / 16;
+    const int64_t total = M * vec_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / vec_per_row;
+        const int64_t c = (i - r * vec_per_row) * 16;
+        const uint4* src = reinterpret_cast<const uint4*>(x + r * ldx + c);
+        const uint4 a = __ldg(src);
+        const uint4 b = __ldg(src + 1);
+        const uint2 qa = quant8_e4m3(a, s);
+        const uint2 qb = quant8_e4m3(b, s);
+        *reinterpret_cast<uint4*>(xq + r * K + c) = make_uint4(qa.x, qa.y, qb.x, qb.y);
+    }
+}
+
+cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* input_scale,
+                             unsigned char* xq, int64_t M, int64_t K, cudaStream_t stream) {
+    const int64_t total = M * (K / 16);
+    if (total == 0) return cudaSuccess;
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = 148 * 16;
+    if (blocks > cap) blocks = cap;
+    act_quant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, input_scale, xq, M, K);
+    return cudaGetLastError();
+}
+
+// dst[n][k] = src[k][n] for bytes, 64x64 tiles through shared memory.
+__global__ void __launch_bounds__(256)
+transpose_u8_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, int64_t K, int64_t N) {
+    __shared__ unsigned char tile[64][64 + 4];
+    const int64_t k0 = (int64_t)blockIdx.y * 64;
+    const int64_t n0 = (int64_t)blockIdx.x * 64;
+    const int tx = threadIdx.x & 63;
+    const int ty = threadIdx.x >> 6;  // 0..3
+    for (int r = ty; r < 64; r += 4) {
+        const int64_t k = k0 + r, n = n0 + tx;
+        tile[r][tx] = (k < K && n < N) ? src[k * N + n] : 0;
+    }
+    __syncthreads();
+    for (int r = ty; r < 64; r += 4) {
+        const int64_t n = n0 + r, k = k0 + tx;
+        if (n < N && k < K) dst[n * K + k] = tile[tx][r];
+    }
+}
+
+cudaError_t launch_transpose_u8(const unsigned char* src_kn, unsigned char* dst_nk, int64_t K, int64_t N,
+                                cudaStream_t stream) {
+    if (K == 0 || N == 0) return cudaSuccess;
+    dim3 grid((unsigned)((N + 63) / 64), (unsigned)((K + 63) / 64));
+    transpose_u8_kernel<<<grid, 256, 0, stream>>>(src_kn, dst_nk, K, N);
+    return cudaGetLastError();
+}
+
+}  // namespace fp8lin

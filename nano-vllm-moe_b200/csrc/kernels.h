@@ -1,0 +1,74 @@
+// Internal launch interfaces between the C-ABI layer (api.cu) and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace fp8lin {
+
+// ---- weight-streaming kernel (stream_kernel.cu) ------------------------------
+struct StreamArgs {
+    const __nv_bfloat16* x;      // [M][ldx]
+    const unsigned char* w;      // [N][K] e4m3
+    const float* w_scale;        // [N]
+    const float* input_scale;    // 1 float (W8A8) or nullptr
+    const __nv_bfloat16* bias;   // [N] or nullptr
+    __nv_bfloat16* y;            // [M][ldy]
+    float* partial;              // split-K scratch
+    int* counters;               // split-K arrival counters (zero between calls)
+    int M, K, N;
+    int ldx, ldy;
+    int k_per_split;
+};
+
+struct StreamPlan {
+    int mt;            // 8-row groups of x per pass: 1, 2, 4 or 8
+    int nwarps;        // warps per CTA (16 output channels each)
+    int m_passes;      // ceil(M / (mt*8))
+    int n_tiles;
+    int splits;
+    int k_per_split;
+    size_t partial_bytes;
+};
+
+StreamPlan plan_stream(int scheme, int64_t M, int64_t K, int64_t N, int force_splits);
+cudaError_t launch_stream(int scheme, const StreamPlan& plan, StreamArgs args, cudaStream_t stream);
+
+// ---- elementwise helpers (elementwise.cu) ------------------------------------
+cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* input_scale,
+                             unsigned char* xq, int64_t M, int64_t K, cudaStream_t stream);
+cudaError_t launch_transpose_u8(const unsigned char* src_kn, unsigned char* dst_nk, int64_t K, int64_t N,
+                                cudaStream_t stream);
+
+// ---- tcgen05 GEMM (umma_gemm.cu) ---------------------------------------------
+struct UmmaArgs {
+    const unsigned char* xq;     // [M][K] e4m3, contiguous (produced by launch_act_quant)
+    const unsigned char* w;      // [N][K] e4m3
+    const float* w_scale;
+    const float* input_scale;
+    const __nv_bfloat16* bias;
+    __nv_bfloat16* y;
+    float* partial;              // split-K scratch (fp32 [splits][M][N])
+    int* counters;
+    int* status;                 // device status word
+    int M, K, N;
+    int ldy;
+};
+
+struct UmmaPlan {
+    int bn;            // tile N: 64, 128 or 256
+    int splits;        // split-K factor
+    int kblocks_per_split;
+    int m_tiles, n_tiles;
+    int grid;          // persistent CTAs
+    size_t partial_bytes;
+};
+
+UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_splits);
+// Returns cudaSuccess or an error; `why` (optional) receives a static description.
+cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why);
+
+}  // namespace fp8lin

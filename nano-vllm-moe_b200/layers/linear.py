@@ -1,0 +1,183 @@
+"""Tensor-parallel linear layers that own the FP8 buffers and call the quant method.
+
+Interface-compatible with the reference's nanovllm/layers/linear.py:15-262
+(constructor arguments, ``weight_loader`` shard ids, ``tp_dim``/``tp_rank``/
+``tp_size`` attributes, ``get_quant_output_offset_size``), so the reference's
+model files and checkpoint loader can use these classes unchanged.
+
+Column-parallel layers split the output channels (N) across the TP group and
+need no communication; the row-parallel layer splits K, adds the bias on rank
+0 only and sums the per-rank bf16 outputs with an NCCL all-reduce.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+
+from ..quantization.base_config import QuantizeMethodBase
+
+
+def divide(numerator: int, denominator: int) -> int:
+    if numerator % denominator != 0:
+        raise AssertionError(f"{numerator} is not divisible by {denominator}")
+    return numerator // denominator
+
+
+def _group_size_rank(group) -> tuple[int, int]:
+    if group is not None:
+        return dist.get_world_size(group), dist.get_rank(group)
+    if dist.is_initialized():
+        return dist.get_world_size(), dist.get_rank()
+    return 1, 0
+
+
+class LinearBase(nn.Module):
+    def __init__(self, input_size: int, output_size: int, tp_dim: int | None = None,
+                 tp_group: Optional[dist.ProcessGroup] = None,
+                 quant_method: QuantizeMethodBase | None = None, **kwargs):
+        super().__init__()
+        self.input_size = input_size
+        self.output_size = output_size
+        self.tp_dim = tp_dim
+        self.tp_group = tp_group
+        self.quant_method = quant_method
+        self.tp_size, self.tp_rank = _group_size_rank(tp_group)
+
+    def is_quantized(self) -> bool:
+        return self.quant_method is not None
+
+    def apply_linear(self, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        if self.quant_method is None:
+            return F.linear(x, self.weight, bias)
+        return self.quant_method.apply(self, x, bias)
+
+    def _make_params(self, k_part: int, n_parts: list[int], bias: bool) -> None:
+        n_part = sum(n_parts)
+        if self.quant_method is None:
+            self.weight = nn.Parameter(torch.empty(n_part, k_part))
+            self.weight.weight_loader = self.weight_loader
+        else:
+            self.quant_method.create_weights(
+                self, input_size_per_partition=k_part, output_partition_sizes=n_parts,
+                input_size=self.input_size, output_size=self.output_size,
+                params_dtype=torch.get_default_dtype())
+        if bias:
+            self.bias = nn.Parameter(torch.empty(n_part))
+            self.bias.weight_loader = self.weight_loader
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:  # pragma: no cover - abstract
+        raise NotImplementedError
+
+
+class ReplicatedLinear(LinearBase):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False,
+                 tp_group: Optional[dist.ProcessGroup] = None, **kwargs):
+        super().__init__(input_size, output_size, tp_group=tp_group, **kwargs)
+        self.quant_method = None
+        self._make_params(input_size, [output_size], bias)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        param.data.copy_(loaded_weight)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, self.weight, self.bias)
+
+
+class ColumnParallelLinear(LinearBase):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False,
+                 tp_group: Optional[dist.ProcessGroup] = None,
+                 quant_method: QuantizeMethodBase | None = None, **kwargs):
+        super().__init__(input_size, output_size, 0, tp_group=tp_group, quant_method=quant_method, **kwargs)
+        self.input_size_per_partition = input_size
+        self.output_size_per_partition = divide(output_size, self.tp_size)
+        self._make_params(input_size, [self.output_size_per_partition], bias)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        rows = param.data.size(self.tp_dim)
+        param.data.copy_(loaded_weight.narrow(self.tp_dim, self.tp_rank * rows, rows))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.apply_linear(x, self.bias)
+
+
+class MergedColumnParallelLinear(ColumnParallelLinear):
+    """Several column-parallel projections fused along N (gate_up): shard ids 0, 1, ..."""
+
+    def __init__(self, input_size: int, output_sizes: list[int], bias: bool = False,
+                 tp_group: Optional[dist.ProcessGroup] = None,
+                 quant_method: QuantizeMethodBase | None = None, **kwargs):
+        self.output_sizes = list(output_sizes)
+        super().__init__(input_size, sum(output_sizes), bias=bias, tp_group=tp_group,
+                         quant_method=quant_method, **kwargs)
+        if self.quant_method is not None:
+            self.output_partition_sizes = [s // self.tp_size for s in self.output_sizes]
+
+    def get_quant_output_offset_size(self, loaded_shard_id: int) -> tuple[int, int]:
+        offset = sum(self.output_sizes[:loaded_shard_id]) // self.tp_size
+        return offset, self.output_sizes[loaded_shard_id] // self.tp_size
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, loaded_shard_id: int):
+        offset, size = self.get_quant_output_offset_size(loaded_shard_id)
+        mine = loaded_weight.chunk(self.tp_size, self.tp_dim)[self.tp_rank]
+        param.data.narrow(self.tp_dim, offset, size).copy_(mine)
+
+
+class QKVParallelLinear(ColumnParallelLinear):
+    """q, k and v projections fused along N and split by heads: shard ids "q", "k", "v"."""
+
+    def __init__(self, hidden_size: int, head_size: int, total_num_heads: int,
+                 total_num_kv_heads: int | None = None, bias: bool = False,
+                 tp_group: Optional[dist.ProcessGroup] = None,
+                 quant_method: QuantizeMethodBase | None = None, **kwargs):
+        self.head_size = head_size
+        self.total_num_heads = total_num_heads
+        self.total_num_kv_heads = total_num_kv_heads or total_num_heads
+        tp_size, _ = _group_size_rank(tp_group)
+        self.num_heads = divide(self.total_num_heads, tp_size)
+        self.num_kv_heads = divide(self.total_num_kv_heads, tp_size)
+        output_size = (self.total_num_heads + 2 * self.total_num_kv_heads) * head_size
+        super().__init__(hidden_size, output_size, bias=bias, tp_group=tp_group,
+                         quant_method=quant_method, **kwargs)
+
+    def get_quant_output_offset_size(self, loaded_shard_id: str) -> tuple[int, int]:
+        q = self.num_heads * self.head_size
+        kv = self.num_kv_heads * self.head_size
+        try:
+            return {"q": (0, q), "k": (q, kv), "v": (q + kv, kv)}[loaded_shard_id]
+        except KeyError:
+            raise AssertionError(f"shard id must be 'q', 'k' or 'v', got {loaded_shard_id!r}") from None
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, loaded_shard_id: str):
+        offset, size = self.get_quant_output_offset_size(loaded_shard_id)
+        mine = loaded_weight.chunk(self.tp_size, self.tp_dim)[self.tp_rank]
+        param.data.narrow(self.tp_dim, offset, size).copy_(mine)
+
+
+class RowParallelLinear(LinearBase):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False, reduce_results: bool = True,
+                 tp_group: Optional[dist.ProcessGroup] = None,
+                 quant_method: QuantizeMethodBase | None = None, **kwargs):
+        super().__init__(input_size, output_size, 1, tp_group=tp_group, quant_method=quant_method, **kwargs)
+        self.input_size_per_partition = divide(input_size, self.tp_size)
+        self.output_size_per_partition = output_size
+        self.reduce_results = reduce_results
+        self._make_params(self.input_size_per_partition, [output_size], bias)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        if param.data.dim() == 1:           # bias: replicated, added on rank 0 only
+            param.data.copy_(loaded_weight)
+            return
+        cols = param.data.size(self.tp_dim)
+        param.data.copy_(loaded_weight.narrow(self.tp_dim, self.tp_rank * cols, cols))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.apply_linear(x, self.bias if self.tp_rank == 0 else None)
+        if self.tp_size > 1 and self.reduce_results:
+            dist.all_reduce(y, group=self.tp_group)
+        return y

@@ -1,0 +1,159 @@
+"""Functional launchers over the C ABI — the calls ``Fp8LinearMethod.apply`` makes.
+
+They take torch CUDA tensors, pass raw device pointers and the current CUDA
+stream to ``libfp8lin.so`` and return the bf16 result.  Counterparts in the
+reference: ``launch_w8a16_gemm`` (nanovllm/quantization/kernels/fp8.py:79-109),
+``launch_w8a8_cuda_ptx_jit`` (w8a8_jit.py:521-542), ``launch_w8a8_cutlass_gemm``
+(cuda_ext.py:84-106), ``quantize_activation_w8a8`` (kernels/fp8.py:263-268).
+Unlike the reference there is one backend and no environment-variable dispatch;
+the kernel variant is a pure function of (scheme, M, K, N).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _lib
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("fp8lin kernels need CUDA tensors (there is no CPU path)")
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch for the current stream of ``device``, grown on demand.
+
+    One buffer per (device, stream): calls on different streams never share
+    scratch.  Growing allocates, so warm a shape up once before capturing it
+    in a CUDA graph (or call ``reserve_workspace``)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream_ptr(device))
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(nbytes, _lib.WS_HEADER_BYTES)
+        if ws is not None:
+            size = max(size, 2 * ws.numel())
+        ws = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def reserve_workspace(device: torch.device, nbytes: int) -> None:
+    workspace(device, nbytes)
+
+
+def workspace_bytes(scheme: int, m: int, k: int, n: int) -> int:
+    return int(_lib.load().fp8lin_workspace_bytes(scheme, m, k, n))
+
+
+def variant_name(scheme: int, m: int, k: int, n: int) -> str:
+    return _lib.load().fp8lin_variant_name(scheme, m, k, n).decode()
+
+
+def set_tuning(knob: str, value: int) -> None:
+    _lib.raise_for(_lib.load().fp8lin_set_tuning(knob.encode(), int(value)), "fp8lin_set_tuning")
+
+
+def read_status(device: torch.device) -> int:
+    """Blocking check of the device status word of the current stream's scratch."""
+    ws = workspace(device, _lib.WS_HEADER_BYTES)
+    out = ctypes.c_int(0)
+    rc = _lib.load().fp8lin_read_status(ws.data_ptr(), _stream_ptr(device), ctypes.byref(out))
+    _lib.raise_for(rc, "fp8lin_read_status")
+    return out.value
+
+
+def prepack_weight(qweight_kn: torch.Tensor) -> torch.Tensor:
+    """uint8 e4m3 codes [K, N] (the reference's ``qweight`` buffer) -> [N, K]."""
+    _require_cuda(qweight_kn)
+    if qweight_kn.dtype != torch.uint8 or qweight_kn.dim() != 2:
+        raise ValueError("qweight must be a 2-D uint8 tensor [K, N]")
+    src = qweight_kn.contiguous()
+    k, n = src.shape
+    out = torch.empty((n, k), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        rc = _lib.load().fp8lin_prepack_weight(src.data_ptr(), out.data_ptr(), k, n, _stream_ptr(src.device))
+    _lib.raise_for(rc, "fp8lin_prepack_weight")
+    return out
+
+
+def _check_linear_args(x, w_nk, weight_scale, bias):
+    _require_cuda(x, w_nk, weight_scale, bias)
+    if x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise ValueError("x must be a 2-D bfloat16 tensor [M, K]")
+    if w_nk.dim() != 2 or w_nk.dtype not in (torch.uint8, torch.float8_e4m3fn):
+        raise ValueError("w_nk must be a 2-D uint8/float8_e4m3fn tensor [N, K]")
+    if not w_nk.is_contiguous():
+        raise ValueError("w_nk must be contiguous")
+    n, k = w_nk.shape
+    if x.shape[1] != k:
+        raise ValueError(f"x has K={x.shape[1]} but the weight has K={k}")
+    if weight_scale.dtype != torch.float32 or weight_scale.numel() != n:
+        raise ValueError("weight_scale must be float32 with one value per output channel")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n):
+        raise ValueError("bias must be bfloat16 [N]")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    return x, n, k
+
+
+def launch_w8a16_gemm(x: torch.Tensor, w_nk: torch.Tensor, weight_scale: torch.Tensor,
+                      bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 ``(x @ W^T) * weight_scale + bias`` with e4m3 weights [N, K]."""
+    x, n, k = _check_linear_args(x, w_nk, weight_scale, bias)
+    m = x.shape[0]
+    y = out if out is not None else torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        need = workspace_bytes(_lib.W8A16, m, k, n)
+        ws = workspace(x.device, need)
+        rc = _lib.load().fp8lin_w8a16(
+            x.data_ptr(), x.stride(0), w_nk.data_ptr(), weight_scale.data_ptr(),
+            bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0),
+            m, k, n, ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
+    _lib.raise_for(rc, "fp8lin_w8a16")
+    return y
+
+
+def launch_w8a8_gemm(x: torch.Tensor, w_nk: torch.Tensor, input_scale: torch.Tensor,
+                     weight_scale: torch.Tensor, bias: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """Static-scale W8A8: x is quantised to e4m3 with ``input_scale`` inside the call."""
+    x, n, k = _check_linear_args(x, w_nk, weight_scale, bias)
+    _require_cuda(input_scale)
+    if input_scale.dtype != torch.float32 or input_scale.numel() != 1:
+        raise ValueError("input_scale must be one float32 value on the device")
+    m = x.shape[0]
+    y = out if out is not None else torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        need = workspace_bytes(_lib.W8A8_STATIC, m, k, n)
+        ws = workspace(x.device, need)
+        rc = _lib.load().fp8lin_w8a8(
+            x.data_ptr(), x.stride(0), w_nk.data_ptr(), weight_scale.data_ptr(), input_scale.data_ptr(),
+            bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0),
+            m, k, n, ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
+    _lib.raise_for(rc, "fp8lin_w8a8")
+    return y
+
+
+def quantize_activation(x: torch.Tensor, input_scale: torch.Tensor) -> torch.Tensor:
+    """bf16 [M, K] -> e4m3 codes (uint8) with one static scale."""
+    _require_cuda(x, input_scale)
+    if x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise ValueError("x must be a 2-D bfloat16 tensor")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    m, k = x.shape
+    out = torch.empty((m, k), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().fp8lin_quantize_activation(x.data_ptr(), x.stride(0), input_scale.data_ptr(),
+                                                    out.data_ptr(), m, k, _stream_ptr(x.device))
+    _lib.raise_for(rc, "fp8lin_quantize_activation")
+    return out

@@ -1,0 +1,182 @@
+"""Host-side logic that needs no GPU: buffer/loader parity with the reference
+(golden fixtures), the C-ABI surface, and argument validation."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+class FakeTP:
+    """Pretend to be rank ``rank`` of ``size`` without a process group (the
+    layers only query world size and rank)."""
+
+    def __init__(self, size, rank):
+        self.size, self.rank = size, rank
+
+    def __enter__(self):
+        self.saved = (dist.is_initialized, dist.get_world_size, dist.get_rank)
+        dist.is_initialized = lambda: True
+        dist.get_world_size = lambda group=None: self.size
+        dist.get_rank = lambda group=None: self.rank
+
+    def __exit__(self, *exc):
+        dist.is_initialized, dist.get_world_size, dist.get_rank = self.saved
+
+
+def _build_layers(pkg, g, tp, rank):
+    T = lambda a: torch.from_numpy(np.array(a))
+    with FakeTP(tp, rank):
+        cfg = pkg.Fp8Config("fp8_w8a8_static")
+        col = pkg.ColumnParallelLinear(64, 80, bias=True, quant_method=cfg.get_quant_method(None, "col"))
+        col.qweight.weight_loader(col.qweight, T(g["ckpt_col_q"]))
+        col.weight_scale.weight_loader(col.weight_scale, T(g["ckpt_col_s"]))
+        col.input_scale.weight_loader(col.input_scale, T(g["ckpt_in_s"]))
+        mrg = pkg.MergedColumnParallelLinear(64, [96, 32], quant_method=cfg.get_quant_method(None, "gate_up"))
+        for sid, nm in ((0, "gate"), (1, "up")):
+            mrg.qweight.weight_loader(mrg.qweight, T(g[f"ckpt_{nm}_q"]), sid)
+            mrg.weight_scale.weight_loader(mrg.weight_scale, T(g[f"ckpt_{nm}_s"]), sid)
+        mrg.input_scale.weight_loader(mrg.input_scale, T(g["ckpt_in_s"]))
+        qkv = pkg.QKVParallelLinear(64, 16, 4, 2, bias=True, quant_method=cfg.get_quant_method(None, "qkv"))
+        for sid in ("q", "k", "v"):
+            qkv.qweight.weight_loader(qkv.qweight, T(g[f"ckpt_{sid}_q"]), sid)
+            qkv.weight_scale.weight_loader(qkv.weight_scale, T(g[f"ckpt_{sid}_s"]), sid)
+        qkv.input_scale.weight_loader(qkv.input_scale, T(g["ckpt_in_s"]))
+        row = pkg.RowParallelLinear(128, 48, bias=True, quant_method=cfg.get_quant_method(None, "down"))
+        row.qweight.weight_loader(row.qweight, T(g["ckpt_row_q"]))
+        row.weight_scale.weight_loader(row.weight_scale, T(g["ckpt_row_s"]))
+        row.input_scale.weight_loader(row.input_scale, T(g["ckpt_in_s"]))
+        col2 = pkg.ColumnParallelLinear(64, 80, quant_method=pkg.Fp8Config("fp8_w8a16").get_quant_method(None, "c2"))
+        col2.weight_scale.weight_loader(col2.weight_scale, torch.tensor([0.25]))
+    return {"col": col, "mrg": mrg, "qkv": qkv, "row": row, "col2": col2}
+
+
+@pytest.mark.parametrize("tp,rank", [(1, 0), (2, 0), (2, 1)])
+def test_loaders_fill_buffers_like_the_reference(pkg, golden, tp, rank):
+    g = golden("loaders")
+    layers = _build_layers(pkg, g, tp, rank)
+    for nm in ("col", "mrg", "qkv", "row"):
+        tag = f"tp{tp}_r{rank}_{nm}"
+        lay = layers[nm]
+        assert lay.qweight.dtype == torch.uint8 and lay.weight_scale.dtype == torch.float32
+        np.testing.assert_array_equal(lay.qweight.numpy(), g[tag + "_qweight"])
+        np.testing.assert_array_equal(lay.weight_scale.numpy(), g[tag + "_weight_scale"])
+        np.testing.assert_array_equal(lay.input_scale.numpy(), g[tag + "_input_scale"])
+    # scalar weight scale: the reference fills element 0 only (the rest of its buffer is
+    # uninitialised memory); this build broadcasts the value to every channel
+    assert layers["col2"].weight_scale.numpy()[0] == g[f"tp{tp}_r{rank}_col2_weight_scale"][0]
+    np.testing.assert_array_equal(layers["col2"].weight_scale.numpy(), np.full(80 // tp, 0.25, np.float32))
+    assert hasattr(layers["col2"], "input_scale") == bool(g[f"tp{tp}_r{rank}_has_input_scale_w8a16"])
+
+
+def test_layer_attributes_match_reference_contract(pkg):
+    with FakeTP(2, 1):
+        qkv = pkg.QKVParallelLinear(64, 16, 4, 2, quant_method=pkg.Fp8Config().get_quant_method(None))
+    assert (qkv.tp_dim, qkv.tp_size, qkv.tp_rank) == (0, 2, 1)
+    assert (qkv.num_heads, qkv.num_kv_heads) == (2, 1)
+    assert qkv.get_quant_output_offset_size("k") == (32, 16)
+    with pytest.raises(AssertionError):
+        with FakeTP(8, 0):
+            pkg.QKVParallelLinear(3584, 128, 28, 4)          # 28 heads do not divide by 8
+    with FakeTP(4, 3):
+        row = pkg.RowParallelLinear(128, 48, quant_method=pkg.Fp8Config().get_quant_method(None))
+    assert row.tp_dim == 1 and row.input_size_per_partition == 32 and row.qweight.shape == (32, 48)
+
+
+def test_config_registry(pkg):
+    class HF:
+        quantization_type = "fp8_w8a8_static"
+    cfg = pkg.get_quant_config(HF())
+    assert isinstance(cfg, pkg.Fp8Config) and cfg.get_name() == "fp8"
+    assert pkg.get_quant_config(object()) is None
+    with pytest.raises(ValueError):
+        pkg.Fp8Config("int4")
+    assert isinstance(cfg.get_quant_method(None, "x"), pkg.QuantizeMethodBase)
+
+
+def test_apply_raises_on_cpu_like_the_reference(pkg):
+    for scheme, text in (("fp8_w8a8_static", "FP8 W8A8 static requires CUDA"), ("fp8_w8a16", "requires CUDA")):
+        lay = pkg.ColumnParallelLinear(32, 16, quant_method=pkg.Fp8Config(scheme).get_quant_method(None))
+        pkg.process_weights_after_loading(lay)            # no-op on CPU, as in the reference
+        with pytest.raises(RuntimeError, match=text):
+            lay(torch.zeros(2, 32, dtype=torch.bfloat16))
+
+
+def test_unquantized_layers_still_work(pkg):
+    lay = pkg.ColumnParallelLinear(8, 4, bias=True)
+    lay.weight.weight_loader(lay.weight, torch.eye(4, 8))
+    lay.bias.weight_loader(lay.bias, torch.ones(4))
+    y = lay(torch.ones(2, 8))
+    np.testing.assert_allclose(y.detach().numpy(), np.full((2, 4), 2.0))
+
+
+# ---- the C ABI ----------------------------------------------------------------
+
+def _declared_symbols():
+    text = (ROOT / "include" / "fp8lin.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fp8lin_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = pkg._lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/fp8lin.h but not exported"
+        assert n in pkg._lib.SIGNATURES, f"{n} has no ctypes prototype"
+    assert lib.fp8lin_version() == 1
+
+
+def test_argument_validation_without_a_gpu(pkg):
+    lib = pkg._lib.load()
+    L = pkg._lib
+    buf = ctypes.create_string_buffer(4096)
+    p = (ctypes.addressof(buf) + 255) & ~255
+    # K not a multiple of 16
+    rc = lib.fp8lin_w8a8(p, 40, p, p, p, None, p, 64, 1, 40, 64, None, 0, None)
+    assert rc == L.ERR_SHAPE and "multiple of 16" in L.last_error()
+    rc = lib.fp8lin_w8a16(None, 64, p, p, None, p, 64, 1, 64, 64, None, 0, None)
+    assert rc == L.ERR_NULL
+    rc = lib.fp8lin_w8a16(p + 2, 64, p, p, None, p, 64, 1, 64, 64, None, 0, None)
+    assert rc == L.ERR_ALIGN
+    rc = lib.fp8lin_w8a16(p, 32, p, p, None, p, 64, 1, 64, 64, None, 0, None)
+    assert rc == L.ERR_SHAPE                                  # ldx < K
+    assert lib.fp8lin_w8a16(p, 64, p, p, None, p, 64, 0, 64, 64, None, 0, None) == L.OK   # M == 0: nothing to do
+    assert lib.fp8lin_set_tuning(b"no_such_knob", 1) == L.ERR_ARG
+    assert lib.fp8lin_prepack_weight(None, p, 64, 64, None) == L.ERR_NULL
+    with pytest.raises(ValueError):
+        L.raise_for(L.ERR_SHAPE, "x")
+    with pytest.raises(RuntimeError):
+        L.raise_for(L.ERR_LAUNCH, "x")
+
+
+def test_workspace_and_variant_queries(pkg):
+    lib = pkg._lib.load()
+    L = pkg._lib
+    assert lib.fp8lin_packed_bytes(2048, 11008) == 2048 * 11008
+    for scheme in (L.W8A16, L.W8A8_STATIC):
+        for m, k, n in [(1, 2048, 2048), (16, 2048, 11008), (256, 11008, 2048), (1024, 2048, 11008), (64, 18944, 3584)]:
+            need = lib.fp8lin_workspace_bytes(scheme, m, k, n)
+            assert need >= L.WS_HEADER_BYTES and need % 256 == 0
+            assert need < (1 << 31)
+    assert lib.fp8lin_variant_name(L.W8A8_STATIC, 1024, 2048, 11008).decode().startswith("umma_w8a8_128x")
+    assert lib.fp8lin_variant_name(L.W8A8_STATIC, 16, 2048, 11008).decode().startswith("stream_mma_w8a8_m16")
+    assert lib.fp8lin_variant_name(L.W8A16, 1, 2048, 2048).decode().startswith("stream_mma_w8a16_m8")
+
+
+def test_kernels_refuse_cpu_tensors(pkg):
+    from importlib import import_module
+    K = import_module("nano-vllm-moe_b200.quantization.kernels")
+    x = torch.zeros(2, 32, dtype=torch.bfloat16)
+    w = torch.zeros(16, 32, dtype=torch.uint8)
+    s = torch.ones(16)
+    with pytest.raises(ValueError, match="CUDA"):
+        K.launch_w8a16_gemm(x, w, s)
+    with pytest.raises(ValueError, match="CUDA"):
+        K.launch_w8a8_gemm(x, w, torch.ones(()), s)
