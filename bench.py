@@ -120,7 +120,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def mark(self):
+        """Index of the next sample; brackets the timed region."""
+        return len(self.lines)
+
+    def stop(self, first=0, last=None):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -130,7 +134,11 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        window = self.lines[first:last]
+        scope = "timed region"
+        if not window:
+            window, scope = self.lines, "whole run (timed region shorter than one sample)"
+        for line in window:
             f = [s.strip() for s in line.split(",")]
             if len(f) < 9:
                 continue
@@ -142,7 +150,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "scope": scope, "reasons": sorted(reasons)}
 
 
 # --------------------------------------------------------------------------- reference arm (CPU)
@@ -186,8 +194,8 @@ def run_reference_arm(args, scheme, ops, flops):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -233,8 +241,8 @@ def main():
             q, s = make_weights(k, n, SEED + 1000 * c + 10 * i, dev)
             x, bias, in_scale = make_inputs(m, k, n, SEED + 10 * i + 1, dev)
             cls = pkg.ColumnParallelLinear if kind == "col" else pkg.RowParallelLinear
-            lay = cls(k, n, bias=True, quant_method=cfg.get_quant_method(None, label))
-            lay = lay.to(dev)
+            with torch.device(dev):   # buffers are created on the GPU, as the reference's runner does
+                lay = cls(k, n, bias=True, quant_method=cfg.get_quant_method(None, label))
             lay.qweight.weight_loader(lay.qweight, q)
             lay.weight_scale.weight_loader(lay.weight_scale, s)
             if scheme == "fp8_w8a8_static":
@@ -294,12 +302,17 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        t_wait = time.time()
+        while sampler.mark() == 0 and time.time() - t_wait < 3.0:   # nvidia-smi takes a moment to start
+            step(0)
+            torch.cuda.synchronize()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    mark0 = sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -308,7 +321,7 @@ def main():
     e1.record()
     barrier()
     ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(mark0, sampler.mark()) if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms_total], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
