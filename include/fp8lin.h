@@ -5,9 +5,10 @@
  * (nanovllm/quantization/fp8.py, Fp8LinearMethod.apply).  Every pointer is a
  * CUDA device pointer unless stated otherwise; `stream` is a cudaStream_t
  * passed as void*.  All calls are asynchronous on `stream`, allocate nothing
- * on the device, never synchronise the host (except fp8lin_read_status) and
- * are safe to capture in a CUDA graph.  The library owns no tensor: every
- * buffer, including scratch, belongs to the caller.
+ * on the device and never synchronise the host (except fp8lin_read_status);
+ * the linears that take a caller-owned workspace are safe to capture in a CUDA
+ * graph.  The library owns no tensor: every buffer, including scratch, belongs
+ * to the caller (the one exception, fp8lin_linear_static_scratch, says so).
  *
  * Number formats
  *   activations x, bias, outputs y : bfloat16, row-major, row strides ldx/ldy in ELEMENTS
@@ -92,6 +93,22 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
                 const float* input_scale, const void* bias, void* y, int64_t ldy,
                 int64_t M, int64_t K, int64_t N,
                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Decode-sized linear (M <= 64, either scheme) that needs no workspace from the
+ * caller and allocates nothing.  It has no counterpart in the reference; it
+ * exists for callers that cannot allocate: a server whose KV-cache pool has
+ * taken all free HBM, or a latency-critical loop that must not risk the stall
+ * an allocation can cause.  Its split-K scratch is a fixed 16 MiB (+64 KiB
+ * header) array inside the library image, one copy per GPU, held from library
+ * load to process exit.  Shapes whose split-K partial sums exceed 16 MiB, or
+ * M > 64, are refused with FP8LIN_ERR_WORKSPACE.  The first call on each GPU
+ * looks up the array's device address (cudaGetSymbolAddress) -- make that
+ * first call outside any stream capture.  All calls on a GPU share the array:
+ * calls that may overlap in time (different streams or threads) race on it and
+ * must be serialised by the caller.  input_scale is ignored for FP8LIN_W8A16. */
+int fp8lin_linear_static_scratch(int scheme, const void* x, int64_t ldx, const void* w_nk,
+                                 const float* w_scale, const float* input_scale, const void* bias,
+                                 void* y, int64_t ldy, int64_t M, int64_t K, int64_t N, void* stream);
 
 /* Stand-alone activation quantiser; replaces quantize_activation_kernel
  * (csrc/w8a8_cutlass_kernel.cu:406-430) / act_quant_fp8_kernel (kernels/fp8.py:232-249).

@@ -63,6 +63,16 @@ bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
 
 }  // namespace
 
+namespace fp8lin {
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+}  // namespace fp8lin
+
 extern "C" {
 
 int fp8lin_version(void) { return FP8LIN_VERSION; }

@@ -9,6 +9,9 @@
 
 namespace fp8lin {
 
+// Record a printf-style message for fp8lin_last_error() and return `code` (defined in api.cu).
+int set_error(int code, const char* fmt, ...);
+
 // ---- weight-streaming kernel (stream_kernel.cu) ------------------------------
 struct StreamArgs {
     const __nv_bfloat16* x;      // [M][ldx]
