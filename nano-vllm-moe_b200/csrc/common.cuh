@@ -60,16 +60,36 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint16_t v) {
     return r;
 }
 
-// Static activation quantiser for 8 bf16 values (one 16-byte word) -> 8 e4m3 bytes.
-// True IEEE division so the codes equal the reference's torch path bit for bit.
-__device__ __forceinline__ uint2 quant8_e4m3(uint4 v, float s) {
+// Correctly rounded x / s in three instructions, given r = 1/s rounded to nearest
+// (Markstein): q0 = x*r is within an ulp, the FMA residual e = x - q0*s is exact,
+// and q0 + e*r rounds to the true quotient.  Overflowing or non-finite q0 is
+// returned as is (the exact division overflows there too), and so is a zero q0
+// (the correction would turn -0 into +0), so the saturating e4m3 conversion
+// that follows sees the same value as after a true division.
+struct ExactDiv {
+    float s, r;
+    __device__ __forceinline__ explicit ExactDiv(float scale) {
+        s = scale;
+        r = __fdiv_rn(1.0f, scale);
+    }
+    __device__ __forceinline__ float operator()(float x) const {
+        const float q0 = x * r;
+        const float e = fmaf(-q0, s, x);
+        const float q1 = fmaf(e, r, q0);
+        return (fabsf(q0) <= 3.0e38f && q0 != 0.f) ? q1 : q0;
+    }
+};
+
+// Static activation quantiser for 8 bf16 values (one 16-byte word) -> 8 e4m3 bytes;
+// the codes equal the reference's torch path (true division, RNE, clamp to +-448) bit for bit.
+__device__ __forceinline__ uint2 quant8_e4m3(uint4 v, const ExactDiv& d) {
     uint2 r;
-    uint32_t a = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.x), s), __fdiv_rn(bf16_hi(v.x), s));
-    uint32_t b = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.y), s), __fdiv_rn(bf16_hi(v.y), s));
-    uint32_t c = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.z), s), __fdiv_rn(bf16_hi(v.z), s));
-    uint32_t d = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.w), s), __fdiv_rn(bf16_hi(v.w), s));
+    uint32_t a = cvt_e4m3x2(d(bf16_lo(v.x)), d(bf16_hi(v.x)));
+    uint32_t b = cvt_e4m3x2(d(bf16_lo(v.y)), d(bf16_hi(v.y)));
+    uint32_t c = cvt_e4m3x2(d(bf16_lo(v.z)), d(bf16_hi(v.z)));
+    uint32_t e = cvt_e4m3x2(d(bf16_lo(v.w)), d(bf16_hi(v.w)));
     r.x = a | (b << 16);
-    r.y = c | (d << 16);
+    r.y = c | (e << 16);
     return r;
 }
 

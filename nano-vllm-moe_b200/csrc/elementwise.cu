@@ -10,7 +10,7 @@ namespace fp8lin {
 __global__ void __launch_bounds__(256)
 act_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ input_scale,
                  unsigned char* __restrict__ xq, int64_t M, int64_t K) {
-    const float s = fmaxf(__ldg(input_scale), 1e-12f);
+    const ExactDiv s(fmaxf(__ldg(input_scale), 1e-12f));
     const int64_t vec_per_row = K / 16;
     const int64_t total = M * vec_per_row;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;

@@ -102,6 +102,7 @@ stream_linear_kernel(StreamArgs p) {
 
     float in_scale = 1.f;
     if (SCHEME == FP8LIN_W8A8_STATIC) in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
+    const ExactDiv div_scale(in_scale);
 
     float acc[MT][4];
 #pragma unroll
@@ -131,7 +132,10 @@ stream_linear_kernel(StreamArgs p) {
             const int r = v / XS::kVecPerRow;
             const int c = (v % XS::kVecPerRow) * 8;
             if (SCHEME == FP8LIN_W8A8_STATIC) {
-                *reinterpret_cast<uint2*>(base + r * XT::kRowBytes + c) = quant8_e4m3(xr[i], in_scale);
+                // rows beyond M (and K tails) were loaded as zeros: nothing to convert
+                const bool zero = (xr[i].x | xr[i].y | xr[i].z | xr[i].w) == 0u;
+                *reinterpret_cast<uint2*>(base + r * XT::kRowBytes + c) =
+                    zero ? make_uint2(0u, 0u) : quant8_e4m3(xr[i], div_scale);
             } else {
                 *reinterpret_cast<uint4*>(base + r * XT::kRowBytes + c * 2) = bf16x8_to_f16x8(xr[i]);
             }

@@ -40,7 +40,9 @@ struct UmmaCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+    // epilogue staging: per epilogue warp two 32-row x 128-byte boxes (4 KiB each)
+    static constexpr int kStagingBytes = 4 * 2 * 4096;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
 };
 
 // ---- PTX wrappers --------------------------------------------------------------
@@ -78,6 +80,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+
+// TMA store of one shared-memory box; elements outside the tensor are not written,
+// which is what clips the M and N tails.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
@@ -155,6 +171,7 @@ __device__ __forceinline__ void decode_work(const UmmaSched& s, int w, int& tm, 
 template <int BN>
 __global__ void __launch_bounds__(192, 1)
 umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_part,
                  UmmaArgs p, UmmaSched sched) {
     using Cfg = UmmaCfg<BN>;
     constexpr int S = Cfg::kStages;
@@ -256,9 +273,20 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
     } else {
         // ================= epilogue (warps 2..5) =================
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        // Each warp owns TMEM lanes [32q, 32q+32) = 32 rows of the tile.  A lane holds one
+        // row; 32 columns at a time come out of TMEM, are scaled/biased/rounded and written
+        // to a 32-row x 128-byte staging box in shared memory in the 128-byte-swizzle
+        // pattern (16-byte chunk index XOR row&7, bank-conflict free), and lane 0 hands
+        // the box to a TMA store.  Two boxes per warp alternate so the next 64 columns
+        // are converted while the previous store drains.
+        const int q = warp & 3;
+        const int ew = warp - 2;                                   // 0..3: staging slot
         const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
+        const uint32_t stage0 = smem_base + S * Cfg::kStageBytes + ew * 8192;
+        const uint32_t row_off = lane * 128;
+        const uint32_t sw = lane & 7;
         int tl = 0;
+        uint32_t nstore = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < sched.total_work && ok; w += gridDim.x, ++tl) {
             int tm, tn, split;
@@ -271,24 +299,26 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 s_abort = 1; ok = false; break;
             }
             tc_fence_after();
-            const int row = tm * kBM + q * 32 + lane;
-            const bool row_ok = row < p.M;
+            const int row0 = tm * kBM + q * 32;                    // first row of this warp's box
             const int n0 = tn * BN;
             const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
 
             if (sched.splits == 1) {
-                __nv_bfloat16* yrow = p.y + (size_t)row * p.ldy;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    __syncwarp();
-                    tmem_ld32(t_addr + c * 32, v);
                     const int nc = n0 + c * 32;
-                    if (nc >= p.N) continue;
+                    if (nc >= p.N) break;                          // uniform: whole chunk is past N
+                    const uint32_t box = stage0 + ((nstore & 1) * 4096);
+                    if ((c & 1) == 0) {
+                        // the store issued two boxes ago read this buffer: wait until it is done with it
+                        if (lane == 0) tma_store_wait_read<1>();
+                        __syncwarp();
+                    }
+                    uint32_t v[32];
+                    tmem_ld32(t_addr + c * 32, v);
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
-                        const int n = nc + j;
-                        if (n >= p.N) break;
+                        const int n = min(nc + j, p.N - 8);        // clamp keeps the loads in bounds; TMA clips the store
                         const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.w_scale + n));
                         const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.w_scale + n + 4));
                         float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -301,39 +331,51 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         float o[8];
 #pragma unroll
                         for (int e = 0; e < 8; ++e) o[e] = fmaf(__uint_as_float(v[j + e]) * in_scale, sc[e], b[e]);
-                        if (row_ok) {
-                            uint4 out;
-                            out.x = pack_bf16x2(o[0], o[1]); out.y = pack_bf16x2(o[2], o[3]);
-                            out.z = pack_bf16x2(o[4], o[5]); out.w = pack_bf16x2(o[6], o[7]);
-                            *reinterpret_cast<uint4*>(yrow + n) = out;
-                        }
+                        const uint32_t chunk = (uint32_t)((c & 1) * 4 + (j >> 3));
+                        const uint32_t dst = box + row_off + ((chunk ^ sw) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                     "r"(pack_bf16x2(o[0], o[1])), "r"(pack_bf16x2(o[2], o[3])),
+                                     "r"(pack_bf16x2(o[4], o[5])), "r"(pack_bf16x2(o[6], o[7])) : "memory");
+                    }
+                    if ((c & 1) == 1 || nc + 32 >= p.N) {
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) tma_store_2d(&tmap_y, box, n0 + (c & ~1) * 32, row0);
+                        ++nstore;
                     }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
             } else {
-                // split-K: park the fp32 tile, last arriver reduces
-                float* prow = p.partial + ((size_t)split * p.M + row) * p.N;
+                // split-K: park the fp32 tile in scratch ([split][m_tiles*128][N]); a box is 32 rows x 32 floats
+                const int prow0 = (split * sched.m_tiles + tm) * kBM + q * 32;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    __syncwarp();
-                    tmem_ld32(t_addr + c * 32, v);
                     const int nc = n0 + c * 32;
-                    if (nc < p.N && row_ok) {
+                    if (nc >= p.N) break;
+                    const uint32_t box = stage0 + ((nstore & 1) * 4096);
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    uint32_t v[32];
+                    tmem_ld32(t_addr + c * 32, v);
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            if (nc + j < p.N)
-                                __stcg(reinterpret_cast<float4*>(prow + nc + j),
-                                       make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                   __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])));
-                        }
+                    for (int j = 0; j < 32; j += 4) {
+                        const uint32_t dst = box + row_off + ((((uint32_t)j >> 2) ^ sw) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[j]), "r"(v[j + 1]),
+                                     "r"(v[j + 2]), "r"(v[j + 3]) : "memory");
                     }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) tma_store_2d(&tmap_part, box, nc, prow0);
+                    ++nstore;
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(&bar_tempty[as]));
+                    tma_store_wait_all();          // this warp's partial rows are in global memory
+                }
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) {
@@ -345,38 +387,38 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 const bool last = s_last != 0;
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // s_last may be rewritten next tile
-                if (last && row_ok) {
+                if (last) {
                     __threadfence();
-                    __nv_bfloat16* yrow = p.y + (size_t)row * p.ldy;
-                    for (int n = n0; n < min(n0 + BN, p.N); n += 8) {
-                        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        for (int s = 0; s < sched.splits; ++s) {
-                            const float* ps = p.partial + ((size_t)s * p.M + row) * p.N + n;
-                            const float4 u0 = __ldcg(reinterpret_cast<const float4*>(ps));
-                            const float4 u1 = __ldcg(reinterpret_cast<const float4*>(ps + 4));
-                            a[0] += u0.x; a[1] += u0.y; a[2] += u0.z; a[3] += u0.w;
-                            a[4] += u1.x; a[5] += u1.y; a[6] += u1.z; a[7] += u1.w;
+                    // coalesced reduction: the warp walks its 32 rows, lanes span the columns
+                    const int ncols = min(BN, p.N - n0);
+                    const size_t split_stride = (size_t)sched.m_tiles * kBM * p.N;
+                    for (int r = 0; r < 32; ++r) {
+                        const int row = tm * kBM + q * 32 + r;
+                        if (row >= p.M) break;
+                        const float* prow = p.partial + (size_t)row * p.N + n0;
+                        __nv_bfloat16* yrow = p.y + (size_t)row * p.ldy + n0;
+                        for (int cc = lane * 4; cc < ncols; cc += 128) {
+                            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (int sp = 0; sp < sched.splits; ++sp) {
+                                const float4 u = __ldcg(reinterpret_cast<const float4*>(prow + sp * split_stride + cc));
+                                a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+                            }
+                            const float4 sc = __ldg(reinterpret_cast<const float4*>(p.w_scale + n0 + cc));
+                            float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+                            if (p.bias) {
+                                const uint2 bv = __ldg(reinterpret_cast<const uint2*>(p.bias + n0 + cc));
+                                b0 = bf16_lo(bv.x); b1 = bf16_hi(bv.x); b2 = bf16_lo(bv.y); b3 = bf16_hi(bv.y);
+                            }
+                            uint2 out;
+                            out.x = pack_bf16x2(fmaf(a.x * in_scale, sc.x, b0), fmaf(a.y * in_scale, sc.y, b1));
+                            out.y = pack_bf16x2(fmaf(a.z * in_scale, sc.z, b2), fmaf(a.w * in_scale, sc.w, b3));
+                            *reinterpret_cast<uint2*>(yrow + cc) = out;
                         }
-                        const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.w_scale + n));
-                        const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.w_scale + n + 4));
-                        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                        float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (p.bias) {
-                            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
-                            b[0] = bf16_lo(bv.x); b[1] = bf16_hi(bv.x); b[2] = bf16_lo(bv.y); b[3] = bf16_hi(bv.y);
-                            b[4] = bf16_lo(bv.z); b[5] = bf16_hi(bv.z); b[6] = bf16_lo(bv.w); b[7] = bf16_hi(bv.w);
-                        }
-                        float o[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) o[e] = fmaf(a[e] * in_scale, sc[e], b[e]);
-                        uint4 out;
-                        out.x = pack_bf16x2(o[0], o[1]); out.y = pack_bf16x2(o[2], o[3]);
-                        out.z = pack_bf16x2(o[4], o[5]); out.w = pack_bf16x2(o[6], o[7]);
-                        *reinterpret_cast<uint4*>(yrow + n) = out;
                     }
                 }
             }
         }
+        if (lane == 0) tma_store_wait_all();
     }
 
     tc_fence_before();
@@ -419,13 +461,27 @@ static bool encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint
     return r == CUDA_SUCCESS;
 }
 
+// Output-side maps: 2-D tensor [rows][cols] with a row pitch in bytes, box = 128 bytes x 32 rows.
+static bool encode_out_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, uint32_t elem_bytes,
+                          uint64_t rows, uint64_t cols, uint64_t pitch_bytes) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {128u / elem_bytes, 32u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_splits) {
     UmmaPlan best{};
     const int kblocks = (int)((K + kBK - 1) / kBK);
     const int m_tiles = (int)((M + kBM - 1) / kBM);
     double best_cost = 1e30;
     const int bns[3] = {256, 128, 64};
-    const double unit[3] = {1.0, 0.56, 0.36};  // relative time of one K block of a tile (smaller tiles use shared memory less well)
+    const double unit[3] = {1.0, 0.85, 0.6};  // relative time of one K block of a tile (smaller tiles use shared memory less well)
     for (int i = 0; i < 3; ++i) {
         const int bn = bns[i];
         if (force_bn > 0 && bn != force_bn) continue;
@@ -452,7 +508,7 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
             best.bn = bn; best.splits = splits; best.kblocks_per_split = kps;
             best.m_tiles = m_tiles; best.n_tiles = n_tiles;
             best.grid = (int)(work < 148 ? work : 148);
-            best.partial_bytes = splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
+            best.partial_bytes = splits > 1 ? (size_t)splits * m_tiles * kBM * N * sizeof(float) : 0;
         }
     }
     return best;
@@ -460,7 +516,7 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
 
 template <int BN>
 static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb,
-                             cudaStream_t stream) {
+                             const CUtensorMap& ty, const CUtensorMap& tp, cudaStream_t stream) {
     using Cfg = UmmaCfg<BN>;
     auto kern = umma_w8a8_kernel<BN>;
     static bool configured = false;
@@ -473,7 +529,7 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     s.m_tiles = pl.m_tiles; s.n_tiles = pl.n_tiles; s.splits = pl.splits;
     s.kblocks_total = (a.K + kBK - 1) / kBK; s.kblocks_per_split = pl.kblocks_per_split;
     s.total_work = pl.m_tiles * pl.n_tiles * pl.splits;
-    kern<<<pl.grid, 192, Cfg::kSmemBytes, stream>>>(ta, tb, a, s);
+    kern<<<pl.grid, 192, Cfg::kSmemBytes, stream>>>(ta, tb, ty, tp, a, s);
     return cudaGetLastError();
 }
 
@@ -484,10 +540,23 @@ cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }
+    CUtensorMap ty, tp;
+    if (!encode_out_2d(&ty, a.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.M, (uint64_t)a.N,
+                       (uint64_t)a.ldy * 2)) {
+        if (why) *why = "cuTensorMapEncodeTiled failed for y";
+        return cudaErrorInvalidValue;
+    }
+    tp = ty;
+    if (pl.splits > 1 &&
+        !encode_out_2d(&tp, a.partial, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                       (uint64_t)pl.splits * pl.m_tiles * kBM, (uint64_t)a.N, (uint64_t)a.N * 4)) {
+        if (why) *why = "cuTensorMapEncodeTiled failed for the split-K scratch";
+        return cudaErrorInvalidValue;
+    }
     switch (pl.bn) {
-        case 256: return launch_bn<256>(pl, a, ta, tb, stream);
-        case 128: return launch_bn<128>(pl, a, ta, tb, stream);
-        case 64: return launch_bn<64>(pl, a, ta, tb, stream);
+        case 256: return launch_bn<256>(pl, a, ta, tb, ty, tp, stream);
+        case 128: return launch_bn<128>(pl, a, ta, tb, ty, tp, stream);
+        case 64: return launch_bn<64>(pl, a, ta, tb, ty, tp, stream);
     }
     if (why) *why = "unsupported tile width";
     return cudaErrorInvalidValue;

@@ -59,6 +59,30 @@ def test_activation_codes_match_reference_bit_for_bit(golden):
     np.testing.assert_array_equal(got, O.quantize_activation(from_bf16(view), np.float32(0.0121)))
 
 
+def test_activation_quantiser_exhaustive_over_bf16():
+    """Every finite bf16 value x a set of scales (calibration-like, powers of two, all-ones
+    mantissa, the 1e-12 clamp): the device codes equal true-division codes bit for bit."""
+    Kn = kernels()
+    bits = np.arange(65536, dtype=np.uint32)
+    x = (bits << 16).view(np.float32).reshape(4096, 16)
+    finite = np.isfinite(x)
+    xt = torch.from_numpy(bits.astype(np.int32).astype(np.int16).reshape(4096, 16)).view(torch.bfloat16).cuda()
+    scales = [0.0121, 0.011764526, 1.0, 16.0, 0.5, 3.1e-3, np.float32(1.9999999), np.float32(0.012499999),
+              1e-13, 7.3, 1.0e-5, 2.5e4]
+    rng = np.random.default_rng(12)
+    scales += list(np.exp(rng.uniform(np.log(1e-4), np.log(10.0), 20)).astype(np.float32))
+    for s in scales:
+        s = np.float32(s)
+        got = Kn.quantize_activation(xt, torch.tensor(float(s), dtype=torch.float32, device="cuda")).cpu().numpy()
+        with np.errstate(over="ignore", invalid="ignore"):
+            want = O.quantize_activation(np.where(finite, x, 0), s)
+        np.testing.assert_array_equal(got[finite], want[finite], err_msg=f"scale {s}")
+        inf = np.isinf(x)
+        assert ((got[inf] & 0x7F) == 0x7E).all()              # +-inf saturates to +-448 like clamp()
+        nan = np.isnan(x)
+        assert ((got[nan] & 0x7F) == 0x7F).all()
+
+
 @pytest.mark.parametrize("scheme", SCHEMES)
 def test_golden_random_cases(golden, scheme):
     g = golden("linear")
