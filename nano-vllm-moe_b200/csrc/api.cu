@@ -25,6 +25,8 @@ struct Tuning {
     int stream_max_m = -1;    // largest M routed to the streaming kernel (W8A8)
     int umma_bn = -1;         // force tile width of the tcgen05 kernel
     int umma_splits = -1;     // force split-K factor of the tcgen05 kernel
+    int swap_splits = -1;     // force split-K factor of the swapped-operand decode kernel
+    int swap_enable = -1;     // 0 routes decode-sized W8A8 to the mma.sync streaming kernel instead
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -54,6 +56,11 @@ int validate_common(const void* x, int64_t ldx, const void* w, const float* w_sc
         return fail(FP8LIN_ERR_ALIGN, "x, w_nk, w_scale and bias must be 16-byte aligned");
     if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
     return FP8LIN_OK;
+}
+
+bool swap_eligible(int64_t M) {
+    const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
+    return g_tune.swap_enable != 0 && M <= 64 && M <= max_m;
 }
 
 bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
@@ -138,6 +145,19 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
     if (rc != FP8LIN_OK || M == 0) return rc;
     if (!input_scale) return fail(FP8LIN_ERR_NULL, "input_scale must not be NULL");
     cudaStream_t st = (cudaStream_t)stream;
+    if (swap_eligible(M)) {
+        SwapPlan sp = plan_swap(M, K, N, g_tune.swap_splits);
+        WsView wsv = ws_view(workspace, workspace_bytes);
+        if (!workspace) return fail(FP8LIN_ERR_WORKSPACE, "workspace (at least the %d-byte header) is required", FP8LIN_WS_HEADER_BYTES);
+        UmmaArgs a;
+        a.xq = nullptr; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
+        a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y; a.partial = nullptr; a.counters = nullptr;
+        a.status = wsv.status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ldy;
+        const char* why = nullptr;
+        cudaError_t e = launch_swap_w8a8(sp, a, x, ldx, st, &why);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 decode kernel launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+        return FP8LIN_OK;
+    }
     if (!umma_eligible(M, N, ldy, y))
         return run_stream(FP8LIN_W8A8_STATIC, x, ldx, w_nk, w_scale, input_scale, bias, y, ldy, M, K, N, workspace,
                           workspace_bytes, st);
@@ -182,6 +202,11 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
         snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s%d", pl.bn, pl.splits);
         return buf;
     }
+    if (scheme == FP8LIN_W8A8_STATIC && swap_eligible(M)) {
+        SwapPlan pl = plan_swap(M, K, N, g_tune.swap_splits);
+        snprintf(buf, sizeof(buf), "umma_swap_w8a8_m%d_s%d", pl.mp, pl.splits);
+        return buf;
+    }
     StreamPlan sp = plan_stream(scheme, M, K, N, g_tune.stream_splits);
     snprintf(buf, sizeof(buf), "stream_mma_%s_m%d_s%d", scheme == FP8LIN_W8A16 ? "w8a16" : "w8a8", sp.mt * 8, sp.splits);
     return buf;
@@ -193,6 +218,8 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "stream_max_m")) g_tune.stream_max_m = value;
     else if (!strcmp(knob, "umma_bn")) g_tune.umma_bn = value;
     else if (!strcmp(knob, "umma_splits")) g_tune.umma_splits = value;
+    else if (!strcmp(knob, "swap_splits")) g_tune.swap_splits = value;
+    else if (!strcmp(knob, "swap_enable")) g_tune.swap_enable = value;
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;
 }

@@ -74,4 +74,19 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
 // Returns cudaSuccess or an error; `why` (optional) receives a static description.
 cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why);
 
+// ---- swapped-operand tcgen05 kernel for M <= 64 (umma_swap.cu) -------------------
+struct SwapPlan {
+    int mp;            // token tile (MMA N): 16, 32 or 64
+    int n_tiles;       // 128-channel tiles
+    int splits;        // cluster split-K factor (1 = persistent over tiles)
+    int kblocks_per_split;
+    int grid;
+};
+
+SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits);
+// `a.xq`, `a.partial`, `a.counters` are unused: x is quantised inside the kernel and split-K
+// is reduced through cluster shared memory.
+cudaError_t launch_swap_w8a8(const SwapPlan& plan, const UmmaArgs& a, const void* x, int64_t ldx,
+                             cudaStream_t stream, const char** why);
+
 }  // namespace fp8lin

@@ -1,144 +1,65 @@
-// Large-M W8A8 linear on the 5th-generation tensor cores (sm_100a).
+// Large- and mid-M W8A8 linear on the 5th-generation tensor cores (sm_100a).
 //
 //   y[M,N] = bf16( (xq[M,K] . W[N,K]^T) * in_scale * w_scale[n] + bias[n] )
 //
-// Persistent, warp-specialised kernel, one CTA per SM:
+// Warp-specialised kernel, one CTA per SM, 10 warps:
 //   warp 0      TMA producer: cp.async.bulk.tensor.2d loads of a 128 x 128-byte
 //               xq tile and a BN x 128-byte weight tile per K block into a
 //               multi-stage shared-memory ring (128-byte swizzle), signalled by
 //               mbarrier complete_tx.  No cluster multicast anywhere.
-//   warp 1      MMA issuer: one elected lane issues tcgen05.mma
-//               .cta_group::1.kind::f8f6f4 (M=128, N=BN, K=32) four times per K
-//               block, accumulating in TMEM; tcgen05.commit releases the ring
-//               slot and, after the last K block, publishes the accumulator.
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns one
-//               32-lane quarter of TMEM), apply in_scale * w_scale[n] + bias[n]
-//               in fp32, round once to bf16 and store.  Two accumulator stages
-//               in TMEM let the epilogue of tile i overlap the main loop of
-//               tile i+1.
-// Split-K (few output tiles, long K): every split writes its fp32 tile to
-// scratch and the last CTA to arrive at the tile's counter sums the splits in
-// order and runs the epilogue.
+//   warp 1      MMA issuer: one lane issues tcgen05.mma.cta_group::1
+//               .kind::f8f6f4 (M=128, N=BN, K=32) four times per K block,
+//               accumulating in TMEM; tcgen05.commit releases the ring slot
+//               and, after the last K block, publishes the accumulator.
+//   warps 2..9  epilogue: two warps per 32-lane quarter of TMEM, each taking
+//               half of the tile's columns: tcgen05.ld 64 columns, one FMA per
+//               element with in_scale*w_scale[n] and bias[n] staged in shared
+//               memory, one rounding to bf16, swizzled staging box, TMA store
+//               (which clips the M and N tails).
 //
-// Tensor-bound for M >= ~1024: 2*M*K*N flops per call; HBM-bound below that.
-// Every wait is bounded: a barrier that does not flip within about a second
-// records a status code in the caller's scratch header and the CTA unwinds
-// (drains its ring, frees TMEM) instead of hanging the GPU.
-#include "common.cuh"
-#include "kernels.h"
+// Two launch shapes:
+//  * persistent (kSplit = false): grid = min(tiles, SMs); two accumulator
+//    stages in TMEM let the epilogue of tile i overlap the main loop of tile
+//    i+1.  Tensor-bound: 2*M*K*N flops per call.
+//  * cluster split-K (kSplit = true): for shapes with few output tiles and a
+//    long K, the CTAs of a thread-block cluster (2..8) each run one K slice of
+//    the same tile, park their fp32 accumulators in their own shared memory and,
+//    after a cluster barrier, every CTA sums one band of rows across the
+//    cluster's shared memories (ld.shared::cluster, fixed order, deterministic),
+//    applies the epilogue and stores.  No global scratch, no counters.
+//    HBM/L2-bound: K*N + M*K + 2*M*N bytes per call.
+//
+// Every mbarrier wait is bounded: a barrier that does not flip within about a
+// second records a status code in the caller's scratch header and the CTA
+// unwinds (drains its ring, frees TMEM) instead of hanging the GPU.
+#include "umma_common.cuh"
 
 namespace fp8lin {
 
 constexpr int kBM = 128;
 constexpr int kBK = 128;  // bytes == e4m3 elements per K block
-constexpr long long kWaitCycles = 2000000000LL;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = (2 + kEpiWarps) * 32;
 
 template <int BN>
 struct UmmaCfg {
     static constexpr int kABytes = kBM * kBK;
     static constexpr int kBBytes = BN * kBK;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 5 : 8);   // ring + staging + statics <= 227 KB
     static constexpr int kTmemCols = 2 * BN;
-    // epilogue staging: per epilogue warp two 32-row x 128-byte boxes (4 KiB each)
-    static constexpr int kStagingBytes = 4 * 2 * 4096;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
+    static constexpr int kRingBytes = kStages * kStageBytes;
+    // columns per TMEM read / staging box of an epilogue warp (the 256-wide tile leaves
+    // shared memory for 32-column boxes only)
+    static constexpr int kPiece = BN == 256 ? 32 : (BN / 2 < 64 ? BN / 2 : 64);
+    static constexpr int kBoxBytes = 32 * kPiece * 2;
+    static constexpr int kStagingBytes = kEpiWarps * kBoxBytes; // one 32-row box per epilogue warp
+    static constexpr int kSmemBytes = kRingBytes + kStagingBytes + 1024;
+    // split-K: fp32 tile parked over the (then idle) ring; 16 bytes of padding per row
+    // spread consecutive rows over the banks
+    static constexpr int kPartPitch = BN * 4 + 16;
+    static_assert(kBM * kPartPitch <= kRingBytes, "parked tile must fit in the ring");
 };
-
-// ---- PTX wrappers --------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-// Bounded wait; false = gave up (status word written).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    long long start = -1;
-    for (uint32_t it = 0;; ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-        if ((it & 0x3ff) == 0x3ff) {
-            const long long now = clock64();
-            if (start < 0) start = now;
-            else if (now - start > kWaitCycles) { atomicExch(status, code); return false; }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-
-// TMA store of one shared-memory box; elements outside the tensor are not written,
-// which is what clips the M and N tails.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
-}
-
-// 32 lanes x 32 columns of fp32 from TMEM (lane i of the warp reads TMEM lane base+i).
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3ffff) >> 4);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                    // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-    return d;
-}
 
 template <int BN>
 __host__ __device__ constexpr uint32_t make_idesc() {
@@ -153,11 +74,9 @@ struct UmmaSched {
     int m_tiles, n_tiles, splits, kblocks_total, kblocks_per_split, total_work;
 };
 
-// work item -> (tile_m, tile_n, split); 8 M-tiles share a weight column block
-// before the next column block starts, so concurrently running CTAs reuse L2 lines.
-__device__ __forceinline__ void decode_work(const UmmaSched& s, int w, int& tm, int& tn, int& split) {
-    split = w % s.splits;
-    const int tile = w / s.splits;
+// tile index -> (tile_m, tile_n); 8 M-tiles share a weight column block before the next
+// column block starts, so concurrently running CTAs reuse L2 lines.
+__device__ __forceinline__ void decode_tile(const UmmaSched& s, int tile, int& tm, int& tn) {
     constexpr int kGroupM = 8;
     const int per_group = kGroupM * s.n_tiles;
     const int group = tile / per_group;
@@ -168,11 +87,10 @@ __device__ __forceinline__ void decode_work(const UmmaSched& s, int w, int& tm, 
     tn = r / gsize;
 }
 
-template <int BN>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, bool kSplit>
+__global__ void __launch_bounds__(kThreads, 1)
 umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_part,
-                 UmmaArgs p, UmmaSched sched) {
+                 const __grid_constant__ CUtensorMap tmap_y, UmmaArgs p, UmmaSched sched) {
     using Cfg = UmmaCfg<BN>;
     constexpr int S = Cfg::kStages;
     extern __shared__ unsigned char smem_raw[];
@@ -182,15 +100,21 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __shared__ __align__(8) uint64_t bar_tempty[2];
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile int s_abort;
-    __shared__ int s_last;
+    __shared__ __align__(16) float s_scale[2][BN];   // in_scale * w_scale[n] for the tile in flight
+    __shared__ __align__(16) float s_bias[2][BN];
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    // In split mode a cluster shares one tile: tile = cluster id, K slice = rank in the cluster.
+    const int split_rank = kSplit ? (int)cluster_ctarank() : 0;
+    const int first_work = kSplit ? (int)(blockIdx.x / sched.splits) : (int)blockIdx.x;
+    const int work_step = kSplit ? sched.total_work : (int)gridDim.x;      // split mode: exactly one tile
+
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&bar_full[i]), 1); mbar_init(smem_u32(&bar_empty[i]), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bar_tfull[i]), 1); mbar_init(smem_u32(&bar_tempty[i]), 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bar_tfull[i]), 1); mbar_init(smem_u32(&bar_tempty[i]), kEpiWarps); }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -208,11 +132,11 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
             uint32_t it = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < sched.total_work && ok; w += gridDim.x) {
-                int tm, tn, split;
-                decode_work(sched, w, tm, tn, split);
-                const int kb0 = split * sched.kblocks_per_split;
-                const int kb1 = min(sched.kblocks_total, kb0 + sched.kblocks_per_split);
+            for (int w = first_work; w < sched.total_work && ok; w += work_step) {
+                int tm, tn;
+                decode_tile(sched, w, tm, tn);
+                const int kb0 = split_rank * sched.kblocks_per_split;
+                const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int st = it % S;
                     const uint32_t ph = (it / S) & 1;
@@ -239,11 +163,9 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t it = 0;
             int tl = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < sched.total_work && ok; w += gridDim.x, ++tl) {
-                int tm, tn, split;
-                decode_work(sched, w, tm, tn, split);
-                const int kb0 = split * sched.kblocks_per_split;
-                const int kb1 = min(sched.kblocks_total, kb0 + sched.kblocks_per_split);
+            for (int w = first_work; w < sched.total_work && ok; w += work_step, ++tl) {
+                const int kb0 = split_rank * sched.kblocks_per_split;
+                const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
                 const int as = tl & 1;
                 const uint32_t aph = (tl >> 1) & 1;
                 if (s_abort || !mbar_wait(smem_u32(&bar_tempty[as]), aph ^ 1, p.status, kDevTimeoutTmemEmpty)) {
@@ -272,153 +194,122 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
         }
     } else {
-        // ================= epilogue (warps 2..5) =================
-        // Each warp owns TMEM lanes [32q, 32q+32) = 32 rows of the tile.  A lane holds one
-        // row; 32 columns at a time come out of TMEM, are scaled/biased/rounded and written
-        // to a 32-row x 128-byte staging box in shared memory in the 128-byte-swizzle
-        // pattern (16-byte chunk index XOR row&7, bank-conflict free), and lane 0 hands
-        // the box to a TMA store.  Two boxes per warp alternate so the next 64 columns
-        // are converted while the previous store drains.
+        // ================= epilogue (warps 2..9) =================
+        // Warp (q, h): TMEM lanes [32q, 32q+32) = 32 rows of the tile, column half h.
+        const int ew = warp - 2;
         const int q = warp & 3;
-        const int ew = warp - 2;                                   // 0..3: staging slot
+        const int h = ew >> 2;
+        const int et = threadIdx.x - 64;                            // 0..255 among the epilogue threads
+        constexpr int kHalf = BN / 2;
+        constexpr int kPiece = Cfg::kPiece;
         const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
-        const uint32_t stage0 = smem_base + S * Cfg::kStageBytes + ew * 8192;
-        const uint32_t row_off = lane * 128;
-        const uint32_t sw = lane & 7;
+        const uint32_t box = smem_base + Cfg::kRingBytes + ew * Cfg::kBoxBytes;
+        const uint32_t row_off = lane * (kPiece * 2);
+        const uint32_t sw = kPiece == 64 ? (lane & 7) : ((lane >> 1) & 3);   // 128-byte / 64-byte swizzle
         int tl = 0;
-        uint32_t nstore = 0;
         bool ok = true;
-        for (int w = blockIdx.x; w < sched.total_work && ok; w += gridDim.x, ++tl) {
-            int tm, tn, split;
-            decode_work(sched, w, tm, tn, split);
+        for (int w = first_work; w < sched.total_work && ok; w += work_step, ++tl) {
+            int tm, tn;
+            decode_tile(sched, w, tm, tn);
             const int as = tl & 1;
             const uint32_t aph = (tl >> 1) & 1;
-            // (no s_abort shortcut here: the four epilogue warps must take the same
-            //  branch because they meet at a named barrier below)
+            const int n0 = tn * BN;
+            // stage this tile's per-column multiplier and bias while the main loop runs
+            for (int i = et; i < BN; i += kEpiWarps * 32) {
+                const int n = n0 + i;
+                s_scale[as][i] = n < p.N ? in_scale * __ldg(p.w_scale + n) : 0.f;
+                s_bias[as][i] = (n < p.N && p.bias) ? __bfloat162float(p.bias[n]) : 0.f;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            // (no s_abort shortcut here: the epilogue warps must take the same branch
+            //  because they meet at the named barrier above on the next tile)
             if (!mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull)) {
                 s_abort = 1; ok = false; break;
             }
             tc_fence_after();
-            const int row0 = tm * kBM + q * 32;                    // first row of this warp's box
-            const int n0 = tn * BN;
-            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
+            const int row0 = tm * kBM + q * 32;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + h * kHalf;
 
-            if (sched.splits == 1) {
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    const int nc = n0 + c * 32;
-                    if (nc >= p.N) break;                          // uniform: whole chunk is past N
-                    const uint32_t box = stage0 + ((nstore & 1) * 4096);
-                    if ((c & 1) == 0) {
-                        // the store issued two boxes ago read this buffer: wait until it is done with it
-                        if (lane == 0) tma_store_wait_read<1>();
-                        __syncwarp();
-                    }
-                    uint32_t v[32];
-                    tmem_ld32(t_addr + c * 32, v);
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        const int n = min(nc + j, p.N - 8);        // clamp keeps the loads in bounds; TMA clips the store
-                        const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.w_scale + n));
-                        const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.w_scale + n + 4));
-                        float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (p.bias) {
-                            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
-                            b[0] = bf16_lo(bv.x); b[1] = bf16_hi(bv.x); b[2] = bf16_lo(bv.y); b[3] = bf16_hi(bv.y);
-                            b[4] = bf16_lo(bv.z); b[5] = bf16_hi(bv.z); b[6] = bf16_lo(bv.w); b[7] = bf16_hi(bv.w);
-                        }
-                        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                        float o[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) o[e] = fmaf(__uint_as_float(v[j + e]) * in_scale, sc[e], b[e]);
-                        const uint32_t chunk = (uint32_t)((c & 1) * 4 + (j >> 3));
-                        const uint32_t dst = box + row_off + ((chunk ^ sw) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
-                                     "r"(pack_bf16x2(o[0], o[1])), "r"(pack_bf16x2(o[2], o[3])),
-                                     "r"(pack_bf16x2(o[4], o[5])), "r"(pack_bf16x2(o[6], o[7])) : "memory");
-                    }
-                    if ((c & 1) == 1 || nc + 32 >= p.N) {
-                        fence_async_smem();
-                        __syncwarp();
-                        if (lane == 0) tma_store_2d(&tmap_y, box, n0 + (c & ~1) * 32, row0);
-                        ++nstore;
-                    }
-                }
-                tc_fence_before();
+            for (int c0 = 0; c0 < kHalf; c0 += kPiece) {
+                const int col = h * kHalf + c0;                      // first column of this piece inside the tile
+                if (n0 + col >= p.N) break;                          // uniform: the rest is past N
+                uint32_t v[kPiece];
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
-            } else {
-                // split-K: park the fp32 tile in scratch ([split][m_tiles*128][N]); a box is 32 rows x 32 floats
-                const int prow0 = (split * sched.m_tiles + tm) * kBM + q * 32;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    const int nc = n0 + c * 32;
-                    if (nc >= p.N) break;
-                    const uint32_t box = stage0 + ((nstore & 1) * 4096);
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
-                    uint32_t v[32];
-                    tmem_ld32(t_addr + c * 32, v);
+                tmem_ld32_nowait(t_addr + c0, v);
+                if (kPiece == 64) tmem_ld32_nowait(t_addr + c0 + 32, v + 32);
+                tmem_ld_wait();
+                if (!kSplit) {
+                    uint32_t o[kPiece / 2];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const uint32_t dst = box + row_off + ((((uint32_t)j >> 2) ^ sw) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[j]), "r"(v[j + 1]),
-                                     "r"(v[j + 2]), "r"(v[j + 3]) : "memory");
+                    for (int j = 0; j < kPiece; j += 4) {
+                        const float4 sc = *reinterpret_cast<const float4*>(&s_scale[as][col + j]);
+                        const float4 bi = *reinterpret_cast<const float4*>(&s_bias[as][col + j]);
+                        o[j / 2] = pack_bf16x2(fmaf(__uint_as_float(v[j]), sc.x, bi.x), fmaf(__uint_as_float(v[j + 1]), sc.y, bi.y));
+                        o[j / 2 + 1] = pack_bf16x2(fmaf(__uint_as_float(v[j + 2]), sc.z, bi.z), fmaf(__uint_as_float(v[j + 3]), sc.w, bi.w));
+                    }
+                    // the previous store out of this box must have finished reading it
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < kPiece / 8; ++j) {
+                        const uint32_t dst = box + row_off + (((uint32_t)j ^ sw) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[4 * j]), "r"(o[4 * j + 1]),
+                                     "r"(o[4 * j + 2]), "r"(o[4 * j + 3]) : "memory");
                     }
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0) tma_store_2d(&tmap_part, box, nc, prow0);
-                    ++nstore;
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(smem_u32(&bar_tempty[as]));
-                    tma_store_wait_all();          // this warp's partial rows are in global memory
-                }
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64) {
-                    int* counter = p.counters + (tm * sched.n_tiles + tn);
-                    const int prev = atomicAdd(counter, 1);
-                    s_last = (prev == sched.splits - 1);
-                    if (s_last) *counter = 0;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const bool last = s_last != 0;
-                asm volatile("bar.sync 1, 128;" ::: "memory");  // s_last may be rewritten next tile
-                if (last) {
-                    __threadfence();
-                    // coalesced reduction: the warp walks its 32 rows, lanes span the columns
-                    const int ncols = min(BN, p.N - n0);
-                    const size_t split_stride = (size_t)sched.m_tiles * kBM * p.N;
-                    for (int r = 0; r < 32; ++r) {
-                        const int row = tm * kBM + q * 32 + r;
-                        if (row >= p.M) break;
-                        const float* prow = p.partial + (size_t)row * p.N + n0;
-                        __nv_bfloat16* yrow = p.y + (size_t)row * p.ldy + n0;
-                        for (int cc = lane * 4; cc < ncols; cc += 128) {
-                            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-                            for (int sp = 0; sp < sched.splits; ++sp) {
-                                const float4 u = __ldcg(reinterpret_cast<const float4*>(prow + sp * split_stride + cc));
-                                a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
-                            }
-                            const float4 sc = __ldg(reinterpret_cast<const float4*>(p.w_scale + n0 + cc));
-                            float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
-                            if (p.bias) {
-                                const uint2 bv = __ldg(reinterpret_cast<const uint2*>(p.bias + n0 + cc));
-                                b0 = bf16_lo(bv.x); b1 = bf16_hi(bv.x); b2 = bf16_lo(bv.y); b3 = bf16_hi(bv.y);
-                            }
-                            uint2 out;
-                            out.x = pack_bf16x2(fmaf(a.x * in_scale, sc.x, b0), fmaf(a.y * in_scale, sc.y, b1));
-                            out.y = pack_bf16x2(fmaf(a.z * in_scale, sc.z, b2), fmaf(a.w * in_scale, sc.w, b3));
-                            *reinterpret_cast<uint2*>(yrow + cc) = out;
-                        }
+                    if (lane == 0) tma_store_2d(&tmap_y, box, n0 + col, row0);
+                } else {
+                    // park the raw fp32 accumulators in this CTA's shared memory (over the idle ring)
+                    const uint32_t dst0 = smem_base + (uint32_t)(q * 32 + lane) * Cfg::kPartPitch + (uint32_t)col * 4;
+#pragma unroll
+                    for (int j = 0; j < kPiece; j += 4) {
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 4), "r"(v[j]), "r"(v[j + 1]),
+                                     "r"(v[j + 2]), "r"(v[j + 3]) : "memory");
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
         }
-        if (lane == 0) tma_store_wait_all();
+        if (!kSplit && lane == 0) tma_store_wait_all();
+    }
+
+    if (kSplit) {
+        // ---- cluster reduction: CTA r sums rows [r*band, (r+1)*band) of the tile over all K slices ----
+        __syncwarp();
+        cluster_sync_all();                                   // every CTA's parked tile is visible
+        int tm, tn;
+        decode_tile(sched, first_work, tm, tn);
+        const int n0 = tn * BN;
+        const int band = (kBM + sched.splits - 1) / sched.splits;
+        const int r_beg = split_rank * band;
+        const int r_end = min(kBM, r_beg + band);
+        constexpr int kVecPerRow = BN / 4;
+        const int total = (r_end - r_beg) * kVecPerRow;
+        const bool healthy = (s_abort == 0);
+        for (int i = threadIdx.x; i < total && healthy; i += kThreads) {
+            const int r = r_beg + i / kVecPerRow;
+            const int c = (i % kVecPerRow) * 4;
+            const int row = tm * kBM + r;
+            const int n = n0 + c;
+            if (row >= p.M || n >= p.N) continue;
+            const uint32_t local = smem_base + (uint32_t)r * Cfg::kPartPitch + (uint32_t)c * 4;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < sched.splits; ++s) {
+                const float4 u = ld_cluster_f4(map_to_cta(local, (uint32_t)s));
+                a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+            }
+            const float4 sc = *reinterpret_cast<const float4*>(&s_scale[0][c]);
+            const float4 bi = *reinterpret_cast<const float4*>(&s_bias[0][c]);
+            uint2 out;
+            out.x = pack_bf16x2(fmaf(a.x, sc.x, bi.x), fmaf(a.y, sc.y, bi.y));
+            out.y = pack_bf16x2(fmaf(a.z, sc.z, bi.z), fmaf(a.w, sc.w, bi.w));
+            *reinterpret_cast<uint2*>(p.y + (size_t)row * p.ldy + n) = out;
+        }
+        cluster_sync_all();                                   // nobody exits while a peer still reads its tile
     }
 
     tc_fence_before();
@@ -431,11 +322,41 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 // ---- host side -------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int max_active_clusters(const void* kernel, int threads, size_t smem_bytes, int cluster) {
+    static const int fallback[9] = {148, 148, 74, 48, 32, 24, 24, 16, 16};
+    if (cluster < 1 || cluster > 8) return 0;
+    struct Entry { const void* k; int c; int n; };
+    static Entry cache[64];
+    static int used = 0;
+    for (int i = 0; i < used; ++i)
+        if (cache[i].k == kernel && cache[i].c == cluster) return cache[i].n;
+    int n = fallback[cluster];
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(cluster * 64));
+        cfg.blockDim = dim3((unsigned)threads);
+        cfg.dynamicSmemBytes = smem_bytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int q = 0;
+        if (cudaOccupancyMaxActiveClusters(&q, kernel, &cfg) == cudaSuccess && q > 0) n = q;
+        else cudaGetLastError();
+    } else {
+        cudaGetLastError();
+        return n;            // no device: do not cache, a later call may have one
+    }
+    if (used < 64) cache[used++] = Entry{kernel, cluster, n};
+    return n;
+}
 
-static EncodeTiledFn get_encode_fn() {
+EncodeTiledFn get_encode_fn() {
     static EncodeTiledFn fn = nullptr;
     if (fn) return fn;
     void* sym = nullptr;
@@ -448,7 +369,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D byte tensor [rows][cols] (cols contiguous), box = 128 bytes x box_rows, 128-byte swizzle.
-static bool encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+bool encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {cols, rows};
@@ -461,17 +382,20 @@ static bool encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint
     return r == CUDA_SUCCESS;
 }
 
-// Output-side maps: 2-D tensor [rows][cols] with a row pitch in bytes, box = 128 bytes x 32 rows.
-static bool encode_out_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, uint32_t elem_bytes,
-                          uint64_t rows, uint64_t cols, uint64_t pitch_bytes) {
+// Output map: bf16 [rows][cols] with a row pitch in bytes, box = box_cols x 32 rows,
+// swizzle span = the box's row length (128 or 64 bytes).
+static bool encode_out_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                          uint32_t box_cols) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {pitch_bytes};
-    cuuint32_t box[2] = {128u / elem_bytes, 32u};
+    cuuint32_t box[2] = {box_cols, 32u};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    box_cols * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
@@ -481,7 +405,7 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
     const int m_tiles = (int)((M + kBM - 1) / kBM);
     double best_cost = 1e30;
     const int bns[3] = {256, 128, 64};
-    const double unit[3] = {1.0, 0.85, 0.6};  // relative time of one K block of a tile (smaller tiles use shared memory less well)
+    const double unit[3] = {1.0, 0.8, 0.6};  // relative time of one K block of a tile (smaller tiles use shared memory less well)
     for (int i = 0; i < 3; ++i) {
         const int bn = bns[i];
         if (force_bn > 0 && bn != force_bn) continue;
@@ -489,36 +413,44 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
         const long tiles = (long)m_tiles * n_tiles;
         int splits = 1;
         if (force_splits > 0) splits = force_splits;
-        else if (tiles < 148) {
+        else if (tiles <= 74) {
             splits = (int)(148 / tiles);
-            const int max_by_k = kblocks / 4 > 0 ? kblocks / 4 : 1;  // at least four K blocks per split
+            const int max_by_k = kblocks / 4 > 0 ? kblocks / 4 : 1;  // at least four K blocks per slice
             if (splits > max_by_k) splits = max_by_k;
-            if (splits > 16) splits = 16;
         }
+        if (splits > 8) splits = 8;                                   // portable cluster size
         if (splits > kblocks) splits = kblocks;
-        if (tiles > kWsMaxCounters) splits = 1;
-        const int kps = (kblocks + splits - 1) / splits;
-        splits = (kblocks + kps - 1) / kps;
+        if (splits < 1) splits = 1;
+        int kps = (kblocks + splits - 1) / splits;
+        splits = (kblocks + kps - 1) / kps;                           // no empty K slice
         const long work = tiles * splits;
-        const long waves = (work + 147) / 148;
-        // main-loop time + fixed per-tile epilogue/prologue + split-K reduction traffic
-        const double cost = waves * (kps * unit[i] + 3.0 * unit[i]) + (splits > 1 ? 0.5 * splits : 0.0);
+        long waves = (work + 147) / 148;
+        if (splits > 1) {
+            const void* kern = bn == 256 ? (const void*)umma_w8a8_kernel<256, true>
+                             : bn == 128 ? (const void*)umma_w8a8_kernel<128, true> : (const void*)umma_w8a8_kernel<64, true>;
+            const size_t smem = bn == 256 ? UmmaCfg<256>::kSmemBytes : bn == 128 ? UmmaCfg<128>::kSmemBytes : UmmaCfg<64>::kSmemBytes;
+            int slots = max_active_clusters(kern, kThreads, smem, splits);
+            if (slots < 1) slots = 1;
+            waves = (tiles + slots - 1) / slots;
+        }
+        // main loop + fixed per-tile prologue/epilogue; split-K pays one cluster reduction
+        const double cost = waves * (kps * unit[i] + 3.0 * unit[i]) + (splits > 1 ? 2.0 : 0.0);
         if (cost < best_cost) {
             best_cost = cost;
             best.bn = bn; best.splits = splits; best.kblocks_per_split = kps;
             best.m_tiles = m_tiles; best.n_tiles = n_tiles;
-            best.grid = (int)(work < 148 ? work : 148);
-            best.partial_bytes = splits > 1 ? (size_t)splits * m_tiles * kBM * N * sizeof(float) : 0;
+            best.grid = splits > 1 ? (int)work : (int)(work < 148 ? work : 148);
+            best.partial_bytes = 0;
         }
     }
     return best;
 }
 
-template <int BN>
+template <int BN, bool kSplit>
 static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb,
-                             const CUtensorMap& ty, const CUtensorMap& tp, cudaStream_t stream) {
+                             const CUtensorMap& ty, cudaStream_t stream) {
     using Cfg = UmmaCfg<BN>;
-    auto kern = umma_w8a8_kernel<BN>;
+    auto kern = umma_w8a8_kernel<BN, kSplit>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -528,35 +460,38 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     UmmaSched s;
     s.m_tiles = pl.m_tiles; s.n_tiles = pl.n_tiles; s.splits = pl.splits;
     s.kblocks_total = (a.K + kBK - 1) / kBK; s.kblocks_per_split = pl.kblocks_per_split;
-    s.total_work = pl.m_tiles * pl.n_tiles * pl.splits;
-    kern<<<pl.grid, 192, Cfg::kSmemBytes, stream>>>(ta, tb, ty, tp, a, s);
-    return cudaGetLastError();
+    s.total_work = pl.m_tiles * pl.n_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (kSplit) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)pl.splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s);
 }
 
 cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why) {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, ty;
+    const uint32_t piece = pl.bn == 256 ? 32 : (pl.bn / 2 < 64 ? pl.bn / 2 : 64);
     if (!encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K, kBM) ||
-        !encode_u8_2d(&tb, a.w, (uint64_t)a.N, (uint64_t)a.K, (uint32_t)pl.bn)) {
+        !encode_u8_2d(&tb, a.w, (uint64_t)a.N, (uint64_t)a.K, (uint32_t)pl.bn) ||
+        !encode_out_2d(&ty, a.y, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldy * 2, piece)) {
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }
-    CUtensorMap ty, tp;
-    if (!encode_out_2d(&ty, a.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)a.M, (uint64_t)a.N,
-                       (uint64_t)a.ldy * 2)) {
-        if (why) *why = "cuTensorMapEncodeTiled failed for y";
-        return cudaErrorInvalidValue;
-    }
-    tp = ty;
-    if (pl.splits > 1 &&
-        !encode_out_2d(&tp, a.partial, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
-                       (uint64_t)pl.splits * pl.m_tiles * kBM, (uint64_t)a.N, (uint64_t)a.N * 4)) {
-        if (why) *why = "cuTensorMapEncodeTiled failed for the split-K scratch";
-        return cudaErrorInvalidValue;
-    }
+    const bool split = pl.splits > 1;
     switch (pl.bn) {
-        case 256: return launch_bn<256>(pl, a, ta, tb, ty, tp, stream);
-        case 128: return launch_bn<128>(pl, a, ta, tb, ty, tp, stream);
-        case 64: return launch_bn<64>(pl, a, ta, tb, ty, tp, stream);
+        case 256: return split ? launch_bn<256, true>(pl, a, ta, tb, ty, stream) : launch_bn<256, false>(pl, a, ta, tb, ty, stream);
+        case 128: return split ? launch_bn<128, true>(pl, a, ta, tb, ty, stream) : launch_bn<128, false>(pl, a, ta, tb, ty, stream);
+        case 64: return split ? launch_bn<64, true>(pl, a, ta, tb, ty, stream) : launch_bn<64, false>(pl, a, ta, tb, ty, stream);
     }
     if (why) *why = "unsupported tile width";
     return cudaErrorInvalidValue;

@@ -1,0 +1,399 @@
+// Decode-sized W8A8 linear (M <= 64) on tcgen05 with the operands swapped:
+//
+//   y^T[N, M] = W[N, K] . xq[M, K]^T        (weights are the 128-row MMA "A" operand,
+//                                            the few tokens are the MMA "N" dimension)
+//
+// HBM-bound: the kernel exists to keep as many weight bytes in flight per SM as
+// shared memory allows.  Algorithmic bytes per call: K*N + 2*M*K + 2*M*N + 6*N.
+//
+//   warp 0       TMA producer.  Per 128-byte K block: one 128 x 128-byte weight
+//                tile (128-byte swizzle) and the raw bf16 activation block
+//                [MP x 128] into a ring of 5..9 stages (144..80 KB of weights in
+//                flight per SM).
+//   warps 2..9   activation converters, one ring slot per warp (up to eight K
+//                blocks are converted concurrently): quantise the M real rows of
+//                the raw block to e4m3 with the static scale (exact division)
+//                and write them into the K-major, 128-byte-swizzled MMA "B"
+//                tile (rows M..MP-1 stay zero); fence.proxy.async; arrive.
+//   warp 1       MMA issuer: tcgen05.mma.cta_group::1.kind::f8f6f4, M=128, N=MP,
+//                K=32, four per K block, fp32 accumulators in TMEM (2 stages).
+//   warps 10..13 epilogue: tcgen05.ld one output channel per lane, MP tokens per
+//                lane; y[m][n] = bf16(acc*in_scale*w_scale[n] + bias[n]); the 32
+//                lanes of a warp write 32 consecutive channels of one token.
+//
+// Launch shapes: persistent over the N/128 channel tiles, or, when there are too
+// few tiles to occupy 148 SMs, cluster split-K: the CTAs of a cluster (2..8)
+// take K slices of one tile, park fp32 partials in their own shared memory and
+// each reduces a band of channels over the cluster with ld.shared::cluster
+// (fixed order, deterministic).  All mbarrier waits are bounded.
+#include "umma_common.cuh"
+
+namespace fp8lin {
+
+constexpr int kConvWarps = 8;
+constexpr int kSwapThreads = (2 + kConvWarps + 4) * 32;
+constexpr int kTileN = 128;   // output channels per tile = MMA M
+constexpr int kKB = 128;      // K elements per block
+
+template <int MP>
+struct SwapCfg {
+    static constexpr int kWBytes = kTileN * kKB;                 // 16 KB e4m3 weight tile
+    static constexpr int kXqBytes = MP * kKB;                    // quantised activation tile (MMA B)
+    static constexpr int kXrawBytes = MP * kKB * 2;              // raw bf16 activation block
+    static constexpr int kStageBytes = kWBytes + kXqBytes + kXrawBytes;
+    static constexpr int kStages = MP <= 16 ? 9 : (MP <= 32 ? 7 : 5);
+    static constexpr int kRingBytes = kStages * kStageBytes;
+    static constexpr int kSmemBytes = kRingBytes + 1024;
+    static constexpr int kTmemCols = 2 * MP < 32 ? 32 : 2 * MP;
+    static constexpr int kPartPitch = MP * 4 + 16;               // parked fp32 tile row pitch (split-K)
+    static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment for the swizzle");
+    static_assert(kTileN * kPartPitch <= kRingBytes, "parked tile must fit in the ring");
+};
+
+struct SwapSched {
+    int n_tiles, splits, kblocks_total, kblocks_per_split;
+};
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* v);
+template <>
+__device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld_cols<32>(uint32_t taddr, uint32_t* v) { tmem_ld32_nowait(taddr, v); }
+template <>
+__device__ __forceinline__ void tmem_ld_cols<64>(uint32_t taddr, uint32_t* v) {
+    tmem_ld32_nowait(taddr, v);
+    tmem_ld32_nowait(taddr + 32, v + 32);
+}
+
+template <int MP, bool kSplit>
+__global__ void __launch_bounds__(kSwapThreads, 1)
+swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                 UmmaArgs p, SwapSched sched) {
+    using Cfg = SwapCfg<MP>;
+    constexpr int S = Cfg::kStages;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[S];     // TMA bytes landed (weights + raw x)
+    __shared__ __align__(8) uint64_t bar_xq[S];       // quantised x tile written (one converter warp)
+    __shared__ __align__(8) uint64_t bar_empty[S];    // MMAs that read the stage are done
+    __shared__ __align__(8) uint64_t bar_tfull[2];
+    __shared__ __align__(8) uint64_t bar_tempty[2];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile int s_abort;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int split_rank = kSplit ? (int)cluster_ctarank() : 0;
+    const int first_tile = kSplit ? (int)(blockIdx.x / sched.splits) : (int)blockIdx.x;
+    const int tile_step = kSplit ? sched.n_tiles : (int)gridDim.x;
+    const int kb0 = split_rank * sched.kblocks_per_split;
+    const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S; ++i) {
+            mbar_init(smem_u32(&bar_full[i]), 1);
+            mbar_init(smem_u32(&bar_xq[i]), 1);
+            mbar_init(smem_u32(&bar_empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bar_tfull[i]), 1); mbar_init(smem_u32(&bar_tempty[i]), 4); }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), Cfg::kTmemCols);
+    // rows M..MP-1 of every quantised-activation tile are zero for the whole kernel
+    for (int i = threadIdx.x; i < S * MP * 8; i += kSwapThreads) {
+        const int st = i / (MP * 8), r = i % (MP * 8);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(smem_base + st * Cfg::kStageBytes + Cfg::kWBytes + r * 16), "r"(0u) : "memory");
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int st = it % S;
+                    const uint32_t ph = (it / S) & 1;
+                    if (s_abort || !mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1, p.status, kDevTimeoutEmpty)) {
+                        s_abort = 1; ok = false; break;
+                    }
+                    const uint32_t full = smem_u32(&bar_full[st]);
+                    mbar_expect_tx(full, Cfg::kWBytes + (uint32_t)p.M * 256u);   // the x box holds the M real rows only
+                    const uint32_t sa = smem_base + st * Cfg::kStageBytes;
+                    tma_load_2d(sa, &tmap_w, kb * kKB, t * kTileN, full);
+                    tma_load_2d(sa + Cfg::kWBytes + Cfg::kXqBytes, &tmap_x, kb * kKB, 0, full);
+                }
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_mn(kTileN, MP, 0, 0);
+            uint32_t it = 0;
+            int tl = 0;
+            bool ok = true;
+            for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step, ++tl) {
+                const int as = tl & 1;
+                const uint32_t aph = (tl >> 1) & 1;
+                if (s_abort || !mbar_wait(smem_u32(&bar_tempty[as]), aph ^ 1, p.status, kDevTimeoutTmemEmpty)) {
+                    s_abort = 1; ok = false; break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * MP;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int st = it % S;
+                    const uint32_t ph = (it / S) & 1;
+                    if (s_abort || !mbar_wait(smem_u32(&bar_full[st]), ph, p.status, kDevTimeoutFull) ||
+                        !mbar_wait(smem_u32(&bar_xq[st]), ph, p.status, kDevTimeoutFull)) {
+                        s_abort = 1; ok = false; break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + st * Cfg::kStageBytes;
+                    const uint64_t da = make_smem_desc(sa);
+                    const uint64_t db = make_smem_desc(sa + Cfg::kWBytes);
+#pragma unroll
+                    for (int k = 0; k < kKB / 32; ++k)
+                        umma_f8(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    umma_commit(smem_u32(&bar_empty[st]));
+                }
+                if (ok) umma_commit(smem_u32(&bar_tfull[as]));
+            }
+        }
+    } else if (warp < 2 + kConvWarps) {
+        // ================= activation converters (warps 2..9) =================
+        const int cw = warp - 2;
+        const ExactDiv div_scale(fmaxf(__ldg(p.input_scale), 1e-12f));
+        const int items = p.M * 8;                          // (row, 16-element chunk) pairs of the real rows
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step) {
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                // a ring slot always belongs to the same warp, so every warp sees the phases of
+                // the barriers it waits on in order (a parity wait may only look one phase ahead)
+                const int st = it % S;
+                if (st % kConvWarps != cw) continue;
+                const uint32_t ph = (it / S) & 1;
+                if (s_abort || !mbar_wait(smem_u32(&bar_full[st]), ph, p.status, kDevTimeoutFull)) { s_abort = 1; ok = false; break; }
+                const uint32_t sa = smem_base + st * Cfg::kStageBytes;
+                const uint32_t xq = sa + Cfg::kWBytes;
+                const uint32_t xr = xq + Cfg::kXqBytes;
+                for (int i = lane; i < items; i += 32) {
+                    const int m = i >> 3, c = i & 7;
+                    uint4 a, b;
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w)
+                                 : "r"(xr + m * 256 + c * 32));
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+                                 : "r"(xr + m * 256 + c * 32 + 16));
+                    const uint2 qa = quant8_e4m3(a, div_scale);
+                    const uint2 qb = quant8_e4m3(b, div_scale);
+                    const uint32_t dst = xq + m * 128 + (((uint32_t)c ^ (uint32_t)(m & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(qa.x), "r"(qa.y), "r"(qb.x), "r"(qb.y)
+                                 : "memory");
+                }
+                fence_async_smem();                          // generic-proxy writes -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_xq[st]));
+            }
+        }
+    } else {
+        // ================= epilogue (warps 10..13) =================
+        const int q = warp & 3;
+        const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
+        int tl = 0;
+        bool ok = true;
+        for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step, ++tl) {
+            const int as = tl & 1;
+            const uint32_t aph = (tl >> 1) & 1;
+            const int n = t * kTileN + q * 32 + lane;
+            float ws = 0.f, bs = 0.f;
+            if (!kSplit && n < p.N) {
+                ws = __ldg(p.w_scale + n);
+                if (p.bias) bs = __bfloat162float(p.bias[n]);
+            }
+            if (!mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
+            tc_fence_after();
+            uint32_t v[MP];
+            __syncwarp();
+            tmem_ld_cols<MP>(tmem_base + ((uint32_t)(q * 32) << 16) + as * MP, v);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
+            if (!kSplit) {
+                if (n < p.N) {
+#pragma unroll
+                    for (int m = 0; m < MP; ++m)
+                        if (m < p.M) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(fmaf(__uint_as_float(v[m]) * in_scale, ws, bs));
+                }
+            } else {
+                const uint32_t dst = smem_base + (uint32_t)(q * 32 + lane) * Cfg::kPartPitch;
+#pragma unroll
+                for (int m = 0; m < MP; m += 4)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + m * 4), "r"(v[m]), "r"(v[m + 1]),
+                                 "r"(v[m + 2]), "r"(v[m + 3]) : "memory");
+            }
+        }
+    }
+
+    if (kSplit) {
+        // ---- cluster reduction: CTA r finishes channels [r*band, (r+1)*band) of the tile ----
+        __syncwarp();
+        cluster_sync_all();
+        const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
+        const int band = (kTileN + sched.splits - 1) / sched.splits;
+        const int r_beg = split_rank * band;
+        const int rows = min(kTileN, r_beg + band) - r_beg;
+        const bool healthy = (s_abort == 0);
+        // consecutive threads take consecutive channels, so the stores of one token coalesce
+        for (int i = threadIdx.x; i < rows * (MP / 4) && healthy; i += kSwapThreads) {
+            const int rl = i % rows;
+            const int mg = (i / rows) * 4;
+            const int n = first_tile * kTileN + r_beg + rl;
+            if (n >= p.N || mg >= p.M) continue;
+            const uint32_t local = smem_base + (uint32_t)(r_beg + rl) * Cfg::kPartPitch + (uint32_t)mg * 4;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < sched.splits; ++s) {
+                const float4 u = ld_cluster_f4(map_to_cta(local, (uint32_t)s));
+                a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+            }
+            const float ws = __ldg(p.w_scale + n);
+            const float bs = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+            const float o[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (mg + j < p.M) p.y[(size_t)(mg + j) * p.ldy + n] = __float2bfloat16_rn(fmaf(o[j] * in_scale, ws, bs));
+        }
+        cluster_sync_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------
+
+// raw bf16 activations [M][ldx]: box = 128 elements x box_rows, no swizzle; rows past M read as zero
+static bool encode_x_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                          uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)kKB, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int MP>
+static int swap_max_clusters(int cluster) {
+    using Cfg = SwapCfg<MP>;
+    const void* kern = (const void*)swap_w8a8_kernel<MP, true>;
+    return max_active_clusters(kern, kSwapThreads, Cfg::kSmemBytes, cluster);
+}
+
+SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits) {
+    SwapPlan pl{};
+    pl.mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    pl.n_tiles = (int)((N + kTileN - 1) / kTileN);
+    const int kblocks = (int)((K + kKB - 1) / kKB);
+    int best_s = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= 8; ++s) {
+        if (force_splits > 0 && s != (force_splits > 8 ? 8 : force_splits)) continue;
+        if (s > kblocks) break;
+        if (force_splits <= 0 && s > 1 && kblocks / s < 4) break;          // at least four K blocks per slice
+        const int kps = (kblocks + s - 1) / s;
+        if ((kblocks + kps - 1) / kps != s) continue;                        // would leave an empty slice
+        int slots = 148;
+        if (s > 1) slots = pl.mp == 16 ? swap_max_clusters<16>(s) : (pl.mp == 32 ? swap_max_clusters<32>(s) : swap_max_clusters<64>(s));
+        if (slots < 1) slots = 1;
+        const int waves = (pl.n_tiles + slots - 1) / slots;
+        // K blocks per CTA plus a fixed cost (launch, first loads, epilogue; cluster reduction when split)
+        const double cost = waves * (kps + (s > 1 ? 8.0 : 6.0));
+        if (cost < best_cost) { best_cost = cost; best_s = s; }
+    }
+    pl.splits = best_s;
+    pl.kblocks_per_split = (kblocks + best_s - 1) / best_s;
+    pl.grid = pl.splits > 1 ? pl.n_tiles * pl.splits : (pl.n_tiles < 148 ? pl.n_tiles : 148);
+    return pl;
+}
+
+template <int MP, bool kSplit>
+static cudaError_t launch_swap(const SwapPlan& pl, const UmmaArgs& a, const CUtensorMap& tw, const CUtensorMap& tx,
+                               cudaStream_t stream) {
+    using Cfg = SwapCfg<MP>;
+    auto kern = swap_w8a8_kernel<MP, kSplit>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    SwapSched s;
+    s.n_tiles = pl.n_tiles; s.splits = pl.splits;
+    s.kblocks_total = (a.K + kKB - 1) / kKB; s.kblocks_per_split = pl.kblocks_per_split;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.grid);
+    cfg.blockDim = dim3(kSwapThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (kSplit) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)pl.splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s);
+}
+
+cudaError_t launch_swap_w8a8(const SwapPlan& pl, const UmmaArgs& a, const void* x, int64_t ldx, cudaStream_t stream,
+                             const char** why) {
+    CUtensorMap tw, tx;
+    if (!encode_u8_2d(&tw, a.w, (uint64_t)a.N, (uint64_t)a.K, kTileN) ||
+        !encode_x_bf16(&tx, x, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)ldx * 2, (uint32_t)a.M)) {
+        if (why) *why = "cuTensorMapEncodeTiled failed";
+        return cudaErrorInvalidValue;
+    }
+    const bool split = pl.splits > 1;
+    switch (pl.mp) {
+        case 16: return split ? launch_swap<16, true>(pl, a, tw, tx, stream) : launch_swap<16, false>(pl, a, tw, tx, stream);
+        case 32: return split ? launch_swap<32, true>(pl, a, tw, tx, stream) : launch_swap<32, false>(pl, a, tw, tx, stream);
+        case 64: return split ? launch_swap<64, true>(pl, a, tw, tx, stream) : launch_swap<64, false>(pl, a, tw, tx, stream);
+    }
+    if (why) *why = "unsupported token-tile width";
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace fp8lin

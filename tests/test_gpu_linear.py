@@ -22,7 +22,7 @@ SCHEMES = ["fp8_w8a16", "fp8_w8a8_static"]
 def _clean_tuning_and_status():
     Kn = kernels()
     yield
-    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits"):
+    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable"):
         Kn.set_tuning(knob, -1)
     torch.cuda.synchronize()
     assert Kn.read_status(torch.device("cuda", 0)) == 0
@@ -123,9 +123,18 @@ STREAM_SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("scheme", SCHEMES)
+@pytest.mark.parametrize("scheme", SCHEMES + ["fp8_w8a8_static/mma_sync"])
 @pytest.mark.parametrize("m,k,n", STREAM_SHAPES)
 def test_streaming_kernel_parity(scheme, m, k, n):
+    """Decode-sized shapes: W8A16 on the mma.sync streaming kernel, W8A8 on the swapped-operand
+    tcgen05 kernel, and W8A8 on the mma.sync streaming kernel (kept for shapes the tcgen05 path
+    does not take)."""
+    if scheme.endswith("/mma_sync"):
+        kernels().set_tuning("swap_enable", 0)
+        scheme = scheme.split("/")[0]
+        assert kernels().variant_name(1, m, k, n).startswith("stream_mma_w8a8")
+    elif scheme == "fp8_w8a8_static":
+        assert kernels().variant_name(1, m, k, n).startswith("umma_swap_w8a8")
     c = O.make_case(20260519 + m * 7 + k + n, m, k, n)
     d = upload_case(c)
     y = run_linear(scheme, d)
@@ -144,6 +153,7 @@ def test_streaming_split_k_is_deterministic_and_equal(scheme):
     d = upload_case(c)
     ref = oracle_linear(scheme, c)
     outs = []
+    Kn.set_tuning("swap_enable", 0)
     for splits in (1, 2, 7, 14):
         Kn.set_tuning("stream_splits", splits)
         y1 = run_linear(scheme, d)
@@ -206,12 +216,28 @@ def test_tcgen05_tile_and_split_variants(bn, splits):
     assert_parity(y, oracle_linear("fp8_w8a8_static", c), f"umma bn={bn} splits={splits}")
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("m", [1, 16, 17, 33, 64])
+def test_swapped_tcgen05_kernel_split_variants(m, splits):
+    Kn = kernels()
+    Kn.set_tuning("swap_splits", splits)
+    c = O.make_case(900 + m + splits, m, 2048, 640)
+    d = upload_case(c)
+    y1 = run_linear("fp8_w8a8_static", d)
+    y2 = run_linear("fp8_w8a8_static", d)
+    np.testing.assert_array_equal(y1, y2)
+    assert_parity(y1, oracle_linear("fp8_w8a8_static", c), f"swap m={m} splits={splits}")
+
+
 def test_tcgen05_matches_streaming_kernel():
     # the two W8A8 kernels quantise x identically, so they agree to accumulation order
     Kn = kernels()
     c = O.make_case(123, 64, 2048, 1024)
     d = upload_case(c)
+    y_swap = run_linear("fp8_w8a8_static", d)
+    Kn.set_tuning("swap_enable", 0)
     y_stream = run_linear("fp8_w8a8_static", d)
+    assert_parity(y_swap, y_stream, "swap vs stream", ulps=1.0)
     Kn.set_tuning("stream_max_m", 0)
     y_umma = run_linear("fp8_w8a8_static", d)
     assert_parity(y_umma, y_stream, "umma vs stream", ulps=1.0)

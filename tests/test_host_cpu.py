@@ -166,7 +166,7 @@ def test_workspace_and_variant_queries(pkg):
             assert need >= L.WS_HEADER_BYTES and need % 256 == 0
             assert need < (1 << 31)
     assert lib.fp8lin_variant_name(L.W8A8_STATIC, 1024, 2048, 11008).decode().startswith("umma_w8a8_128x")
-    assert lib.fp8lin_variant_name(L.W8A8_STATIC, 16, 2048, 11008).decode().startswith("stream_mma_w8a8_m16")
+    assert lib.fp8lin_variant_name(L.W8A8_STATIC, 16, 2048, 11008).decode().startswith("umma_swap_w8a8_m16")
     assert lib.fp8lin_variant_name(L.W8A16, 1, 2048, 2048).decode().startswith("stream_mma_w8a16_m8")
 
 
