@@ -16,11 +16,17 @@
  *   scales                         : float32
  *
  * Weight layouts
- *   "kn"  : [K][N], N contiguous — the layout of the reference's `qweight`
- *           buffer (fp8.py:80-83) after its loaders ran.
- *   "nk"  : [N][K], K contiguous — the layout every kernel here streams
- *           (it is also the checkpoint's own layout, quantize.py:56).
- *           Produce it once per layer with fp8lin_prepack_weight.
+ *   "kn"     : [K][N], N contiguous — the layout of the reference's `qweight`
+ *              buffer (fp8.py:80-83) after its loaders ran.
+ *   "nk"     : [N][K], K contiguous — the checkpoint's own layout (quantize.py:56).
+ *   "packed" : what every kernel here reads.  128-channel x 128-byte tiles, each
+ *              tile contiguous (16 KiB), the tiles of one channel block consecutive
+ *              along K; N and K zero-padded to multiples of 128:
+ *                byte(n,k) = ((n/128)*ceil(K/128) + k/128)*16384 + (n%128)*128 + k%128
+ *              A CTA streaming a channel block reads one sequential range of HBM and a
+ *              tile is exactly one TMA box.  Produce it once per layer with
+ *              fp8lin_prepack_weight (from "kn") or fp8lin_pack_weight_nk (from "nk").
+ *              In the prototypes below `w_nk` names this packed buffer.
  *
  * Return value: 0 on success, otherwise one of the FP8LIN_ERR_* codes;
  * fp8lin_last_error() returns a thread-local description of the last failure.
@@ -58,9 +64,11 @@ const char* fp8lin_last_error(void);
 /* ---- weight prepack -------------------------------------------------------
  * Replaces the derived copies the reference builds in
  * Fp8LinearMethod.process_weights_after_loading (fp8.py:106-111).
- * qweight_kn: u8 [K][N]  ->  w_nk: u8 [N][K].  K % 16 == 0. */
+ * qweight_kn: u8 [K][N] (or qweight_nk: u8 [N][K])  ->  packed tiles, fp8lin_packed_bytes(K,N)
+ * bytes, 16-byte aligned.  K % 16 == 0. */
 size_t fp8lin_packed_bytes(int64_t K, int64_t N);
-int fp8lin_prepack_weight(const void* qweight_kn, void* w_nk, int64_t K, int64_t N, void* stream);
+int fp8lin_prepack_weight(const void* qweight_kn, void* w_packed, int64_t K, int64_t N, void* stream);
+int fp8lin_pack_weight_nk(const void* qweight_nk, void* w_packed, int64_t K, int64_t N, void* stream);
 
 /* ---- scratch --------------------------------------------------------------
  * Bytes of caller-owned scratch a linear call of this shape needs (split-K

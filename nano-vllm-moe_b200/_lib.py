@@ -24,6 +24,7 @@ SIGNATURES = {
     "fp8lin_last_error": (c_char_p, []),
     "fp8lin_packed_bytes": (c_size_t, [c_int64, c_int64]),
     "fp8lin_prepack_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "fp8lin_pack_weight_nk": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "fp8lin_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int64]),
     "fp8lin_w8a16": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                              c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),

@@ -27,6 +27,7 @@ struct Tuning {
     int umma_splits = -1;     // force split-K factor of the tcgen05 kernel
     int swap_splits = -1;     // force split-K factor of the swapped-operand decode kernel
     int swap_enable = -1;     // 0 routes decode-sized W8A8 to the mma.sync streaming kernel instead
+    int swap_min_m = -1;      // smallest M routed to the swapped-operand kernel
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -60,7 +61,10 @@ int validate_common(const void* x, int64_t ldx, const void* w, const float* w_sc
 
 bool swap_eligible(int64_t M) {
     const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
-    return g_tune.swap_enable != 0 && M <= 64 && M <= max_m;
+    // up to 8 rows the mma.sync streaming kernel (several small CTAs per SM) starts and drains
+    // faster than the one-CTA-per-SM tcgen05 pipeline; measured cross-over is between 8 and 16 rows
+    const int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 9;
+    return g_tune.swap_enable != 0 && M >= min_m && M <= 64 && M <= max_m;
 }
 
 bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
@@ -71,6 +75,14 @@ bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
 }  // namespace
 
 namespace fp8lin {
+static int g_pdl = 1;
+void set_pdl_enabled(int on) { g_pdl = on; }
+int pdl_attribute(cudaLaunchAttribute* attr) {
+    if (!g_pdl) return 0;
+    attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr->val.programmaticStreamSerializationAllowed = 1;
+    return 1;
+}
 int set_error(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -85,15 +97,26 @@ extern "C" {
 int fp8lin_version(void) { return FP8LIN_VERSION; }
 const char* fp8lin_last_error(void) { return g_err; }
 
-size_t fp8lin_packed_bytes(int64_t K, int64_t N) { return (K > 0 && N > 0) ? (size_t)K * (size_t)N : 0; }
+size_t fp8lin_packed_bytes(int64_t K, int64_t N) {
+    return (K > 0 && N > 0) ? (size_t)pack_ntiles(N) * (size_t)pack_kblocks(K) * kPackTileBytes : 0;
+}
 
-int fp8lin_prepack_weight(const void* qweight_kn, void* w_nk, int64_t K, int64_t N, void* stream) {
+static int pack_common(const void* src, void* dst, int64_t K, int64_t N, bool src_is_kn, void* stream) {
     if (K <= 0 || N <= 0) return fail(FP8LIN_ERR_SHAPE, "bad shape K=%lld N=%lld", (long long)K, (long long)N);
     if (K % 16 != 0) return fail(FP8LIN_ERR_SHAPE, "K=%lld must be a multiple of 16", (long long)K);
-    if (!qweight_kn || !w_nk) return fail(FP8LIN_ERR_NULL, "qweight_kn and w_nk must not be NULL");
-    cudaError_t e = launch_transpose_u8((const unsigned char*)qweight_kn, (unsigned char*)w_nk, K, N, (cudaStream_t)stream);
+    if (!src || !dst) return fail(FP8LIN_ERR_NULL, "source and destination must not be NULL");
+    if (!aligned16(dst)) return fail(FP8LIN_ERR_ALIGN, "w_packed must be 16-byte aligned");
+    cudaError_t e = launch_pack_tiles((const unsigned char*)src, (unsigned char*)dst, K, N, src_is_kn, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "prepack launch: %s", cudaGetErrorString(e));
     return FP8LIN_OK;
+}
+
+int fp8lin_prepack_weight(const void* qweight_kn, void* w_packed, int64_t K, int64_t N, void* stream) {
+    return pack_common(qweight_kn, w_packed, K, N, true, stream);
+}
+
+int fp8lin_pack_weight_nk(const void* qweight_nk, void* w_packed, int64_t K, int64_t N, void* stream) {
+    return pack_common(qweight_nk, w_packed, K, N, false, stream);
 }
 
 size_t fp8lin_workspace_bytes(int scheme, int64_t M, int64_t K, int64_t N) {
@@ -220,6 +243,8 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "umma_splits")) g_tune.umma_splits = value;
     else if (!strcmp(knob, "swap_splits")) g_tune.swap_splits = value;
     else if (!strcmp(knob, "swap_enable")) g_tune.swap_enable = value;
+    else if (!strcmp(knob, "swap_min_m")) g_tune.swap_min_m = value;
+    else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;
 }

@@ -37,6 +37,29 @@ __host__ __device__ inline WsView ws_view(void* ws, size_t bytes) {
 enum : int { kDevOk = 0, kDevTimeoutFull = 0x101, kDevTimeoutEmpty = 0x102, kDevTimeoutTmemFull = 0x103,
              kDevTimeoutTmemEmpty = 0x104 };
 
+// ---- packed weight layout ----------------------------------------------------------
+// Weights are stored as 128-channel x 128-byte tiles, each tile contiguous (16 KiB),
+// tiles of one channel block consecutive along K:
+//   byte(n, k) = ((n / 128) * KB + k / 128) * 16384 + (n % 128) * 128 + (k % 128),  KB = ceil(K / 128)
+// N and K are zero-padded to multiples of 128.  A CTA that streams a channel block
+// reads one long sequential range of HBM, and a tile is exactly one TMA box.
+constexpr int kPackTile = 128;
+constexpr int kPackTileBytes = kPackTile * kPackTile;
+__host__ __device__ inline int64_t pack_kblocks(int64_t K) { return (K + kPackTile - 1) / kPackTile; }
+__host__ __device__ inline int64_t pack_ntiles(int64_t N) { return (N + kPackTile - 1) / kPackTile; }
+__host__ __device__ inline size_t pack_offset(int64_t n, int64_t k, int64_t KB) {
+    return (size_t)((n >> 7) * KB + (k >> 7)) * kPackTileBytes + (size_t)(n & 127) * kPackTile + (size_t)(k & 127);
+}
+
+// ---- programmatic dependent launch ------------------------------------------------
+// Every kernel lets the next kernel in the stream start launching early
+// (pdl_launch_dependents) and, before it touches memory a predecessor may still be
+// writing or reading (activations, outputs, scratch), waits for the predecessors to
+// finish (pdl_wait).  Weights are never written by a kernel, so their first loads are
+// issued before the wait.  Both are no-ops when the launch carries no such dependency.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- small numeric helpers ----------------------------------------------------
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }

@@ -37,30 +37,45 @@ cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* i
     return cudaGetLastError();
 }
 
-// dst[n][k] = src[k][n] for bytes, 64x64 tiles through shared memory.
+// Pack e4m3 weight bytes into the tiled layout (see pack_offset).  One CTA fills one
+// 128 x 128 tile through shared memory; `src_is_kn` selects the source orientation:
+// [K][N] (the reference's runtime buffer) or [N][K] (the checkpoint's layout).
 __global__ void __launch_bounds__(256)
-transpose_u8_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, int64_t K, int64_t N) {
-    __shared__ unsigned char tile[64][64 + 4];
-    const int64_t k0 = (int64_t)blockIdx.y * 64;
-    const int64_t n0 = (int64_t)blockIdx.x * 64;
-    const int tx = threadIdx.x & 63;
-    const int ty = threadIdx.x >> 6;  // 0..3
-    for (int r = ty; r < 64; r += 4) {
-        const int64_t k = k0 + r, n = n0 + tx;
-        tile[r][tx] = (k < K && n < N) ? src[k * N + n] : 0;
+pack_tiles_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, int64_t K, int64_t N,
+                  int src_is_kn) {
+    __shared__ unsigned char tile[128][128 + 4];      // [n][k]
+    const int64_t KB = pack_kblocks(K);
+    const int64_t tn = blockIdx.x, kb = blockIdx.y;
+    const int64_t n0 = tn * 128, k0 = kb * 128;
+    if (src_is_kn) {
+        // rows of the source are k, columns n: read along n (coalesced), store transposed
+        for (int i = threadIdx.x; i < 128 * 128; i += 256) {
+            const int kk = i >> 7, nn = i & 127;
+            const int64_t k = k0 + kk, n = n0 + nn;
+            tile[nn][kk] = (k < K && n < N) ? src[k * N + n] : 0;
+        }
+    } else {
+        for (int i = threadIdx.x; i < 128 * 128; i += 256) {
+            const int nn = i >> 7, kk = i & 127;
+            const int64_t k = k0 + kk, n = n0 + nn;
+            tile[nn][kk] = (k < K && n < N) ? src[n * K + k] : 0;
+        }
     }
     __syncthreads();
-    for (int r = ty; r < 64; r += 4) {
-        const int64_t n = n0 + r, k = k0 + tx;
-        if (n < N && k < K) dst[n * K + k] = tile[tx][r];
+    unsigned char* out = dst + (size_t)(tn * KB + kb) * kPackTileBytes;
+    for (int i = threadIdx.x; i < 128 * 32; i += 256) {             // 4 bytes per thread, coalesced
+        const int nn = i >> 5, k4 = (i & 31) * 4;
+        const uint32_t v = (uint32_t)tile[nn][k4] | ((uint32_t)tile[nn][k4 + 1] << 8) |
+                           ((uint32_t)tile[nn][k4 + 2] << 16) | ((uint32_t)tile[nn][k4 + 3] << 24);
+        *reinterpret_cast<uint32_t*>(out + nn * 128 + k4) = v;
     }
 }
 
-cudaError_t launch_transpose_u8(const unsigned char* src_kn, unsigned char* dst_nk, int64_t K, int64_t N,
-                                cudaStream_t stream) {
+cudaError_t launch_pack_tiles(const unsigned char* src, unsigned char* dst, int64_t K, int64_t N, bool src_is_kn,
+                              cudaStream_t stream) {
     if (K == 0 || N == 0) return cudaSuccess;
-    dim3 grid((unsigned)((N + 63) / 64), (unsigned)((K + 63) / 64));
-    transpose_u8_kernel<<<grid, 256, 0, stream>>>(src_kn, dst_nk, K, N);
+    dim3 grid((unsigned)pack_ntiles(N), (unsigned)pack_kblocks(K));
+    pack_tiles_kernel<<<grid, 256, 0, stream>>>(src, dst, K, N, src_is_kn ? 1 : 0);
     return cudaGetLastError();
 }
 

@@ -12,10 +12,15 @@ namespace fp8lin {
 // Record a printf-style message for fp8lin_last_error() and return `code` (defined in api.cu).
 int set_error(int code, const char* fmt, ...);
 
+// Fills the attribute that makes a launch a programmatic dependent of the previous kernel in
+// its stream; returns the number of attributes written (0 when disabled by the tuning knob).
+int pdl_attribute(cudaLaunchAttribute* attr);
+void set_pdl_enabled(int on);
+
 // ---- weight-streaming kernel (stream_kernel.cu) ------------------------------
 struct StreamArgs {
     const __nv_bfloat16* x;      // [M][ldx]
-    const unsigned char* w;      // [N][K] e4m3
+    const unsigned char* w;      // packed e4m3 tiles (pack_offset)
     const float* w_scale;        // [N]
     const float* input_scale;    // 1 float (W8A8) or nullptr
     const __nv_bfloat16* bias;   // [N] or nullptr
@@ -43,13 +48,13 @@ cudaError_t launch_stream(int scheme, const StreamPlan& plan, StreamArgs args, c
 // ---- elementwise helpers (elementwise.cu) ------------------------------------
 cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* input_scale,
                              unsigned char* xq, int64_t M, int64_t K, cudaStream_t stream);
-cudaError_t launch_transpose_u8(const unsigned char* src_kn, unsigned char* dst_nk, int64_t K, int64_t N,
-                                cudaStream_t stream);
+cudaError_t launch_pack_tiles(const unsigned char* src, unsigned char* dst, int64_t K, int64_t N, bool src_is_kn,
+                              cudaStream_t stream);
 
 // ---- tcgen05 GEMM (umma_gemm.cu) ---------------------------------------------
 struct UmmaArgs {
     const unsigned char* xq;     // [M][K] e4m3, contiguous (produced by launch_act_quant)
-    const unsigned char* w;      // [N][K] e4m3
+    const unsigned char* w;      // packed e4m3 tiles (pack_offset)
     const float* w_scale;
     const float* input_scale;
     const __nv_bfloat16* bias;

@@ -97,8 +97,11 @@ stream_linear_kernel(StreamArgs p) {
     // rows of W this lane streams (clamped: out-of-range rows are computed but never stored)
     const int row_a = min(n_warp0 + g, p.N - 1);
     const int row_b = min(n_warp0 + g + 8, p.N - 1);
-    const unsigned char* wa = p.w + (size_t)row_a * p.K;
-    const unsigned char* wb = p.w + (size_t)row_b * p.K;
+    // packed layout: tile (row / 128, k / 128) is 16 KiB contiguous, row r of a tile at r * 128
+    const int KB = (p.K + 127) >> 7;
+    const unsigned char* wa = p.w + ((size_t)(row_a >> 7) * KB) * kPackTileBytes + (row_a & 127) * 128;
+    const unsigned char* wb = p.w + ((size_t)(row_b >> 7) * KB) * kPackTileBytes + (row_b & 127) * 128;
+    auto tile_off = [](int k) { return (size_t)(k >> 7) * kPackTileBytes + (k & 127); };
 
     float in_scale = 1.f;
     if (SCHEME == FP8LIN_W8A8_STATIC) in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
@@ -149,8 +152,8 @@ stream_linear_kernel(StreamArgs p) {
     auto load_w_step = [&](int chunk, int s) {
         const int k = k_beg + chunk * kChunk + s * 64 + t * 16;
         if (k < k_end) {
-            wr[2 * s] = ld_stream16(wa + k);
-            wr[2 * s + 1] = ld_stream16(wb + k);
+            wr[2 * s] = ld_stream16(wa + tile_off(k));
+            wr[2 * s + 1] = ld_stream16(wb + tile_off(k));
         } else {
             wr[2 * s] = make_uint4(0, 0, 0, 0);
             wr[2 * s + 1] = make_uint4(0, 0, 0, 0);
@@ -158,7 +161,9 @@ stream_linear_kernel(StreamArgs p) {
     };
 
 #pragma unroll
-    for (int s = 0; s < 4; ++s) load_w_step(0, s);
+    for (int s = 0; s < 4; ++s) load_w_step(0, s);       // weights first: they do not depend on the predecessor
+    pdl_launch_dependents();
+    pdl_wait();                                           // x, y and the split-K scratch may belong to the predecessor
 #pragma unroll
     for (int part = 0; part < kParts; ++part) { load_x(0, part); store_x(0, part); }
     __syncthreads();
@@ -281,8 +286,15 @@ static cudaError_t launch_one(const StreamArgs& a, dim3 grid, cudaStream_t strea
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
     }
-    kern<<<grid, NWARPS * 32, smem, stream>>>(a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NWARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.numAttrs = pdl_attribute(attr);
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 StreamPlan plan_stream(int scheme, int64_t M, int64_t K, int64_t N, int force_splits) {

@@ -147,7 +147,14 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     mbar_expect_tx(full, Cfg::kStageBytes);
                     const uint32_t sa = smem_base + st * Cfg::kStageBytes;
                     tma_load_2d(sa, &tmap_a, kb * kBK, tm * kBM, full);
-                    tma_load_2d(sa + Cfg::kABytes, &tmap_b, kb * kBK, tn * BN, full);
+                    // packed weights: the tile of channel block cb and K block kb is rows
+                    // [(cb*KB + kb)*128, +128) of a [tiles*128][128-byte] matrix
+#pragma unroll
+                    for (int sub = 0; sub < (BN + 127) / 128; ++sub) {
+                        const int n_sub = tn * BN + sub * 128;
+                        const int wrow = ((n_sub >> 7) * sched.kblocks_total + kb) * 128 + (n_sub & 127);
+                        tma_load_2d(sa + Cfg::kABytes + sub * 128 * kBK, &tmap_b, 0, wrow, full);
+                    }
                 }
             }
             if (!ok) {
@@ -482,7 +489,8 @@ cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t
     CUtensorMap ta, tb, ty;
     const uint32_t piece = pl.bn == 256 ? 32 : (pl.bn / 2 < 64 ? pl.bn / 2 : 64);
     if (!encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K, kBM) ||
-        !encode_u8_2d(&tb, a.w, (uint64_t)a.N, (uint64_t)a.K, (uint32_t)pl.bn) ||
+        !encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128,
+                      (uint32_t)(pl.bn < 128 ? pl.bn : 128)) ||
         !encode_out_2d(&ty, a.y, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldy * 2, piece)) {
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;

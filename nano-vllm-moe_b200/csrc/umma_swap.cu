@@ -10,8 +10,8 @@
 //                tile (128-byte swizzle) and the raw bf16 activation block
 //                [MP x 128] into a ring of 5..9 stages (144..80 KB of weights in
 //                flight per SM).
-//   warps 2..9   activation converters, one ring slot per warp (up to eight K
-//                blocks are converted concurrently): quantise the M real rows of
+//   warps 2..9   activation converters in teams of 1, 2 or 4 warps, one ring slot per
+//                team (several K blocks are converted concurrently): quantise the M real rows of
 //                the raw block to e4m3 with the static scale (exact division)
 //                and write them into the K-major, 128-byte-swizzled MMA "B"
 //                tile (rows M..MP-1 stay zero); fence.proxy.async; arrive.
@@ -42,6 +42,8 @@ struct SwapCfg {
     static constexpr int kXrawBytes = MP * kKB * 2;              // raw bf16 activation block
     static constexpr int kStageBytes = kWBytes + kXqBytes + kXrawBytes;
     static constexpr int kStages = MP <= 16 ? 9 : (MP <= 32 ? 7 : 5);
+    // converter warps that share one K block (more rows -> more warps per block)
+    static constexpr int kTeam = MP <= 16 ? 1 : (MP <= 32 ? 2 : 4);
     static constexpr int kRingBytes = kStages * kStageBytes;
     static constexpr int kSmemBytes = kRingBytes + 1024;
     static constexpr int kTmemCols = 2 * MP < 32 ? 32 : 2 * MP;
@@ -100,7 +102,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) {
             mbar_init(smem_u32(&bar_full[i]), 1);
-            mbar_init(smem_u32(&bar_xq[i]), 1);
+            mbar_init(smem_u32(&bar_xq[i]), Cfg::kTeam);
             mbar_init(smem_u32(&bar_empty[i]), 1);
         }
         for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bar_tfull[i]), 1); mbar_init(smem_u32(&bar_tempty[i]), 4); }
@@ -119,6 +121,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -127,17 +130,33 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
             uint32_t it = 0;
             bool ok = true;
+            // First pass over the ring: the weight tiles go out at once; the activation blocks
+            // follow when the predecessor kernel (which may be producing x) has finished.
+            const int first_kb = min(kb1 - kb0, S);
+            if (first_tile < sched.n_tiles) {
+                for (int i = 0; i < first_kb; ++i) {
+                    const uint32_t full = smem_u32(&bar_full[i]);
+                    mbar_expect_tx(full, Cfg::kWBytes + (uint32_t)p.M * 256u);   // the x box holds the M real rows only
+                    tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_w, 0,
+                                (first_tile * sched.kblocks_total + kb0 + i) * kTileN, full);   // one packed tile
+                }
+                pdl_wait();
+                for (int i = 0; i < first_kb; ++i)
+                    tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kWBytes + Cfg::kXqBytes, &tmap_x,
+                                (kb0 + i) * kKB, 0, smem_u32(&bar_full[i]));
+            }
             for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step) {
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    if (it < (uint32_t)first_kb) continue;                       // issued above
                     const int st = it % S;
                     const uint32_t ph = (it / S) & 1;
                     if (s_abort || !mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1, p.status, kDevTimeoutEmpty)) {
                         s_abort = 1; ok = false; break;
                     }
                     const uint32_t full = smem_u32(&bar_full[st]);
-                    mbar_expect_tx(full, Cfg::kWBytes + (uint32_t)p.M * 256u);   // the x box holds the M real rows only
+                    mbar_expect_tx(full, Cfg::kWBytes + (uint32_t)p.M * 256u);
                     const uint32_t sa = smem_base + st * Cfg::kStageBytes;
-                    tma_load_2d(sa, &tmap_w, kb * kKB, t * kTileN, full);
+                    tma_load_2d(sa, &tmap_w, 0, (t * sched.kblocks_total + kb) * kTileN, full);
                     tma_load_2d(sa + Cfg::kWBytes + Cfg::kXqBytes, &tmap_x, kb * kKB, 0, full);
                 }
             }
@@ -182,7 +201,9 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     } else if (warp < 2 + kConvWarps) {
         // ================= activation converters (warps 2..9) =================
-        const int cw = warp - 2;
+        constexpr int kTeams = kConvWarps / Cfg::kTeam;
+        const int team = (warp - 2) / Cfg::kTeam;            // a ring slot always belongs to the same team
+        const int member = (warp - 2) % Cfg::kTeam;
         const ExactDiv div_scale(fmaxf(__ldg(p.input_scale), 1e-12f));
         const int items = p.M * 8;                          // (row, 16-element chunk) pairs of the real rows
         uint32_t it = 0;
@@ -192,13 +213,13 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 // a ring slot always belongs to the same warp, so every warp sees the phases of
                 // the barriers it waits on in order (a parity wait may only look one phase ahead)
                 const int st = it % S;
-                if (st % kConvWarps != cw) continue;
+                if (st % kTeams != team) continue;
                 const uint32_t ph = (it / S) & 1;
                 if (s_abort || !mbar_wait(smem_u32(&bar_full[st]), ph, p.status, kDevTimeoutFull)) { s_abort = 1; ok = false; break; }
                 const uint32_t sa = smem_base + st * Cfg::kStageBytes;
                 const uint32_t xq = sa + Cfg::kWBytes;
                 const uint32_t xr = xq + Cfg::kXqBytes;
-                for (int i = lane; i < items; i += 32) {
+                for (int i = member * 32 + lane; i < items; i += 32 * Cfg::kTeam) {
                     const int m = i >> 3, c = i & 7;
                     uint4 a, b;
                     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w)
@@ -218,6 +239,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     } else {
         // ================= epilogue (warps 10..13) =================
+        pdl_wait();                                          // y may still be read by the predecessor
         const int q = warp & 3;
         const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
         int tl = 0;
@@ -259,6 +281,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     if (kSplit) {
         // ---- cluster reduction: CTA r finishes channels [r*band, (r+1)*band) of the tile ----
         __syncwarp();
+        pdl_wait();
         cluster_sync_all();
         const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
         const int band = (kTileN + sched.splits - 1) / sched.splits;
@@ -366,22 +389,24 @@ static cudaError_t launch_swap(const SwapPlan& pl, const UmmaArgs& a, const CUte
     cfg.blockDim = dim3(kSwapThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    int na = pdl_attribute(attr);
     if (kSplit) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)pl.splits;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)pl.splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
     }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s);
 }
 
 cudaError_t launch_swap_w8a8(const SwapPlan& pl, const UmmaArgs& a, const void* x, int64_t ldx, cudaStream_t stream,
                              const char** why) {
     CUtensorMap tw, tx;
-    if (!encode_u8_2d(&tw, a.w, (uint64_t)a.N, (uint64_t)a.K, kTileN) ||
+    if (!encode_u8_2d(&tw, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128, kTileN) ||
         !encode_x_bf16(&tx, x, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)ldx * 2, (uint32_t)a.M)) {
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;

@@ -12,8 +12,8 @@ Differences, all deliberate:
 * one backend (libfp8lin.so); no NANOVLLM_FP8_W8A8_RUNTIME_BACKEND dispatch;
 * per-output-channel weight scales are kept for W8A8 too (the reference folds
   them into one per-tensor scale and re-rounds the weights, fp8.py:100-105);
-* after loading, the weight is repacked once to [N_part, K_part] (the layout
-  every kernel streams) and the [K, N] copy is released.
+* after loading, the weight is repacked once into 128 x 128-byte tiles (the
+  layout every kernel streams, ``qweight_packed``) and the [K, N] copy is released.
 """
 from __future__ import annotations
 
@@ -135,12 +135,12 @@ class Fp8LinearMethod(QuantizeMethodBase):
         if major != 10:
             raise RuntimeError("the fp8lin kernels are built for sm_100a (B200) only")
         _lib.load()  # fail here, loudly, if the CUDA library was not built
-        layer.register_buffer("qweight_nk", kernels.prepack_weight(layer.qweight), persistent=False)
+        layer.register_buffer("qweight_packed", kernels.prepack_weight(layer.qweight), persistent=False)
         layer.weight_scale.data = layer.weight_scale.data.to(torch.float32).contiguous()
         if self.is_w8a8:
             layer.input_scale.data = layer.input_scale.data.to(torch.float32).reshape(())
         if not self.quant_config.keep_checkpoint_layout:
-            layer.qweight = torch.empty((0, 0), dtype=torch.uint8, device=layer.qweight_nk.device)
+            layer.qweight = torch.empty((0, 0), dtype=torch.uint8, device=layer.qweight_packed.device)
         layer._fp8_backend = "fp8lin_w8a8" if self.is_w8a8 else "fp8lin_w8a16"
 
     # ---- forward ---------------------------------------------------------------------
@@ -158,7 +158,7 @@ class Fp8LinearMethod(QuantizeMethodBase):
         if bias is not None and bias.dtype != torch.bfloat16:
             bias = bias.to(torch.bfloat16)
         if self.is_w8a8:
-            y = kernels.launch_w8a8_gemm(x2, layer.qweight_nk, layer.input_scale, layer.weight_scale, bias)
+            y = kernels.launch_w8a8_gemm(x2, layer.qweight_packed, layer.input_scale, layer.weight_scale, bias)
         else:
-            y = kernels.launch_w8a16_gemm(x2, layer.qweight_nk, layer.weight_scale, bias)
+            y = kernels.launch_w8a16_gemm(x2, layer.qweight_packed, layer.weight_scale, bias)
         return y.view(*x.shape[:-1], y.shape[-1]).to(x.dtype)

@@ -71,33 +71,47 @@ def read_status(device: torch.device) -> int:
     return out.value
 
 
-def prepack_weight(qweight_kn: torch.Tensor) -> torch.Tensor:
-    """uint8 e4m3 codes [K, N] (the reference's ``qweight`` buffer) -> [N, K]."""
-    _require_cuda(qweight_kn)
-    if qweight_kn.dtype != torch.uint8 or qweight_kn.dim() != 2:
-        raise ValueError("qweight must be a 2-D uint8 tensor [K, N]")
-    src = qweight_kn.contiguous()
-    k, n = src.shape
-    out = torch.empty((n, k), dtype=torch.uint8, device=src.device)
+def packed_bytes(k: int, n: int) -> int:
+    return int(_lib.load().fp8lin_packed_bytes(k, n))
+
+
+def _pack(src: torch.Tensor, k: int, n: int, from_kn: bool) -> torch.Tensor:
+    _require_cuda(src)
+    if src.dtype not in (torch.uint8, torch.float8_e4m3fn) or src.dim() != 2:
+        raise ValueError("weight codes must be a 2-D uint8/float8_e4m3fn tensor")
+    src = src.contiguous()
+    out = torch.empty(packed_bytes(k, n), dtype=torch.uint8, device=src.device)
+    fn = _lib.load().fp8lin_prepack_weight if from_kn else _lib.load().fp8lin_pack_weight_nk
     with torch.cuda.device(src.device):
-        rc = _lib.load().fp8lin_prepack_weight(src.data_ptr(), out.data_ptr(), k, n, _stream_ptr(src.device))
-    _lib.raise_for(rc, "fp8lin_prepack_weight")
+        rc = fn(src.data_ptr(), out.data_ptr(), k, n, _stream_ptr(src.device))
+    _lib.raise_for(rc, "fp8lin_prepack_weight" if from_kn else "fp8lin_pack_weight_nk")
     return out
 
 
-def _check_linear_args(x, w_nk, weight_scale, bias):
-    _require_cuda(x, w_nk, weight_scale, bias)
+def prepack_weight(qweight_kn: torch.Tensor) -> torch.Tensor:
+    """e4m3 codes [K, N] (the reference's ``qweight`` buffer) -> the kernels' packed tile layout."""
+    k, n = qweight_kn.shape
+    return _pack(qweight_kn, k, n, True)
+
+
+def pack_weight_nk(qweight_nk: torch.Tensor) -> torch.Tensor:
+    """e4m3 codes [N, K] (the checkpoint layout) -> the kernels' packed tile layout."""
+    n, k = qweight_nk.shape
+    return _pack(qweight_nk, k, n, False)
+
+
+def _check_linear_args(x, w_packed, weight_scale, bias):
+    _require_cuda(x, w_packed, weight_scale, bias)
     if x.dim() != 2 or x.dtype != torch.bfloat16:
         raise ValueError("x must be a 2-D bfloat16 tensor [M, K]")
-    if w_nk.dim() != 2 or w_nk.dtype not in (torch.uint8, torch.float8_e4m3fn):
-        raise ValueError("w_nk must be a 2-D uint8/float8_e4m3fn tensor [N, K]")
-    if not w_nk.is_contiguous():
-        raise ValueError("w_nk must be contiguous")
-    n, k = w_nk.shape
-    if x.shape[1] != k:
-        raise ValueError(f"x has K={x.shape[1]} but the weight has K={k}")
-    if weight_scale.dtype != torch.float32 or weight_scale.numel() != n:
+    if w_packed.dtype != torch.uint8 or w_packed.dim() != 1 or not w_packed.is_contiguous():
+        raise ValueError("w_packed must be the flat uint8 buffer made by prepack_weight / pack_weight_nk")
+    if weight_scale.dtype != torch.float32 or weight_scale.dim() != 1:
         raise ValueError("weight_scale must be float32 with one value per output channel")
+    n, k = weight_scale.numel(), x.shape[1]
+    if k % 16 != 0 or w_packed.numel() != packed_bytes(k, n):
+        raise ValueError(f"x has K={k}, weight_scale has N={n}, but the packed weight holds "
+                         f"{w_packed.numel()} bytes (expected {packed_bytes(k, n) if k % 16 == 0 else 'K % 16 == 0'})")
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n):
         raise ValueError("bias must be bfloat16 [N]")
     if x.stride(1) != 1:
@@ -105,28 +119,28 @@ def _check_linear_args(x, w_nk, weight_scale, bias):
     return x, n, k
 
 
-def launch_w8a16_gemm(x: torch.Tensor, w_nk: torch.Tensor, weight_scale: torch.Tensor,
+def launch_w8a16_gemm(x: torch.Tensor, w_packed: torch.Tensor, weight_scale: torch.Tensor,
                       bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """bf16 ``(x @ W^T) * weight_scale + bias`` with e4m3 weights [N, K]."""
-    x, n, k = _check_linear_args(x, w_nk, weight_scale, bias)
+    """bf16 ``(x @ W^T) * weight_scale + bias`` with packed e4m3 weights."""
+    x, n, k = _check_linear_args(x, w_packed, weight_scale, bias)
     m = x.shape[0]
     y = out if out is not None else torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
         need = workspace_bytes(_lib.W8A16, m, k, n)
         ws = workspace(x.device, need)
         rc = _lib.load().fp8lin_w8a16(
-            x.data_ptr(), x.stride(0), w_nk.data_ptr(), weight_scale.data_ptr(),
+            x.data_ptr(), x.stride(0), w_packed.data_ptr(), weight_scale.data_ptr(),
             bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0),
             m, k, n, ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
     _lib.raise_for(rc, "fp8lin_w8a16")
     return y
 
 
-def launch_w8a8_gemm(x: torch.Tensor, w_nk: torch.Tensor, input_scale: torch.Tensor,
+def launch_w8a8_gemm(x: torch.Tensor, w_packed: torch.Tensor, input_scale: torch.Tensor,
                      weight_scale: torch.Tensor, bias: torch.Tensor | None = None,
                      out: torch.Tensor | None = None) -> torch.Tensor:
     """Static-scale W8A8: x is quantised to e4m3 with ``input_scale`` inside the call."""
-    x, n, k = _check_linear_args(x, w_nk, weight_scale, bias)
+    x, n, k = _check_linear_args(x, w_packed, weight_scale, bias)
     _require_cuda(input_scale)
     if input_scale.dtype != torch.float32 or input_scale.numel() != 1:
         raise ValueError("input_scale must be one float32 value on the device")
@@ -136,7 +150,7 @@ def launch_w8a8_gemm(x: torch.Tensor, w_nk: torch.Tensor, input_scale: torch.Ten
         need = workspace_bytes(_lib.W8A8_STATIC, m, k, n)
         ws = workspace(x.device, need)
         rc = _lib.load().fp8lin_w8a8(
-            x.data_ptr(), x.stride(0), w_nk.data_ptr(), weight_scale.data_ptr(), input_scale.data_ptr(),
+            x.data_ptr(), x.stride(0), w_packed.data_ptr(), weight_scale.data_ptr(), input_scale.data_ptr(),
             bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0),
             m, k, n, ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
     _lib.raise_for(rc, "fp8lin_w8a8")

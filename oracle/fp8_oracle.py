@@ -414,6 +414,17 @@ def known_answer_case(pattern, m, n, k, seed=42):
     return bf16_round(x), e4m3_encode(w), np.float32(si), np.float32(sw)
 
 
+def pack_tiles(wq_nk: np.ndarray) -> np.ndarray:
+    """[N,K] codes -> the kernels' packed layout (this build's own format, no reference
+    counterpart): 128 x 128-byte tiles, tile (n/128, k/128) at ((n/128)*KB + k/128)*16384,
+    byte (n%128)*128 + k%128 inside it, zero padding."""
+    n, k = wq_nk.shape
+    nt, kb = -(-n // 128), -(-k // 128)
+    pad = np.zeros((nt * 128, kb * 128), dtype=np.uint8)
+    pad[:n, :k] = wq_nk
+    return pad.reshape(nt, 128, kb, 128).transpose(0, 2, 1, 3).reshape(-1).copy()
+
+
 # --------------------------------------------------------------------------
 # tolerances shared by the tests
 # --------------------------------------------------------------------------

@@ -27,7 +27,7 @@ def from_bf16(t):
 def upload_case(c):
     d = {
         "x": to_bf16_cuda(c["x"]),
-        "w_nk": torch.from_numpy(c["wq"]).cuda(),
+        "w_nk": kernels().pack_weight_nk(torch.from_numpy(c["wq"]).cuda()),
         "w_scale": torch.from_numpy(c["w_scale"]).cuda(),
         "bias": to_bf16_cuda(c["bias"]) if c.get("bias") is not None else None,
         "input_scale": torch.tensor(float(c["input_scale"]), dtype=torch.float32, device="cuda"),

@@ -22,7 +22,7 @@ SCHEMES = ["fp8_w8a16", "fp8_w8a8_static"]
 def _clean_tuning_and_status():
     Kn = kernels()
     yield
-    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable"):
+    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable", "swap_min_m"):
         Kn.set_tuning(knob, -1)
     torch.cuda.synchronize()
     assert Kn.read_status(torch.device("cuda", 0)) == 0
@@ -34,13 +34,17 @@ def test_library_is_loaded_from_the_tree(pkg):
     assert torch.cuda.get_device_capability(0)[0] == 10
 
 
-def test_prepack_is_a_byte_transpose():
+def test_prepack_layout_is_exact():
     Kn = kernels()
     g = torch.Generator().manual_seed(0)
-    for k, n in [(64, 48), (448, 576), (2048, 2048), (1408, 72)]:
-        q = torch.randint(0, 256, (k, n), dtype=torch.uint8, generator=g)
-        out = Kn.prepack_weight(q.cuda()).cpu()
-        assert torch.equal(out, q.t().contiguous())
+    for k, n in [(64, 48), (448, 576), (2048, 2048), (1408, 72), (16, 8)]:
+        q_nk = torch.randint(0, 256, (n, k), dtype=torch.uint8, generator=g)
+        want = O.pack_tiles(q_nk.numpy())
+        assert want.size == Kn.packed_bytes(k, n)
+        from_nk = Kn.pack_weight_nk(q_nk.cuda()).cpu().numpy()
+        from_kn = Kn.prepack_weight(q_nk.t().contiguous().cuda()).cpu().numpy()
+        np.testing.assert_array_equal(from_nk, want)
+        np.testing.assert_array_equal(from_kn, want)
 
 
 def test_activation_codes_match_reference_bit_for_bit(golden):
@@ -102,7 +106,7 @@ def test_known_answer_patterns(golden, pattern):
     for si, (m, n, k) in enumerate(g["kat_shapes"]):
         m, n, k = int(m), int(n), int(k)
         x, wq, s_in, s_w = O.known_answer_case(pattern, m, n, k)
-        d = {"x": to_bf16_cuda(x), "w_nk": torch.from_numpy(wq).cuda(),
+        d = {"x": to_bf16_cuda(x), "w_nk": Kn.pack_weight_nk(torch.from_numpy(wq).cuda()),
              "w_scale": torch.full((n,), float(s_w), device="cuda"),
              "input_scale": torch.tensor(float(s_in), device="cuda"), "bias": None}
         y = run_linear("fp8_w8a8_static", d, bias=False)
@@ -134,6 +138,7 @@ def test_streaming_kernel_parity(scheme, m, k, n):
         scheme = scheme.split("/")[0]
         assert kernels().variant_name(1, m, k, n).startswith("stream_mma_w8a8")
     elif scheme == "fp8_w8a8_static":
+        kernels().set_tuning("swap_min_m", 1)        # by default M <= 8 goes to the mma.sync kernel
         assert kernels().variant_name(1, m, k, n).startswith("umma_swap_w8a8")
     c = O.make_case(20260519 + m * 7 + k + n, m, k, n)
     d = upload_case(c)
@@ -185,7 +190,7 @@ def test_strided_x_and_empty_batch():
     assert Kn.launch_w8a8_gemm(empty, d["w_nk"], d["input_scale"], d["w_scale"], d["bias"]).shape == (0, 80)
     assert Kn.launch_w8a16_gemm(empty, d["w_nk"], d["w_scale"], None).shape == (0, 80)
     with pytest.raises(ValueError):
-        Kn.launch_w8a16_gemm(d["x"][:, :100].contiguous(), d["w_nk"], d["w_scale"])    # K mismatch
+        Kn.launch_w8a16_gemm(torch.zeros((6, 256), dtype=torch.bfloat16, device="cuda"), d["w_nk"], d["w_scale"])  # K mismatch
 
 
 UMMA_SHAPES = [
@@ -220,6 +225,7 @@ def test_tcgen05_tile_and_split_variants(bn, splits):
 @pytest.mark.parametrize("m", [1, 16, 17, 33, 64])
 def test_swapped_tcgen05_kernel_split_variants(m, splits):
     Kn = kernels()
+    Kn.set_tuning("swap_min_m", 1)
     Kn.set_tuning("swap_splits", splits)
     c = O.make_case(900 + m + splits, m, 2048, 640)
     d = upload_case(c)
@@ -281,7 +287,7 @@ def test_layer_end_to_end(pkg, scheme):
     lay.bias.data = lay.bias.data.to(torch.bfloat16)
     assert lay.qweight.dtype == torch.uint8 and lay.weight_scale.dtype == torch.float32
     pkg.process_weights_after_loading(lay)
-    assert lay.qweight_nk.shape == (n_gate + n_up, k)
+    assert lay.qweight_packed.numel() == kernels().packed_bytes(k, n_gate + n_up)
     x = O.bf16_round(rng.standard_normal((3, m // 3, k), dtype=np.float32))
     y = from_bf16(lay(to_bf16_cuda(x)))
     assert y.shape == (3, 3, n_gate + n_up)

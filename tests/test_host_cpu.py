@@ -160,6 +160,7 @@ def test_workspace_and_variant_queries(pkg):
     lib = pkg._lib.load()
     L = pkg._lib
     assert lib.fp8lin_packed_bytes(2048, 11008) == 2048 * 11008
+    assert lib.fp8lin_packed_bytes(448, 576) == 4 * 5 * 16384      # K and N padded to 128
     for scheme in (L.W8A16, L.W8A8_STATIC):
         for m, k, n in [(1, 2048, 2048), (16, 2048, 11008), (256, 11008, 2048), (1024, 2048, 11008), (64, 18944, 3584)]:
             need = lib.fp8lin_workspace_bytes(scheme, m, k, n)
@@ -174,7 +175,7 @@ def test_kernels_refuse_cpu_tensors(pkg):
     from importlib import import_module
     K = import_module("nano-vllm-moe_b200.quantization.kernels")
     x = torch.zeros(2, 32, dtype=torch.bfloat16)
-    w = torch.zeros(16, 32, dtype=torch.uint8)
+    w = torch.zeros(16384, dtype=torch.uint8)
     s = torch.ones(16)
     with pytest.raises(ValueError, match="CUDA"):
         K.launch_w8a16_gemm(x, w, s)
