@@ -124,6 +124,42 @@ int fp8lin_linear_static_scratch(int scheme, const void* x, int64_t ldx, const v
 int fp8lin_quantize_activation(const void* x, int64_t ldx, const float* input_scale,
                                void* xq, int64_t M, int64_t K, void* stream);
 
+/* ---- MoE expert FFN --------------------------------------------------------------
+ * The routed expert FFN of nanovllm/executor/moe on FP8 operands, as a grouped GEMM
+ * through the same tcgen05 kernels.  Expert weights are packed per expert with
+ * fp8lin_pack_weight_nk and concatenated: w13_packed = E x packed(K=H, N=2I) with rows
+ * [0,I) = gate, [I,2I) = up (the reference's w13 stacking, blocks/base.py:58-63),
+ * w2_packed = E x packed(K=I, N=H).  Scales: w13_scale f32 [E][2I], w2_scale f32 [E][H],
+ * one static activation scale per projection.
+ *
+ * fp8lin_moe_route replaces SoftmaxTopKRouter.select_experts (executor/moe/router.py:24-34):
+ * fp32 softmax over E logits (logits_dtype 0 = f32, 1 = bf16), top-k, optional
+ * renormalisation; topk_w f32 [T][k], topk_ids i32 [T][k]. */
+int fp8lin_moe_route(const void* logits, int logits_dtype, int64_t ld, int64_t T, int E, int top_k,
+                     int renormalize, float* topk_w, int32_t* topk_ids, void* stream);
+
+/* Scratch for fp8lin_moe_experts_w8a8 (zero-filled once, like the linear workspace). */
+size_t fp8lin_moe_workspace_bytes(int64_t rows, int E, int64_t H, int64_t I);
+
+/* Replaces MoEExpertsKernel.apply (experts/eager_experts.py:9-35, experts/optimized.py:142-270)
+ * for `rows` routed rows: ids[r] is the LOCAL expert of routed row r (rows whose id is outside
+ * [0,E) are skipped and their output row is left untouched), topk_w[r] its routing weight, and
+ * the row's activations are x[r / x_div] (x_div = top_k when x holds one row per token, as
+ * NoEPPrepareFinalize.prepare expands it, no_ep.py:27; x_div = 1 when x already holds one row per
+ * routed row, as after the expert-parallel dispatch, torch_alltoall.py:49).
+ *   gu = bf16(W8A8(x_r, W13[e]));  h = bf16(silu(gate) * up);
+ *   out_routed[r] = bf16( W8A8(h, W2[e]) * topk_w[r] )            bf16 [rows][ld_out]
+ * Groups rows by expert on the device (no host synchronisation). */
+int fp8lin_moe_experts_w8a8(const void* x, int64_t ldx, int x_div, const int32_t* ids, const float* topk_w,
+                            int64_t rows, const void* w13_packed, const float* w13_scale,
+                            const float* w13_input_scale, const void* w2_packed, const float* w2_scale,
+                            const float* w2_input_scale, int E, int64_t H, int64_t I, void* out_routed,
+                            int64_t ld_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* y[t] = bf16( sum_j routed[t*top_k + j] ) in slot order; replaces the .view(T,k,H).sum(1) of
+ * NoEPPrepareFinalize.finalize (no_ep.py:45) / TorchAllToAllPrepareFinalize.finalize (:90). */
+int fp8lin_moe_combine(const void* routed, void* y, int64_t T, int top_k, int64_t H, void* stream);
+
 /* Which kernel variant a shape is routed to ("stream_mma_w8a8_m16", "umma_w8a8_128x256", ...),
  * for labelling bench rows and ncu captures.  Host-only, returns a static string. */
 const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);

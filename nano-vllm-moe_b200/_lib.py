@@ -33,6 +33,12 @@ SIGNATURES = {
     "fp8lin_linear_static_scratch": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "fp8lin_quantize_activation": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "fp8lin_moe_route": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fp8lin_moe_workspace_bytes": (c_size_t, [c_int64, c_int, c_int64, c_int64]),
+    "fp8lin_moe_experts_w8a8": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
+                                        c_int64, c_void_p, c_size_t, c_void_p]),
+    "fp8lin_moe_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_void_p]),
     "fp8lin_variant_name": (c_char_p, [c_int, c_int64, c_int64, c_int64]),
     "fp8lin_set_tuning": (c_int, [c_char_p, c_int]),
     "fp8lin_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),

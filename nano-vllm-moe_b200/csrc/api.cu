@@ -249,6 +249,101 @@ int fp8lin_set_tuning(const char* knob, int value) {
     return FP8LIN_OK;
 }
 
+// ---- MoE -------------------------------------------------------------------------------------
+namespace {
+struct MoeWs {
+    size_t off_offsets, off_sorted, off_chunks, off_meta, off_gu, off_hq, total;
+};
+MoeWs moe_ws_layout(int64_t rows, int E, int64_t H, int64_t I) {
+    MoeWs w;
+    size_t o = FP8LIN_WS_HEADER_BYTES;
+    auto take = [&](size_t bytes) { size_t at = o; o = align_up(o + bytes, 256); return at; };
+    w.off_offsets = take((size_t)(E + 1) * 4);
+    w.off_sorted = take((size_t)(rows > 0 ? rows : 1) * 4);
+    w.off_chunks = take((size_t)(E + rows / 16 + 2) * 16);
+    w.off_meta = take(16);
+    w.off_gu = take((size_t)rows * 2 * I * 2);
+    w.off_hq = take((size_t)rows * I);
+    w.total = o;
+    (void)H;
+    return w;
+}
+}  // namespace
+
+int fp8lin_moe_route(const void* logits, int logits_dtype, int64_t ld, int64_t T, int E, int top_k, int renormalize,
+                     float* topk_w, int32_t* topk_ids, void* stream) {
+    if (T < 0 || E <= 0 || E > 1024 || top_k <= 0 || top_k > 32 || top_k > E || ld < E)
+        return fail(FP8LIN_ERR_SHAPE, "bad router shape T=%lld E=%d top_k=%d ld=%lld (E <= 1024, top_k <= 32)",
+                    (long long)T, E, top_k, (long long)ld);
+    if (logits_dtype != 0 && logits_dtype != 1) return fail(FP8LIN_ERR_ARG, "logits_dtype must be 0 (f32) or 1 (bf16)");
+    if (T == 0) return FP8LIN_OK;
+    if (!logits || !topk_w || !topk_ids) return fail(FP8LIN_ERR_NULL, "logits, topk_w and topk_ids must not be NULL");
+    cudaError_t e = launch_moe_route(logits, logits_dtype, ld, (int)T, E, top_k, renormalize, topk_w, topk_ids, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "router launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+size_t fp8lin_moe_workspace_bytes(int64_t rows, int E, int64_t H, int64_t I) {
+    if (rows < 0 || E <= 0 || H <= 0 || I <= 0) return FP8LIN_WS_HEADER_BYTES;
+    return moe_ws_layout(rows, E, H, I).total;
+}
+
+int fp8lin_moe_experts_w8a8(const void* x, int64_t ldx, int x_div, const int32_t* ids, const float* topk_w, int64_t rows,
+                            const void* w13_packed, const float* w13_scale, const float* w13_input_scale,
+                            const void* w2_packed, const float* w2_scale, const float* w2_input_scale,
+                            int E, int64_t H, int64_t I, void* out_routed, int64_t ld_out,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+    if (rows < 0 || E <= 0 || E > 4096 || H <= 0 || I <= 0 || H % 16 != 0 || I % 16 != 0 || x_div <= 0)
+        return fail(FP8LIN_ERR_SHAPE, "bad MoE shape rows=%lld E=%d H=%lld I=%lld (H, I multiples of 16)", (long long)rows, E,
+                    (long long)H, (long long)I);
+    if (rows == 0) return FP8LIN_OK;
+    if (rows > (1ll << 24)) return fail(FP8LIN_ERR_SHAPE, "too many routed rows");
+    if (!x || !ids || !topk_w || !w13_packed || !w13_scale || !w13_input_scale || !w2_packed || !w2_scale ||
+        !w2_input_scale || !out_routed)
+        return fail(FP8LIN_ERR_NULL, "a required MoE pointer is NULL");
+    if (ldx < H || ldx % 8 != 0 || ld_out < H || !aligned16(x) || !aligned16(w13_packed) || !aligned16(w2_packed))
+        return fail(FP8LIN_ERR_ALIGN, "x / packed weights must be 16-byte aligned, ldx a multiple of 8, ldx and ld_out >= H");
+    if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
+    const MoeWs L = moe_ws_layout(rows, E, H, I);
+    if (!workspace || workspace_bytes < L.total)
+        return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes", L.total);
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned char* ws = (unsigned char*)workspace;
+    int* offsets = (int*)(ws + L.off_offsets);
+    int* sorted = (int*)(ws + L.off_sorted);
+    int4* chunks = (int4*)(ws + L.off_chunks);
+    int* meta = (int*)(ws + L.off_meta);
+    __nv_bfloat16* gu = (__nv_bfloat16*)(ws + L.off_gu);
+    unsigned char* hq = ws + L.off_hq;
+    const int mp = grouped_chunk_rows(rows, E);
+    cudaError_t e = launch_moe_align(ids, (int)rows, E, mp, offsets, sorted, chunks, meta, st);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "row grouping launch: %s", cudaGetErrorString(e));
+    const char* why = nullptr;
+    GroupedArgs a;
+    a.x = (const __nv_bfloat16*)x; a.sorted_rows = sorted; a.chunks = chunks; a.meta = meta; a.w_scale = w13_scale;
+    a.input_scale = w13_input_scale; a.topk_w = topk_w; a.out = gu; a.status = (int*)workspace;
+    a.ldx = (int)ldx; a.x_div = x_div; a.ld_out = (int)(2 * I); a.N = (int)(2 * I); a.K = (int)H; a.n_tiles = 0; a.kblocks = 0;
+    e = launch_grouped_w8a8(true, mp, a, w13_packed, E, nullptr, 0, st, &why);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "gate_up grouped GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+    e = launch_silu_mul_quant(gu, w2_input_scale, hq, meta, (int)rows, (int)I, st);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation launch: %s", cudaGetErrorString(e));
+    a.w_scale = w2_scale; a.input_scale = w2_input_scale; a.out = (__nv_bfloat16*)out_routed; a.ld_out = (int)ld_out;
+    a.N = (int)H; a.K = (int)I;
+    e = launch_grouped_w8a8(false, mp, a, w2_packed, E, hq, rows, st, &why);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "down grouped GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+    return FP8LIN_OK;
+}
+
+int fp8lin_moe_combine(const void* routed, void* y, int64_t T, int top_k, int64_t H, void* stream) {
+    if (T < 0 || top_k <= 0 || H <= 0 || H % 8 != 0) return fail(FP8LIN_ERR_SHAPE, "bad combine shape");
+    if (T == 0) return FP8LIN_OK;
+    if (!routed || !y) return fail(FP8LIN_ERR_NULL, "routed and y must not be NULL");
+    if (!aligned16(routed) || !aligned16(y)) return fail(FP8LIN_ERR_ALIGN, "routed and y must be 16-byte aligned");
+    cudaError_t e = launch_moe_combine((const __nv_bfloat16*)routed, (__nv_bfloat16*)y, (int)T, top_k, (int)H, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "combine launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
 int fp8lin_read_status(void* workspace, void* stream, int* status_out) {
     if (!workspace || !status_out) return fail(FP8LIN_ERR_NULL, "workspace and status_out must not be NULL");
     cudaStream_t st = (cudaStream_t)stream;

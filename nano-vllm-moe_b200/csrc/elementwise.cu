@@ -10,6 +10,8 @@ namespace fp8lin {
 __global__ void __launch_bounds__(256)
 act_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ input_scale,
                  unsigned char* __restrict__ xq, int64_t M, int64_t K) {
+    pdl_launch_dependents();       // the GEMM behind this pass may set up and prefetch its weights now
+    pdl_wait();                    // x may come from the kernel before
     const ExactDiv s(fmaxf(__ldg(input_scale), 1e-12f));
     const int64_t vec_per_row = K / 16;
     const int64_t total = M * vec_per_row;
@@ -33,8 +35,14 @@ cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* i
     int64_t blocks = (total + 255) / 256;
     const int64_t cap = 148 * 16;
     if (blocks > cap) blocks = cap;
-    act_quant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, input_scale, xq, M, K);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.numAttrs = pdl_attribute(attr);
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, act_quant_kernel, x, ldx, input_scale, xq, M, K);
 }
 
 // Pack e4m3 weight bytes into the tiled layout (see pack_offset).  One CTA fills one

@@ -94,4 +94,30 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits);
 cudaError_t launch_swap_w8a8(const SwapPlan& plan, const UmmaArgs& a, const void* x, int64_t ldx,
                              cudaStream_t stream, const char** why);
 
+// ---- MoE expert FFN (moe_kernels.cu, umma_grouped.cu) ------------------------------
+cudaError_t launch_moe_route(const void* logits, int logits_bf16, int64_t ld, int T, int E, int top_k, int renormalize,
+                             float* out_w, int* out_ids, cudaStream_t stream);
+cudaError_t launch_moe_align(const int* ids, int rows, int E, int chunk_rows, int* expert_offsets, int* sorted_rows,
+                             int4* chunks, int* meta, cudaStream_t stream);
+cudaError_t launch_silu_mul_quant(const __nv_bfloat16* gu, const float* input_scale, unsigned char* hq, const int* meta,
+                                  int max_rows, int I, cudaStream_t stream);
+cudaError_t launch_moe_combine(const __nv_bfloat16* routed, __nv_bfloat16* y, int T, int top_k, int H, cudaStream_t stream);
+
+struct GroupedArgs {
+    const __nv_bfloat16* x;      // gather flavour: token matrix [x_rows][ldx]
+    const int* sorted_rows;      // routed-row index per sorted position
+    const int4* chunks;          // {expert, first sorted position, rows, 0}
+    const int* meta;             // meta[0] = number of chunks
+    const float* w_scale;        // [E][N]
+    const float* input_scale;    // one float
+    const float* topk_w;         // [routed rows] (down flavour)
+    __nv_bfloat16* out;          // gather: [sorted rows][ld_out]; down: [routed rows][ld_out]
+    int* status;
+    int ldx, x_div, ld_out;
+    int N, K, n_tiles, kblocks;
+};
+int grouped_chunk_rows(int64_t rows, int num_experts);
+cudaError_t launch_grouped_w8a8(bool gather, int mp, GroupedArgs a, const void* w_packed, int num_experts,
+                                const void* xq_sorted, int64_t xq_rows, cudaStream_t stream, const char** why);
+
 }  // namespace fp8lin

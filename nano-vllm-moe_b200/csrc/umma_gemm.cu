@@ -32,6 +32,9 @@
 // Every mbarrier wait is bounded: a barrier that does not flip within about a
 // second records a status code in the caller's scratch header and the CTA
 // unwinds (drains its ring, frees TMEM) instead of hanging the GPU.
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "umma_common.cuh"
 
 namespace fp8lin {
@@ -124,6 +127,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -132,12 +136,32 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
             uint32_t it = 0;
             bool ok = true;
+            bool waited = false;      // weight tiles of the first ring pass go out before the predecessor is done
             for (int w = first_work; w < sched.total_work && ok; w += work_step) {
                 int tm, tn;
                 decode_tile(sched, w, tm, tn);
                 const int kb0 = split_rank * sched.kblocks_per_split;
                 const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                if (!waited) {
+                    const int first_kb = min(kb1 - kb0, S);
+                    for (int i = 0; i < first_kb; ++i) {
+                        const uint32_t full = smem_u32(&bar_full[i]);
+                        mbar_expect_tx(full, Cfg::kStageBytes);
+#pragma unroll
+                        for (int sub = 0; sub < (BN + 127) / 128; ++sub) {
+                            const int n_sub = tn * BN + sub * 128;
+                            const int wrow = ((n_sub >> 7) * sched.kblocks_total + kb0 + i) * 128 + (n_sub & 127);
+                            tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kABytes + sub * 128 * kBK, &tmap_b, 0, wrow, full);
+                        }
+                    }
+                    pdl_wait();       // the quantised activations are written by the kernel before this one
+                    for (int i = 0; i < first_kb; ++i)
+                        tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_a, (kb0 + i) * kBK, tm * kBM, smem_u32(&bar_full[i]));
+                    waited = true;
+                    it = (uint32_t)first_kb;
+                    if (kb0 + first_kb >= kb1) continue;
+                }
+                for (int kb = kb0 + (w == first_work ? min(kb1 - kb0, S) : 0); kb < kb1; ++kb, ++it) {
                     const int st = it % S;
                     const uint32_t ph = (it / S) & 1;
                     if (s_abort || !mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1, p.status, kDevTimeoutEmpty)) {
@@ -203,6 +227,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
         // ================= epilogue (warps 2..9) =================
         // Warp (q, h): TMEM lanes [32q, 32q+32) = 32 rows of the tile, column half h.
+        pdl_wait();                                            // y may still be in use by the predecessor
         const int ew = warp - 2;
         const int q = warp & 3;
         const int h = ew >> 2;
@@ -287,6 +312,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (kSplit) {
         // ---- cluster reduction: CTA r sums rows [r*band, (r+1)*band) of the tile over all K slices ----
         __syncwarp();
+        pdl_wait();
         cluster_sync_all();                                   // every CTA's parked tile is visible
         int tm, tn;
         decode_tile(sched, first_work, tm, tn);
@@ -332,6 +358,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 int max_active_clusters(const void* kernel, int threads, size_t smem_bytes, int cluster) {
     static const int fallback[9] = {148, 148, 74, 48, 32, 24, 24, 16, 16};
     if (cluster < 1 || cluster > 8) return 0;
+    (void)threads;
     struct Entry { const void* k; int c; int n; };
     static Entry cache[64];
     static int used = 0;
@@ -353,8 +380,12 @@ int max_active_clusters(const void* kernel, int threads, size_t smem_bytes, int 
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int q = 0;
-        if (cudaOccupancyMaxActiveClusters(&q, kernel, &cfg) == cudaSuccess && q > 0) n = q;
+        cudaError_t qe = cudaOccupancyMaxActiveClusters(&q, kernel, &cfg);
+        if (qe == cudaSuccess && q > 0) n = q;
         else cudaGetLastError();
+        if (getenv("FP8LIN_DEBUG"))
+            fprintf(stderr, "[fp8lin] max active clusters: size %d smem %zu threads %d -> %d (%s)\n", cluster, smem_bytes,
+                    threads, q, cudaGetErrorString(qe));
     } else {
         cudaGetLastError();
         return n;            // no device: do not cache, a later call may have one
@@ -473,15 +504,17 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    int na = pdl_attribute(attr);
     if (kSplit) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)pl.splits;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)pl.splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
     }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s);
 }
 

@@ -41,7 +41,10 @@ struct SwapCfg {
     static constexpr int kXqBytes = MP * kKB;                    // quantised activation tile (MMA B)
     static constexpr int kXrawBytes = MP * kKB * 2;              // raw bf16 activation block
     static constexpr int kStageBytes = kWBytes + kXqBytes + kXrawBytes;
-    static constexpr int kStages = MP <= 16 ? 9 : (MP <= 32 ? 7 : 5);
+    // M <= 16: two CTAs share an SM (5 stages each, 160 KB of weights in flight per SM), so the
+    // CTAs of the next kernel can start on an SM while this kernel's other CTA is still draining
+    static constexpr int kCtasPerSm = MP <= 16 ? 2 : 1;
+    static constexpr int kStages = MP <= 16 ? 5 : (MP <= 32 ? 7 : 5);
     // converter warps that share one K block (more rows -> more warps per block)
     static constexpr int kTeam = MP <= 16 ? 1 : (MP <= 32 ? 2 : 4);
     static constexpr int kRingBytes = kStages * kStageBytes;
@@ -75,7 +78,7 @@ __device__ __forceinline__ void tmem_ld_cols<64>(uint32_t taddr, uint32_t* v) {
 }
 
 template <int MP, bool kSplit>
-__global__ void __launch_bounds__(kSwapThreads, 1)
+__global__ void __launch_bounds__(kSwapThreads, SwapCfg<MP>::kCtasPerSm)
 swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  UmmaArgs p, SwapSched sched) {
     using Cfg = SwapCfg<MP>;
@@ -356,17 +359,22 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits) {
         if (force_splits <= 0 && s > 1 && kblocks / s < 4) break;          // at least four K blocks per slice
         const int kps = (kblocks + s - 1) / s;
         if ((kblocks + kps - 1) / kps != s) continue;                        // would leave an empty slice
-        int slots = 148;
+        int slots = 148 * (pl.mp == 16 ? 2 : 1);
         if (s > 1) slots = pl.mp == 16 ? swap_max_clusters<16>(s) : (pl.mp == 32 ? swap_max_clusters<32>(s) : swap_max_clusters<64>(s));
         if (slots < 1) slots = 1;
-        const int waves = (pl.n_tiles + slots - 1) / slots;
+        // with two CTAs per SM a second wave of clusters trickles in as slots free up, so a
+        // fractional wave count models it better than a ceiling (measured on 18944 -> 3584)
+        double waves = (double)pl.n_tiles / slots;
+        if (pl.mp != 16) waves = (pl.n_tiles + slots - 1) / slots;
+        if (waves < 1.0) waves = 1.0;
         // K blocks per CTA plus a fixed cost (launch, first loads, epilogue; cluster reduction when split)
-        const double cost = waves * (kps + (s > 1 ? 8.0 : 6.0));
+        const double cost = waves * kps + (s > 1 ? 8.0 : 6.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
     pl.splits = best_s;
     pl.kblocks_per_split = (kblocks + best_s - 1) / best_s;
-    pl.grid = pl.splits > 1 ? pl.n_tiles * pl.splits : (pl.n_tiles < 148 ? pl.n_tiles : 148);
+    const int resident = 148 * (pl.mp == 16 ? 2 : 1);
+    pl.grid = pl.splits > 1 ? pl.n_tiles * pl.splits : (pl.n_tiles < resident ? pl.n_tiles : resident);
     return pl;
 }
 
