@@ -52,6 +52,10 @@ for _m in (4096, 16384, 32640):
     WORKLOADS[f"c4_m{_m}"] = ("fp8_w8a8_static", [("qkv", _m, 3584, 4608, "col"), ("o_proj", _m, 3584, 3584, "row"),
                                                   ("gate_up", _m, 3584, 37888, "col"), ("down", _m, 18944, 3584, "row")])
 
+for _t in (1, 64, 1024, 4096):
+    WORKLOADS[f"c5_t{_t}"] = ("moe_w8a8", _t)
+MOE = {"hidden": 2048, "experts": 60, "inter": 1408, "top_k": 4}
+
 L2_BYTES = 126 * 1024 * 1024
 SEED = 20260519
 
@@ -190,6 +194,181 @@ def run_reference_arm(args, scheme, ops, flops):
     print(json.dumps(line))
 
 
+# --------------------------------------------------------------------------- MoE expert FFN (config 5)
+def make_expert_weights(E, H, I, seed, device):
+    qs13, ss13, qs2, ss2 = [], [], [], []
+    for e in range(E):
+        q, s = make_weights(H, 2 * I, seed + 2 * e, device); qs13.append(q); ss13.append(s)
+        q, s = make_weights(I, H, seed + 2 * e + 1, device); qs2.append(q); ss2.append(s)
+    return torch.stack(qs13), torch.stack(ss13), torch.stack(qs2), torch.stack(ss2)
+
+
+def bench_moe(args, T):
+    """One step = router + dispatch + expert FFN (gate_up, silu*mul, down) + combine for T tokens,
+    hidden 2048, 60 experts, intermediate 1408, top-4 softmax routing without renormalisation.
+    With N > 1 ranks the experts are split over the ranks (expert parallel) and every rank brings
+    T tokens of its own (weak scaling); rows travel by NCCL all-to-all."""
+    import torch.distributed as dist
+    H, E, I, K = MOE["hidden"], MOE["experts"], MOE["inter"], MOE["top_k"]
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    flops_rank = T * K * 6 * H * I
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        from oracle import torch_ref
+        torch.set_num_threads(os.cpu_count() or 1)
+        g = torch.Generator().manual_seed(SEED)
+        ts = min(T, 256)                       # bounded sample: at most 256 tokens, scaled linearly
+        x = torch.randn((ts, H), generator=g).to(torch.bfloat16)
+        logits = torch.randn((ts, E), generator=g)
+        w13 = (torch.randn((E, 2 * I, H), generator=g) * 0.02).to(torch.bfloat16)
+        w2 = (torch.randn((E, H, I), generator=g) * 0.02).to(torch.bfloat16)
+        wts, ids = torch.topk(torch.softmax(logits, dim=-1, dtype=torch.float32), K, dim=-1)
+        times = []
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter(); torch_ref.eager_experts(x, ids, wts, w13, w2); dt = time.perf_counter() - t0
+            if i >= args.warmup:
+                times.append(dt)
+            if sum(times) > 100:
+                break
+        sec = sum(times) / len(times) * (T / ts)
+        val = flops_rank / sec / 1e12
+        print(json.dumps({"impl": "reference", "metric": "fp8_linear_throughput", "value": val, "unit": "TFLOP/s",
+                          "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": sec * 1e3,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                          "dtype": "bf16 (cpu eager experts)", "data": "synthetic",
+                          "config": {"workload": args.workload, "tokens": T, **MOE},
+                          "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                           "sample": f"{ts} of {T} tokens per pass, time scaled linearly"},
+                          "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        if E % world:
+            if rank == 0:
+                print(json.dumps({"metric": "fp8_linear_throughput", "unavailable":
+                                  f"{E} experts do not divide over {world} ranks (the reference rejects it too)"}))
+            dist.destroy_process_group()
+            return
+    moe = importlib.import_module("nano-vllm-moe_b200.executor.moe")
+    Kn = importlib.import_module("nano-vllm-moe_b200.quantization.kernels")
+    peaks = load_peaks()
+    cfg = moe.make_moe_parallel_config(tp_group=None, ep_group=dist.group.WORLD if world > 1 else None,
+                                       global_num_experts=E, intermediate_size=I)
+    el = cfg.local_num_experts
+    q13, s13, q2, s2 = make_expert_weights(el, H, I, SEED + 7919 * rank, dev)
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    calib = torch.randn((4096, H), generator=g, device=dev).to(torch.bfloat16)
+    in13 = (calib.float().abs().amax() / 448.0).reshape(())
+    wts = moe.Fp8ExpertWeights.from_checkpoint_layout(q13, s13, in13, q2, s2, torch.tensor(4.0 / 448.0))
+    del q13, q2
+    pf = moe.TorchAllToAllPrepareFinalize(cfg) if world > 1 else moe.NoEPPrepareFinalize(cfg)
+    kern = moe.MoEKernel(prepare_finalize=pf, experts=moe.Fp8Experts(), parallel_config=cfg)
+    router = moe.SoftmaxTopKRouter(K, False)
+    sets = 8   # inputs are cycled so that small batches do not keep hitting the same L2-resident experts
+    xs = [torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16) for _ in range(sets)]
+    logits = [torch.randn((T, E), generator=g, device=dev) for _ in range(sets)]
+
+    def run(i, x=None):
+        w, ids = router.select_experts(None, logits[i % sets])
+        return kern(xs[i % sets] if x is None else x, w, ids, wts, model_dtype=torch.bfloat16)
+
+    for i in range(sets):
+        run(i)
+    torch.cuda.synchronize()
+    graphs, use_graph = [], (world == 1 and not args.no_graph)
+    if use_graph:
+        side = torch.cuda.Stream(dev)
+        with torch.cuda.stream(side):
+            run(0); torch.cuda.synchronize()
+            for i in range(sets):
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph, stream=side):
+                    run(i)
+                graphs.append(gph)
+
+    def step(i):
+        graphs[i % sets].replay() if use_graph else run(i)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        t_wait = time.time()
+        while sampler.mark() == 0 and time.time() - t_wait < 3.0:
+            step(0); torch.cuda.synchronize()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    mark0 = sampler.mark()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop(mark0, sampler.mark()) if rank == 0 else None
+    # end to end with host buffers
+    hx = [x.cpu().pin_memory() for x in xs]
+    hy = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    dx = torch.empty_like(xs[0])
+    def e2e_step(i):
+        dx.copy_(hx[i % sets], non_blocking=True)
+        hy.copy_(run(i, dx), non_blocking=True)
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(10, min(args.steps, 50))
+    a.record()
+    for i in range(n_e2e):
+        e2e_step(i)
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b) / n_e2e
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    flops = flops_rank * world
+    by = min(E, T * K * world) * 3 * H * I + world * T * K * (H * 2 + 2 * I * 2 + I * 2 + H * 2)
+    t_hbm = by / world / (peaks["hbm_gbs"] * 1e9)
+    t_tc = flops_rank / (2 * peaks["bf16_tflops"] * 1e12)
+    bound = "hbm" if t_hbm >= t_tc else "tensor"
+    ach = by / (ms * 1e-3) / 1e9 / world if bound == "hbm" else flops_rank / (ms * 1e-3) / 1e12
+    peak = peaks["hbm_gbs"] if bound == "hbm" else 2 * peaks["bf16_tflops"]
+    status = Kn.read_status(dev)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "fp8_linear_throughput", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 -> bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens_per_rank": T, **MOE, "parallelism": f"ep{world}" if world > 1 else "single",
+                       "l2": f"expert weights {el * 3 * H * I / 1e6:.0f} MB per rank > 126 MB L2; inputs cycled over {sets} sets",
+                       "launch": "cuda-graph replay" if use_graph else "eager"},
+            "clocks": clocks,
+            "shapes": [{"layer": "moe_ffn", "tokens": T, "us": ms * 1e3, "tflops": flops_rank / (ms * 1e-3) / 1e12,
+                        "gbs": by / world / (ms * 1e-3) / 1e9, "bound": bound, "frac": ach / peak}],
+            "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+                         "frac": ach / peak, "traffic": None, "kernel": "grouped_w8a8_kernel (gate_up + down)",
+                         "peak_source": f"{peaks['source']}"},
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
+            "gpu_launches": 6 * args.steps, "device_status": status}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------- our arm
 def main():
     ap = argparse.ArgumentParser()
@@ -203,6 +382,8 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
+    if args.workload.startswith("c5"):
+        return bench_moe(args, WORKLOADS[args.workload][1])
     scheme, ops = WORKLOADS[args.workload]
     flops = sum(2 * m * k * n for _, m, k, n, _ in ops)
     if args.impl == "reference":

@@ -251,8 +251,11 @@ int fp8lin_set_tuning(const char* knob, int value) {
 
 // ---- MoE -------------------------------------------------------------------------------------
 namespace {
+// from this many routed rows on, the rows are gathered and quantised once by a separate pass
+// instead of inside the gate_up GEMM (where every channel tile would redo it)
+constexpr int64_t kMoePrequantRows = 512;
 struct MoeWs {
-    size_t off_offsets, off_sorted, off_chunks, off_meta, off_gu, off_hq, total;
+    size_t off_offsets, off_sorted, off_chunks, off_meta, off_gu, off_hq, off_xq, total;
 };
 MoeWs moe_ws_layout(int64_t rows, int E, int64_t H, int64_t I) {
     MoeWs w;
@@ -264,8 +267,8 @@ MoeWs moe_ws_layout(int64_t rows, int E, int64_t H, int64_t I) {
     w.off_meta = take(16);
     w.off_gu = take((size_t)rows * 2 * I * 2);
     w.off_hq = take((size_t)rows * I);
+    w.off_xq = take(rows >= kMoePrequantRows ? (size_t)rows * H : 0);
     w.total = o;
-    (void)H;
     return w;
 }
 }  // namespace
@@ -323,12 +326,20 @@ int fp8lin_moe_experts_w8a8(const void* x, int64_t ldx, int x_div, const int32_t
     a.x = (const __nv_bfloat16*)x; a.sorted_rows = sorted; a.chunks = chunks; a.meta = meta; a.w_scale = w13_scale;
     a.input_scale = w13_input_scale; a.topk_w = topk_w; a.out = gu; a.status = (int*)workspace;
     a.ldx = (int)ldx; a.x_div = x_div; a.ld_out = (int)(2 * I); a.N = (int)(2 * I); a.K = (int)H; a.n_tiles = 0; a.kblocks = 0;
-    e = launch_grouped_w8a8(true, mp, a, w13_packed, E, nullptr, 0, st, &why);
+    a.scatter = 0;
+    if (rows >= kMoePrequantRows) {
+        unsigned char* xq = ws + L.off_xq;
+        e = launch_moe_gather_quant((const __nv_bfloat16*)x, ldx, x_div, sorted, meta, w13_input_scale, xq, (int)rows, (int)H, st);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "row gather launch: %s", cudaGetErrorString(e));
+        e = launch_grouped_w8a8(false, mp, a, w13_packed, E, xq, rows, st, &why);
+    } else {
+        e = launch_grouped_w8a8(true, mp, a, w13_packed, E, nullptr, 0, st, &why);
+    }
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "gate_up grouped GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     e = launch_silu_mul_quant(gu, w2_input_scale, hq, meta, (int)rows, (int)I, st);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation launch: %s", cudaGetErrorString(e));
     a.w_scale = w2_scale; a.input_scale = w2_input_scale; a.out = (__nv_bfloat16*)out_routed; a.ld_out = (int)ld_out;
-    a.N = (int)H; a.K = (int)I;
+    a.N = (int)H; a.K = (int)I; a.scatter = 1;
     e = launch_grouped_w8a8(false, mp, a, w2_packed, E, hq, rows, st, &why);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "down grouped GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     return FP8LIN_OK;

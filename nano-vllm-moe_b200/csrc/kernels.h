@@ -99,6 +99,8 @@ cudaError_t launch_moe_route(const void* logits, int logits_bf16, int64_t ld, in
                              float* out_w, int* out_ids, cudaStream_t stream);
 cudaError_t launch_moe_align(const int* ids, int rows, int E, int chunk_rows, int* expert_offsets, int* sorted_rows,
                              int4* chunks, int* meta, cudaStream_t stream);
+cudaError_t launch_moe_gather_quant(const __nv_bfloat16* x, int64_t ldx, int x_div, const int* sorted_rows, const int* meta,
+                                    const float* input_scale, unsigned char* xq, int max_rows, int H, cudaStream_t stream);
 cudaError_t launch_silu_mul_quant(const __nv_bfloat16* gu, const float* input_scale, unsigned char* hq, const int* meta,
                                   int max_rows, int I, cudaStream_t stream);
 cudaError_t launch_moe_combine(const __nv_bfloat16* routed, __nv_bfloat16* y, int T, int top_k, int H, cudaStream_t stream);
@@ -111,7 +113,8 @@ struct GroupedArgs {
     const float* w_scale;        // [E][N]
     const float* input_scale;    // one float
     const float* topk_w;         // [routed rows] (down flavour)
-    __nv_bfloat16* out;          // gather: [sorted rows][ld_out]; down: [routed rows][ld_out]
+    __nv_bfloat16* out;          // gate_up: [sorted rows][ld_out]; down: [routed rows][ld_out]
+    int scatter;                 // 1 = down flavour: multiply by topk_w and scatter to routed-row order
     int* status;
     int ldx, x_div, ld_out;
     int N, K, n_tiles, kblocks;

@@ -137,6 +137,39 @@ cudaError_t launch_moe_align(const int* ids, int rows, int E, int chunk_rows, in
 // (Within an expert the rows land in the arrival order of the atomics.  Every routed row is an
 // independent column of the grouped GEMM, so the order does not change a single output bit.)
 
+// ---- gather + quantise the routed rows once (prefill-sized batches) --------------------------
+// xq[pos][:] = e4m3(x[sorted_rows[pos] / x_div][:] / scale) for every sorted position; the grouped
+// GEMM then takes its "B" tiles by TMA instead of re-quantising the rows for every channel tile.
+__global__ void __launch_bounds__(256)
+moe_gather_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int x_div, const int* __restrict__ sorted_rows,
+                        const int* __restrict__ meta, const float* __restrict__ input_scale,
+                        unsigned char* __restrict__ xq, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int rows = meta[1];
+    const ExactDiv div_scale(fmaxf(__ldg(input_scale), 1e-12f));
+    const int vec_per_row = H / 16;
+    const int64_t total = (int64_t)rows * vec_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t pos = i / vec_per_row;
+        const int c = (int)(i - pos * vec_per_row) * 16;
+        const int src_row = __ldg(sorted_rows + pos) / x_div;
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)src_row * ldx + c);
+        const uint2 qa = quant8_e4m3(__ldg(src), div_scale);
+        const uint2 qb = quant8_e4m3(__ldg(src + 1), div_scale);
+        *reinterpret_cast<uint4*>(xq + pos * H + c) = make_uint4(qa.x, qa.y, qb.x, qb.y);
+    }
+}
+
+cudaError_t launch_moe_gather_quant(const __nv_bfloat16* x, int64_t ldx, int x_div, const int* sorted_rows, const int* meta,
+                                    const float* input_scale, unsigned char* xq, int max_rows, int H, cudaStream_t stream) {
+    int64_t blocks = ((int64_t)max_rows * (H / 16) + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    moe_gather_quant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, x_div, sorted_rows, meta, input_scale, xq, H);
+    return cudaGetLastError();
+}
+
 // ---- h = silu(gate) * up, quantised for the down projection ----------------------------------
 // gu: bf16 [rows][2I] (gate | up), hq: e4m3 [rows][I].  h is rounded to bf16 first (it is the
 // tensor the reference materialises), then divided by the static scale.

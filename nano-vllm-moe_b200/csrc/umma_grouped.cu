@@ -8,14 +8,15 @@
 // the chunk list moe_align_kernel leaves in device memory, so no host synchronisation is needed;
 // the grid is persistent (one CTA per SM) and every CTA strides over the items.
 //
-// Two flavours:
-//   kGather = true  (gate_up projection): the rows are gathered from the bf16 token matrix
-//       through the sorted row index and quantised on the fly (static scale, exact division)
-//       by converter warps straight into the swizzled MMA "B" tile.  Epilogue writes
-//       gu[sorted position][channel] = bf16(acc * in_scale * w_scale[e][channel]).
-//   kGather = false (down projection): the rows are already e4m3 and contiguous in sorted
-//       order, so the "B" tile is one TMA box.  Epilogue multiplies by the routing weight and
-//       scatters to routed-row order: out[routed row][channel] = bf16(acc*in_scale*w_scale*topk_w).
+// Source of the rows (template flag kGather):
+//   true   decode-sized batches of the gate_up projection: the rows are gathered from the bf16
+//          token matrix through the sorted row index and quantised on the fly (static scale,
+//          exact division) by converter warps straight into the swizzled MMA "B" tile.
+//   false  the rows are already e4m3 and contiguous in sorted order (down projection always;
+//          gate_up after moe_gather_quant_kernel for prefill-sized batches): one TMA box.
+// Epilogue (run-time flag `scatter`):
+//   0      gu[sorted position][channel] = bf16(acc * in_scale * w_scale[e][channel])
+//   1      out[routed row][channel] = bf16(acc * in_scale * w_scale[e][channel] * topk_w[routed row])
 //
 // Weight-bandwidth-bound for small batches (each expert's weights are read once per chunk),
 // tensor-bound for prefill-sized batches.  All mbarrier waits are bounded.
@@ -199,6 +200,19 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             const uint32_t aph = (tl >> 1) & 1;
             const int n = t * kGrpTile + q * 32 + lane;                         // output channel of this lane
             const float ws = n < p.N ? in_scale * __ldg(p.w_scale + (size_t)ch.x * p.N + n) : 0.f;
+            // routed-row index and routing weight of the chunk's rows, one row per lane and piece;
+            // the inner loop gets them by shuffle instead of two dependent global loads per row
+            int my_routed[(MP + 31) / 32];
+            float my_w[(MP + 31) / 32];
+#pragma unroll
+            for (int i = 0; i < (MP + 31) / 32; ++i) {
+                const int r = i * 32 + lane;
+                my_routed[i] = 0; my_w[i] = 0.f;
+                if (p.scatter && r < ch.z) {
+                    my_routed[i] = __ldg(p.sorted_rows + ch.y + r);
+                    my_w[i] = __ldg(p.topk_w + my_routed[i]);
+                }
+            }
             if (!mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
             tc_fence_after();
             const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * MP;
@@ -216,18 +230,15 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                         : "r"(t_addr + c0) : "memory");
                 }
                 tmem_ld_wait();
-                if (n < p.N) {
 #pragma unroll
-                    for (int j = 0; j < Cfg::kPiece; ++j) {
-                        const int r = c0 + j;
-                        if (r >= ch.z) break;
+                for (int j = 0; j < Cfg::kPiece; ++j) {
+                    const int r = c0 + j;                                       // uniform across the warp
+                    const int routed = __shfl_sync(0xffffffffu, my_routed[(c0 + j) / 32], (c0 + j) & 31);
+                    const float rw = __shfl_sync(0xffffffffu, my_w[(c0 + j) / 32], (c0 + j) & 31);
+                    if (r < ch.z && n < p.N) {
                         const float acc = __uint_as_float(v[j]) * ws;
-                        if (kGather) {
-                            p.out[(size_t)(ch.y + r) * p.ld_out + n] = __float2bfloat16_rn(acc);
-                        } else {
-                            const int routed = __ldg(p.sorted_rows + ch.y + r);
-                            p.out[(size_t)routed * p.ld_out + n] = __float2bfloat16_rn(acc * __ldg(p.topk_w + routed));
-                        }
+                        if (!p.scatter) p.out[(size_t)(ch.y + r) * p.ld_out + n] = __float2bfloat16_rn(acc);
+                        else p.out[(size_t)routed * p.ld_out + n] = __float2bfloat16_rn(acc * rw);
                     }
                 }
             }

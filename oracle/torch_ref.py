@@ -41,3 +41,22 @@ def time_passes(tensors, steps: int, warmup: int, budget_s: float) -> tuple[list
         if time.perf_counter() - t_start > budget_s:
             break
     return out, torch.get_num_threads()
+
+
+def eager_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """The reference's expert FFN as it runs it (bf16 dense experts, one python loop over experts;
+    nanovllm/executor/moe/experts/eager_experts.py:26-35 + prepare_finalize/no_ep.py:19-45), on CPU.
+    x [T,H] bf16; topk_ids/topk_w [T,k]; w13 [E,2I,H] bf16; w2 [E,H,I] bf16 -> [T,H] bf16."""
+    import torch.nn.functional as F
+    t, k = topk_ids.shape
+    xe = x.repeat_interleave(k, dim=0)
+    ids = topk_ids.reshape(-1)
+    w = topk_w.reshape(-1)
+    out = torch.zeros(xe.shape[0], w2.shape[1], dtype=x.dtype)
+    for e in range(w13.shape[0]):
+        idx = torch.nonzero(ids == e, as_tuple=False).flatten()
+        if idx.numel() == 0:
+            continue
+        gate, up = F.linear(xe[idx], w13[e]).chunk(2, dim=-1)
+        out[idx] = F.linear(F.silu(gate) * up, w2[e]) * w[idx, None].to(x.dtype)
+    return out.view(t, k, -1).sum(dim=1)
