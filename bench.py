@@ -248,7 +248,8 @@ def bench_moe(args, T):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=120))
         if E % world:
             if rank == 0:
                 print(json.dumps({"metric": "fp8_linear_throughput", "unavailable":
@@ -303,9 +304,12 @@ def bench_moe(args, T):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    if world == 1:
         t_wait = time.time()
         while sampler.mark() == 0 and time.time() - t_wait < 3.0:
             step(0); torch.cuda.synchronize()
+    else:
+        time.sleep(1.0)      # every rank must issue the same collectives: no rank-0-only steps here
     for i in range(args.warmup):
         step(i)
     barrier()
@@ -364,9 +368,12 @@ def bench_moe(args, T):
                          "peak_source": f"{peaks['source']}"},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
-            "gpu_launches": 6 * args.steps, "device_status": status}))
+            "gpu_launches": 6 * args.steps, "device_status": status}), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 # --------------------------------------------------------------------------- our arm
@@ -400,7 +407,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=120))
     tp = world
 
     pkg = importlib.import_module("nano-vllm-moe_b200")
@@ -486,10 +494,13 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    if world == 1:
         t_wait = time.time()
         while sampler.mark() == 0 and time.time() - t_wait < 3.0:   # nvidia-smi takes a moment to start
             step(0)
             torch.cuda.synchronize()
+    else:
+        time.sleep(1.0)      # every rank must issue the same collectives: no rank-0-only steps here
     for i in range(args.warmup):
         step(i)
     barrier()
@@ -628,9 +639,15 @@ def main():
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # captured graphs hold NCCL work; drop them before the process group goes away, and do not
+        # let a slow communicator teardown keep the ranks alive after the line is out
+        graphs.clear()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

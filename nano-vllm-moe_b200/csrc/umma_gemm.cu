@@ -6,7 +6,7 @@
 //   warp 0      TMA producer: cp.async.bulk.tensor.2d loads of a 128 x 128-byte
 //               xq tile and a BN x 128-byte weight tile per K block into a
 //               multi-stage shared-memory ring (128-byte swizzle), signalled by
-//               mbarrier complete_tx.  No cluster multicast anywhere.
+//               mbarrier complete_tx; every CTA issues its own loads.
 //   warp 1      MMA issuer: one lane issues tcgen05.mma.cta_group::1
 //               .kind::f8f6f4 (M=128, N=BN, K=32) four times per K block,
 //               accumulating in TMEM; tcgen05.commit releases the ring slot
