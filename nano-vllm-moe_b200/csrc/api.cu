@@ -222,7 +222,8 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
     const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
     if (scheme == FP8LIN_W8A8_STATIC && M > max_m && N % 8 == 0) {
         UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
-        snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s%d", pl.bn, pl.splits);
+        if (pl.tail_tiles) snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s1+tail%dx%d", pl.bn, pl.tail_tiles, pl.tail_splits);
+        else snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s%d", pl.bn, pl.splits);
         return buf;
     }
     if (scheme == FP8LIN_W8A8_STATIC && swap_eligible(M)) {

@@ -72,6 +72,8 @@ struct UmmaPlan {
     int kblocks_per_split;
     int m_tiles, n_tiles;
     int grid;          // persistent CTAs
+    int tail_tiles;    // last tiles finished by a second, cluster split-K launch (0 = none)
+    int tail_splits, tail_kps;
     size_t partial_bytes;
 };
 

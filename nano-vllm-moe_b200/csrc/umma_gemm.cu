@@ -74,7 +74,8 @@ __host__ __device__ constexpr uint32_t make_idesc() {
 }
 
 struct UmmaSched {
-    int m_tiles, n_tiles, splits, kblocks_total, kblocks_per_split, total_work;
+    int m_tiles, n_tiles, splits, kblocks_total, kblocks_per_split;
+    int tile_base, total_work;      // this launch covers tiles [tile_base, total_work)
 };
 
 // tile index -> (tile_m, tile_n); 8 M-tiles share a weight column block before the next
@@ -112,7 +113,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     // In split mode a cluster shares one tile: tile = cluster id, K slice = rank in the cluster.
     const int split_rank = kSplit ? (int)cluster_ctarank() : 0;
-    const int first_work = kSplit ? (int)(blockIdx.x / sched.splits) : (int)blockIdx.x;
+    const int first_work = sched.tile_base + (kSplit ? (int)(blockIdx.x / sched.splits) : (int)blockIdx.x);
     const int work_step = kSplit ? sched.total_work : (int)gridDim.x;      // split mode: exactly one tile
 
     if (threadIdx.x == 0) {
@@ -471,8 +472,11 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
             if (slots < 1) slots = 1;
             waves = (tiles + slots - 1) / slots;
         }
+        double rounds = (double)waves;
+        if (splits == 1 && force_splits <= 0 && kblocks >= 64 && tiles > 148 && tiles % 148 != 0 && tiles % 148 <= 74)
+            rounds = (double)(tiles / 148) + 0.4;      // the last partial round goes to the split-K tail launch
         // main loop + fixed per-tile prologue/epilogue; split-K pays one cluster reduction
-        const double cost = waves * (kps * unit[i] + 3.0 * unit[i]) + (splits > 1 ? 2.0 : 0.0);
+        const double cost = rounds * (kps * unit[i] + 3.0 * unit[i]) + (splits > 1 ? 2.0 : 0.0);
         if (cost < best_cost) {
             best_cost = cost;
             best.bn = bn; best.splits = splits; best.kblocks_per_split = kps;
@@ -481,12 +485,36 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
             best.partial_bytes = 0;
         }
     }
+    // Wave quantisation: a persistent launch over q*148 + r tiles runs q + 1 rounds even when r is
+    // small.  Then the last r tiles go to a second, cluster split-K launch (r * s CTAs <= 148) that
+    // finishes them in about 1/s of a round.
+    best.tail_tiles = 0; best.tail_splits = 1; best.tail_kps = 0;
+    const long tiles = (long)best.m_tiles * best.n_tiles;
+    if (force_splits <= 0 && best.splits == 1 && tiles > 148 && kblocks >= 64) {   // a round must outlast a launch
+        const int r = (int)(tiles % 148);
+        if (r > 0 && r <= 74) {
+            int s = 148 / r;
+            if (s > 8) s = 8;
+            while (s > 1 && kblocks / s < 2) --s;
+            if (s > 1) {
+                const void* kern = best.bn == 256 ? (const void*)umma_w8a8_kernel<256, true>
+                                 : best.bn == 128 ? (const void*)umma_w8a8_kernel<128, true> : (const void*)umma_w8a8_kernel<64, true>;
+                const size_t smem = best.bn == 256 ? UmmaCfg<256>::kSmemBytes : best.bn == 128 ? UmmaCfg<128>::kSmemBytes : UmmaCfg<64>::kSmemBytes;
+                while (s > 1 && max_active_clusters(kern, kThreads, smem, s) < r) --s;
+            }
+            if (s > 1) {
+                const int kps = (kblocks + s - 1) / s;
+                best.tail_tiles = r; best.tail_kps = kps; best.tail_splits = (kblocks + kps - 1) / kps;
+            }
+        }
+    }
     return best;
 }
 
 template <int BN, bool kSplit>
 static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb,
-                             const CUtensorMap& ty, cudaStream_t stream) {
+                             const CUtensorMap& ty, cudaStream_t stream, int tile_base, int tile_end, int splits, int kps,
+                             int grid) {
     using Cfg = UmmaCfg<BN>;
     auto kern = umma_w8a8_kernel<BN, kSplit>;
     static bool configured = false;
@@ -496,11 +524,11 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
         configured = true;
     }
     UmmaSched s;
-    s.m_tiles = pl.m_tiles; s.n_tiles = pl.n_tiles; s.splits = pl.splits;
-    s.kblocks_total = (a.K + kBK - 1) / kBK; s.kblocks_per_split = pl.kblocks_per_split;
-    s.total_work = pl.m_tiles * pl.n_tiles;
+    s.m_tiles = pl.m_tiles; s.n_tiles = pl.n_tiles; s.splits = splits;
+    s.kblocks_total = (a.K + kBK - 1) / kBK; s.kblocks_per_split = kps;
+    s.tile_base = tile_base; s.total_work = tile_end;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)pl.grid);
+    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
@@ -508,7 +536,7 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     int na = pdl_attribute(attr);
     if (kSplit) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)pl.splits;
+        attr[na].val.clusterDim.x = (unsigned)splits;
         attr[na].val.clusterDim.y = 1;
         attr[na].val.clusterDim.z = 1;
         ++na;
@@ -528,14 +556,24 @@ cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }
-    const bool split = pl.splits > 1;
-    switch (pl.bn) {
-        case 256: return split ? launch_bn<256, true>(pl, a, ta, tb, ty, stream) : launch_bn<256, false>(pl, a, ta, tb, ty, stream);
-        case 128: return split ? launch_bn<128, true>(pl, a, ta, tb, ty, stream) : launch_bn<128, false>(pl, a, ta, tb, ty, stream);
-        case 64: return split ? launch_bn<64, true>(pl, a, ta, tb, ty, stream) : launch_bn<64, false>(pl, a, ta, tb, ty, stream);
-    }
-    if (why) *why = "unsupported tile width";
-    return cudaErrorInvalidValue;
+    const int tiles = pl.m_tiles * pl.n_tiles;
+    const int main_tiles = tiles - pl.tail_tiles;
+    auto go = [&](bool split, int base, int end, int splits, int kps, int grid) -> cudaError_t {
+        switch (pl.bn) {
+            case 256: return split ? launch_bn<256, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid)
+                                   : launch_bn<256, false>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid);
+            case 128: return split ? launch_bn<128, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid)
+                                   : launch_bn<128, false>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid);
+            case 64: return split ? launch_bn<64, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid)
+                                  : launch_bn<64, false>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid);
+        }
+        if (why) *why = "unsupported tile width";
+        return cudaErrorInvalidValue;
+    };
+    if (pl.splits > 1) return go(true, 0, tiles, pl.splits, pl.kblocks_per_split, pl.grid);
+    cudaError_t e = go(false, 0, main_tiles, 1, pl.kblocks_per_split, main_tiles < 148 ? main_tiles : 148);
+    if (e != cudaSuccess || pl.tail_tiles == 0) return e;
+    return go(true, main_tiles, tiles, pl.tail_splits, pl.tail_kps, pl.tail_tiles * pl.tail_splits);
 }
 
 }  // namespace fp8lin
