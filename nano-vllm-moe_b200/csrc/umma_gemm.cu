@@ -331,11 +331,14 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int n = n0 + c;
             if (row >= p.M || n >= p.N) continue;
             const uint32_t local = smem_base + (uint32_t)r * Cfg::kPartPitch + (uint32_t)c * 4;
+            // all slices' loads go out before the first add: remote shared memory is a long trip
+            float4 u[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                u[s] = s < sched.splits ? ld_cluster_f4(map_to_cta(local, (uint32_t)s)) : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < sched.splits; ++s) {
-                const float4 u = ld_cluster_f4(map_to_cta(local, (uint32_t)s));
-                a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
-            }
+#pragma unroll
+            for (int s = 0; s < 8; ++s) { a.x += u[s].x; a.y += u[s].y; a.z += u[s].z; a.w += u[s].w; }
             const float4 sc = *reinterpret_cast<const float4*>(&s_scale[0][c]);
             const float4 bi = *reinterpret_cast<const float4*>(&s_bias[0][c]);
             uint2 out;

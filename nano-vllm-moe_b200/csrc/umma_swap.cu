@@ -298,11 +298,14 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const int n = first_tile * kTileN + r_beg + rl;
             if (n >= p.N || mg >= p.M) continue;
             const uint32_t local = smem_base + (uint32_t)(r_beg + rl) * Cfg::kPartPitch + (uint32_t)mg * 4;
+            // all slices' loads go out before the first add: remote shared memory is a long trip
+            float4 u[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                u[s] = s < sched.splits ? ld_cluster_f4(map_to_cta(local, (uint32_t)s)) : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < sched.splits; ++s) {
-                const float4 u = ld_cluster_f4(map_to_cta(local, (uint32_t)s));
-                a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
-            }
+#pragma unroll
+            for (int s = 0; s < 8; ++s) { a.x += u[s].x; a.y += u[s].y; a.z += u[s].z; a.w += u[s].w; }
             const float ws = __ldg(p.w_scale + n);
             const float bs = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
             const float o[4] = {a.x, a.y, a.z, a.w};
