@@ -56,6 +56,10 @@ for _t in (1, 64, 1024, 4096):
     WORKLOADS[f"c5_t{_t}"] = ("moe_w8a8", _t)
 MOE = {"hidden": 2048, "experts": 60, "inter": 1408, "top_k": 4}
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/c2_w8a8_launch_list_and_top_kernels.md, keyed by (M, K, N) of the captured launch
+NCU_TRAFFIC_BYTES = {(1024, 2048, 11008): 87.4e6, (256, 11008, 2048): 25.4e6, (16, 2048, 11008): 22.7e6}
+
 L2_BYTES = 126 * 1024 * 1024
 SEED = 20260519
 
@@ -575,6 +579,8 @@ def main():
     else:
         roofline = {"bound": "tensor", "achieved": dom["tflops"], "peak": fp8_peak, "unit": "TFLOP/s",
                     "frac": dom["tflops"] / fp8_peak, "traffic": None}
+    roofline["traffic"] = NCU_TRAFFIC_BYTES.get((dom["m"], dom["k"], dom["n"])) if tp == 1 else None
+    roofline["algorithmic_bytes"] = algorithmic_bytes(dom["m"], dom["k"], dom["n"])
     roofline["kernel"] = dom["variant"]
     roofline["shape"] = [dom["m"], dom["k"], dom["n"]]
     roofline["peak_source"] = (f"{peaks['source']}: HBM copy {peaks['hbm_gbs']} GB/s; dense-FP8 peak taken as 2 x "
