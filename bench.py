@@ -534,6 +534,8 @@ def main():
         reps = 5
         g = torch.cuda.CUDAGraph()
         try:
+            if not use_graph:
+                raise RuntimeError("eager timing requested")
             with torch.cuda.stream(side):
                 layers[0][i](x)
                 torch.cuda.synchronize()
@@ -552,7 +554,8 @@ def main():
             torch.cuda.synchronize()
             us = a.elapsed_time(b) * 1e3 / (4 * reps * copies)
         except Exception as e:  # noqa: BLE001
-            print(f"[bench] per-shape graph failed for {label}: {e!r}", file=sys.stderr)
+            if use_graph:
+                print(f"[bench] per-shape graph failed for {label}: {e!r}", file=sys.stderr)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             a.record()

@@ -176,8 +176,47 @@ class RowParallelLinear(LinearBase):
         cols = param.data.size(self.tp_dim)
         param.data.copy_(loaded_weight.narrow(self.tp_dim, self.tp_rank * cols, cols))
 
+    # Optional: from this many rows on, cut the row-parallel forward into chunks so that the
+    # all-reduce of chunk i (second stream) runs under the GEMM of chunk i+1.  Off by default:
+    # measured on 2 B200s at M=4096 it is slower than GEMM + one all-reduce replayed from a CUDA
+    # graph (four 7 MB all-reduces cost more than one 29 MB one, and the eager launches are
+    # host-bound); kept for large eager prefills.
+    overlap_min_rows = None
+    overlap_chunks = 4
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = self.apply_linear(x, self.bias if self.tp_rank == 0 else None)
-        if self.tp_size > 1 and self.reduce_results:
+        bias = self.bias if self.tp_rank == 0 else None
+        reduce = self.tp_size > 1 and self.reduce_results
+        rows = x.numel() // x.shape[-1] if x.dim() > 0 else 0
+        if (reduce and self.quant_method is not None and x.is_cuda and x.dtype == torch.bfloat16
+                and self.overlap_min_rows is not None and rows >= self.overlap_min_rows
+                and not torch.cuda.is_current_stream_capturing()):
+            return self._forward_overlapped(x, bias, rows)
+        y = self.apply_linear(x, bias)
+        if reduce:
             dist.all_reduce(y, group=self.tp_group)
         return y
+
+    def _forward_overlapped(self, x: torch.Tensor, bias, rows: int) -> torch.Tensor:
+        """GEMM and all-reduce pipelined over row chunks: same sums as the one-shot form (the
+        reduction is elementwise), but only the last chunk's all-reduce is exposed."""
+        x2 = x.reshape(rows, x.shape[-1])
+        y = torch.empty((rows, self.output_size), dtype=torch.bfloat16, device=x.device)
+        compute = torch.cuda.current_stream(x.device)
+        comm = getattr(self, "_comm_stream", None)
+        if comm is None:
+            comm = self._comm_stream = torch.cuda.Stream(x.device)
+        step = -(-rows // self.overlap_chunks)
+        step = (step + 127) // 128 * 128
+        for r0 in range(0, rows, step):
+            r1 = min(rows, r0 + step)
+            part = y[r0:r1]
+            self.quant_method.apply(self, x2[r0:r1], bias, out=part)
+            done = torch.cuda.Event()
+            done.record(compute)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                dist.all_reduce(part, group=self.tp_group)
+        compute.wait_stream(comm)
+        y.record_stream(comm)
+        return y.view(*x.shape[:-1], self.output_size)

@@ -144,7 +144,10 @@ class Fp8LinearMethod(QuantizeMethodBase):
         layer._fp8_backend = "fp8lin_w8a8" if self.is_w8a8 else "fp8lin_w8a16"
 
     # ---- forward ---------------------------------------------------------------------
-    def apply(self, layer: nn.Module, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    def apply(self, layer: nn.Module, x: torch.Tensor, bias: torch.Tensor | None = None,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+        """``out`` (optional, bf16 [M, N], row stride a multiple of 8) receives the result in place;
+        the row-parallel layer uses it to compute M in chunks into one buffer."""
         backend = getattr(layer, "_fp8_backend", None)
         if not x.is_cuda:
             scheme = "FP8 W8A8 static" if self.is_w8a8 else "FP8 W8A16"
@@ -158,7 +161,9 @@ class Fp8LinearMethod(QuantizeMethodBase):
         if bias is not None and bias.dtype != torch.bfloat16:
             bias = bias.to(torch.bfloat16)
         if self.is_w8a8:
-            y = kernels.launch_w8a8_gemm(x2, layer.qweight_packed, layer.input_scale, layer.weight_scale, bias)
+            y = kernels.launch_w8a8_gemm(x2, layer.qweight_packed, layer.input_scale, layer.weight_scale, bias, out=out)
         else:
-            y = kernels.launch_w8a16_gemm(x2, layer.qweight_packed, layer.weight_scale, bias)
+            y = kernels.launch_w8a16_gemm(x2, layer.qweight_packed, layer.weight_scale, bias, out=out)
+        if out is not None:
+            return out
         return y.view(*x.shape[:-1], y.shape[-1]).to(x.dtype)
