@@ -28,6 +28,7 @@ struct Tuning {
     int swap_splits = -1;     // force split-K factor of the swapped-operand decode kernel
     int swap_enable = -1;     // 0 routes decode-sized W8A8 to the mma.sync streaming kernel instead
     int swap_min_m = -1;      // smallest M routed to the swapped-operand kernel
+    int swap_preq_min_m = -1; // smallest M for which that kernel takes pre-quantised activations
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -65,6 +66,13 @@ bool swap_eligible(int64_t M) {
     // faster than the one-CTA-per-SM tcgen05 pipeline; measured cross-over is between 8 and 16 rows
     const int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 9;
     return g_tune.swap_enable != 0 && M >= min_m && M <= 64 && M <= max_m;
+}
+
+// from this many rows on the swapped-operand kernel takes pre-quantised rows (one extra small
+// pass, but nine ring slots instead of five or seven; measured faster from 17 rows up)
+bool swap_prequant(int64_t M) {
+    const int min_m = g_tune.swap_preq_min_m >= 0 ? g_tune.swap_preq_min_m : 17;
+    return M >= min_m;
 }
 
 bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
@@ -169,11 +177,19 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
     if (!input_scale) return fail(FP8LIN_ERR_NULL, "input_scale must not be NULL");
     cudaStream_t st = (cudaStream_t)stream;
     if (swap_eligible(M)) {
-        SwapPlan sp = plan_swap(M, K, N, g_tune.swap_splits);
+        const bool preq = swap_prequant(M);
+        SwapPlan sp = plan_swap(M, K, N, g_tune.swap_splits, preq);
         WsView wsv = ws_view(workspace, workspace_bytes);
         if (!workspace) return fail(FP8LIN_ERR_WORKSPACE, "workspace (at least the %d-byte header) is required", FP8LIN_WS_HEADER_BYTES);
         UmmaArgs a;
-        a.xq = nullptr; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
+        a.xq = nullptr;
+        if (preq) {
+            if (wsv.body_bytes < align_up((size_t)M * K, 256))
+                return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes", FP8LIN_WS_HEADER_BYTES + align_up((size_t)M * K, 256));
+            cudaError_t qe = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, wsv.body, M, K, st);
+            if (qe != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(qe));
+            a.xq = wsv.body;
+        } a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
         a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y; a.partial = nullptr; a.counters = nullptr;
         a.status = wsv.status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ldy;
         const char* why = nullptr;
@@ -227,8 +243,8 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
         return buf;
     }
     if (scheme == FP8LIN_W8A8_STATIC && swap_eligible(M)) {
-        SwapPlan pl = plan_swap(M, K, N, g_tune.swap_splits);
-        snprintf(buf, sizeof(buf), "umma_swap_w8a8_m%d_s%d", pl.mp, pl.splits);
+        SwapPlan pl = plan_swap(M, K, N, g_tune.swap_splits, swap_prequant(M));
+        snprintf(buf, sizeof(buf), "umma_swap_w8a8_m%d_s%d%s", pl.mp, pl.splits, pl.preq ? "_preq" : "");
         return buf;
     }
     StreamPlan sp = plan_stream(scheme, M, K, N, g_tune.stream_splits);
@@ -245,6 +261,7 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "swap_splits")) g_tune.swap_splits = value;
     else if (!strcmp(knob, "swap_enable")) g_tune.swap_enable = value;
     else if (!strcmp(knob, "swap_min_m")) g_tune.swap_min_m = value;
+    else if (!strcmp(knob, "swap_preq_min_m")) g_tune.swap_preq_min_m = value;
     else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;

@@ -88,11 +88,12 @@ struct SwapPlan {
     int splits;        // cluster split-K factor (1 = persistent over tiles)
     int kblocks_per_split;
     int grid;
+    int preq;          // 1 = activations pre-quantised by act_quant (a.xq), 0 = quantised in the kernel from x
 };
 
-SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits);
-// `a.xq`, `a.partial`, `a.counters` are unused: x is quantised inside the kernel and split-K
-// is reduced through cluster shared memory.
+SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq);
+// `a.partial`, `a.counters` are unused (split-K is reduced through cluster shared memory); `a.xq`
+// only when plan.preq.
 cudaError_t launch_swap_w8a8(const SwapPlan& plan, const UmmaArgs& a, const void* x, int64_t ldx,
                              cudaStream_t stream, const char** why);
 

@@ -35,16 +35,19 @@ constexpr int kSwapThreads = (2 + kConvWarps + 4) * 32;
 constexpr int kTileN = 128;   // output channels per tile = MMA M
 constexpr int kKB = 128;      // K elements per block
 
-template <int MP>
+// kPreQ: the activations were quantised by a pass before the kernel and arrive as ready MMA "B"
+// tiles by TMA; no raw block, no converter work, so more ring slots fit (used for 33..64 rows,
+// where the raw block would leave only five slots).
+template <int MP, bool kPreQ = false>
 struct SwapCfg {
     static constexpr int kWBytes = kTileN * kKB;                 // 16 KB e4m3 weight tile
     static constexpr int kXqBytes = MP * kKB;                    // quantised activation tile (MMA B)
-    static constexpr int kXrawBytes = MP * kKB * 2;              // raw bf16 activation block
+    static constexpr int kXrawBytes = kPreQ ? 0 : MP * kKB * 2;  // raw bf16 activation block
     static constexpr int kStageBytes = kWBytes + kXqBytes + kXrawBytes;
     // M <= 16: two CTAs share an SM (5 stages each, 160 KB of weights in flight per SM), so the
     // CTAs of the next kernel can start on an SM while this kernel's other CTA is still draining
     static constexpr int kCtasPerSm = MP <= 16 ? 2 : 1;
-    static constexpr int kStages = MP <= 16 ? 5 : (MP <= 32 ? 7 : 5);
+    static constexpr int kStages = kPreQ ? (MP <= 16 ? 6 : 9) : (MP <= 16 ? 5 : (MP <= 32 ? 7 : 5));
     // converter warps that share one K block (more rows -> more warps per block)
     static constexpr int kTeam = MP <= 16 ? 1 : (MP <= 32 ? 2 : 4);
     static constexpr int kRingBytes = kStages * kStageBytes;
@@ -77,11 +80,14 @@ __device__ __forceinline__ void tmem_ld_cols<64>(uint32_t taddr, uint32_t* v) {
     tmem_ld32_nowait(taddr + 32, v + 32);
 }
 
-template <int MP, bool kSplit>
-__global__ void __launch_bounds__(kSwapThreads, SwapCfg<MP>::kCtasPerSm)
+template <int MP, bool kSplit, bool kPreQ = false>
+__global__ void __launch_bounds__(kSwapThreads, SwapCfg<MP, kPreQ>::kCtasPerSm)
 swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  UmmaArgs p, SwapSched sched) {
-    using Cfg = SwapCfg<MP>;
+    using Cfg = SwapCfg<MP, kPreQ>;
+    // bytes of activations one K block brings in: M real rows, raw bf16 or ready e4m3
+    const uint32_t x_bytes = (uint32_t)p.M * (kPreQ ? 128u : 256u);
+    constexpr uint32_t kXDst = Cfg::kWBytes + (kPreQ ? 0 : Cfg::kXqBytes);   // where the TMA puts them
     constexpr int S = Cfg::kStages;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[S];     // TMA bytes landed (weights + raw x)
@@ -139,13 +145,13 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             if (first_tile < sched.n_tiles) {
                 for (int i = 0; i < first_kb; ++i) {
                     const uint32_t full = smem_u32(&bar_full[i]);
-                    mbar_expect_tx(full, Cfg::kWBytes + (uint32_t)p.M * 256u);   // the x box holds the M real rows only
+                    mbar_expect_tx(full, Cfg::kWBytes + x_bytes);   // the x box holds the M real rows only
                     tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_w, 0,
                                 (first_tile * sched.kblocks_total + kb0 + i) * kTileN, full);   // one packed tile
                 }
                 pdl_wait();
                 for (int i = 0; i < first_kb; ++i)
-                    tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kWBytes + Cfg::kXqBytes, &tmap_x,
+                    tma_load_2d(smem_base + i * Cfg::kStageBytes + kXDst, &tmap_x,
                                 (kb0 + i) * kKB, 0, smem_u32(&bar_full[i]));
             }
             for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step) {
@@ -157,10 +163,10 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         s_abort = 1; ok = false; break;
                     }
                     const uint32_t full = smem_u32(&bar_full[st]);
-                    mbar_expect_tx(full, Cfg::kWBytes + (uint32_t)p.M * 256u);
+                    mbar_expect_tx(full, Cfg::kWBytes + x_bytes);
                     const uint32_t sa = smem_base + st * Cfg::kStageBytes;
                     tma_load_2d(sa, &tmap_w, 0, (t * sched.kblocks_total + kb) * kTileN, full);
-                    tma_load_2d(sa + Cfg::kWBytes + Cfg::kXqBytes, &tmap_x, kb * kKB, 0, full);
+                    tma_load_2d(sa + kXDst, &tmap_x, kb * kKB, 0, full);
                 }
             }
             if (!ok) {
@@ -187,7 +193,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const int st = it % S;
                     const uint32_t ph = (it / S) & 1;
                     if (s_abort || !mbar_wait(smem_u32(&bar_full[st]), ph, p.status, kDevTimeoutFull) ||
-                        !mbar_wait(smem_u32(&bar_xq[st]), ph, p.status, kDevTimeoutFull)) {
+                        (!kPreQ && !mbar_wait(smem_u32(&bar_xq[st]), ph, p.status, kDevTimeoutFull))) {
                         s_abort = 1; ok = false; break;
                     }
                     tc_fence_after();
@@ -203,7 +209,8 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             }
         }
     } else if (warp < 2 + kConvWarps) {
-        // ================= activation converters (warps 2..9) =================
+        // ================= activation converters (warps 2..9); idle when the rows come pre-quantised ====
+        if (!kPreQ) {
         constexpr int kTeams = kConvWarps / Cfg::kTeam;
         const int team = (warp - 2) / Cfg::kTeam;            // a ring slot always belongs to the same team
         const int member = (warp - 2) % Cfg::kTeam;
@@ -239,6 +246,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_xq[st]));
             }
+        }
         }
     } else {
         // ================= epilogue (warps 10..13) =================
@@ -342,15 +350,16 @@ static bool encode_x_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
     return r == CUDA_SUCCESS;
 }
 
-template <int MP>
+template <int MP, bool kPreQ>
 static int swap_max_clusters(int cluster) {
-    using Cfg = SwapCfg<MP>;
-    const void* kern = (const void*)swap_w8a8_kernel<MP, true>;
+    using Cfg = SwapCfg<MP, kPreQ>;
+    const void* kern = (const void*)swap_w8a8_kernel<MP, true, kPreQ>;
     return max_active_clusters(kern, kSwapThreads, Cfg::kSmemBytes, cluster);
 }
 
-SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits) {
+SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq) {
     SwapPlan pl{};
+    pl.preq = preq ? 1 : 0;
     pl.mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     pl.n_tiles = (int)((N + kTileN - 1) / kTileN);
     const int kblocks = (int)((K + kKB - 1) / kKB);
@@ -363,7 +372,10 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits) {
         const int kps = (kblocks + s - 1) / s;
         if ((kblocks + kps - 1) / kps != s) continue;                        // would leave an empty slice
         int slots = 148 * (pl.mp == 16 ? 2 : 1);
-        if (s > 1) slots = pl.mp == 16 ? swap_max_clusters<16>(s) : (pl.mp == 32 ? swap_max_clusters<32>(s) : swap_max_clusters<64>(s));
+        if (s > 1) {
+            if (preq) slots = pl.mp == 16 ? swap_max_clusters<16, true>(s) : (pl.mp == 32 ? swap_max_clusters<32, true>(s) : swap_max_clusters<64, true>(s));
+            else slots = pl.mp == 16 ? swap_max_clusters<16, false>(s) : (pl.mp == 32 ? swap_max_clusters<32, false>(s) : swap_max_clusters<64, false>(s));
+        }
         if (slots < 1) slots = 1;
         // with two CTAs per SM a second wave of clusters trickles in as slots free up, so a
         // fractional wave count models it better than a ceiling (measured on 18944 -> 3584)
@@ -381,11 +393,11 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits) {
     return pl;
 }
 
-template <int MP, bool kSplit>
+template <int MP, bool kSplit, bool kPreQ>
 static cudaError_t launch_swap(const SwapPlan& pl, const UmmaArgs& a, const CUtensorMap& tw, const CUtensorMap& tx,
                                cudaStream_t stream) {
-    using Cfg = SwapCfg<MP>;
-    auto kern = swap_w8a8_kernel<MP, kSplit>;
+    using Cfg = SwapCfg<MP, kPreQ>;
+    auto kern = swap_w8a8_kernel<MP, kSplit, kPreQ>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -417,17 +429,23 @@ static cudaError_t launch_swap(const SwapPlan& pl, const UmmaArgs& a, const CUte
 cudaError_t launch_swap_w8a8(const SwapPlan& pl, const UmmaArgs& a, const void* x, int64_t ldx, cudaStream_t stream,
                              const char** why) {
     CUtensorMap tw, tx;
-    if (!encode_u8_2d(&tw, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128, kTileN) ||
-        !encode_x_bf16(&tx, x, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)ldx * 2, (uint32_t)a.M)) {
+    bool ok = encode_u8_2d(&tw, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128, kTileN);
+    if (pl.preq) ok = ok && encode_u8_2d(&tx, a.xq, (uint64_t)a.M, (uint64_t)a.K, (uint32_t)a.M);      // ready e4m3 rows
+    else ok = ok && encode_x_bf16(&tx, x, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)ldx * 2, (uint32_t)a.M);
+    if (!ok) {
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }
     const bool split = pl.splits > 1;
-    switch (pl.mp) {
-        case 16: return split ? launch_swap<16, true>(pl, a, tw, tx, stream) : launch_swap<16, false>(pl, a, tw, tx, stream);
-        case 32: return split ? launch_swap<32, true>(pl, a, tw, tx, stream) : launch_swap<32, false>(pl, a, tw, tx, stream);
-        case 64: return split ? launch_swap<64, true>(pl, a, tw, tx, stream) : launch_swap<64, false>(pl, a, tw, tx, stream);
+#define FP8LIN_SWAP_CASE(MP_)                                                                                   \
+    if (pl.mp == MP_) {                                                                                         \
+        if (pl.preq) return split ? launch_swap<MP_, true, true>(pl, a, tw, tx, stream) : launch_swap<MP_, false, true>(pl, a, tw, tx, stream); \
+        return split ? launch_swap<MP_, true, false>(pl, a, tw, tx, stream) : launch_swap<MP_, false, false>(pl, a, tw, tx, stream);            \
     }
+    FP8LIN_SWAP_CASE(16)
+    FP8LIN_SWAP_CASE(32)
+    FP8LIN_SWAP_CASE(64)
+#undef FP8LIN_SWAP_CASE
     if (why) *why = "unsupported token-tile width";
     return cudaErrorInvalidValue;
 }

@@ -22,7 +22,7 @@ SCHEMES = ["fp8_w8a16", "fp8_w8a8_static"]
 def _clean_tuning_and_status():
     Kn = kernels()
     yield
-    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable", "swap_min_m"):
+    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m"):
         Kn.set_tuning(knob, -1)
     torch.cuda.synchronize()
     assert Kn.read_status(torch.device("cuda", 0)) == 0
@@ -233,6 +233,22 @@ def test_swapped_tcgen05_kernel_split_variants(m, splits):
     y2 = run_linear("fp8_w8a8_static", d)
     np.testing.assert_array_equal(y1, y2)
     assert_parity(y1, oracle_linear("fp8_w8a8_static", c), f"swap m={m} splits={splits}")
+
+
+@pytest.mark.parametrize("preq_min", [1, 65])
+@pytest.mark.parametrize("m", [12, 33, 64])
+def test_swapped_kernel_with_and_without_prequantised_rows(m, preq_min):
+    """The swapped-operand kernel either quantises the rows itself or takes them pre-quantised
+    (default from 17 rows); both must give the same bits."""
+    Kn = kernels()
+    Kn.set_tuning("swap_preq_min_m", preq_min)
+    c = O.make_case(4000 + m, m, 1408, 1000)
+    d = upload_case(c)
+    y = run_linear("fp8_w8a8_static", d)
+    assert ("_preq" in Kn.variant_name(1, m, 1408, 1000)) == (m >= preq_min)
+    assert_parity(y, oracle_linear("fp8_w8a8_static", c), f"swap preq_min={preq_min} m={m}")
+    Kn.set_tuning("swap_preq_min_m", 65 if preq_min == 1 else 1)
+    np.testing.assert_array_equal(y, run_linear("fp8_w8a8_static", d))
 
 
 def test_tcgen05_matches_streaming_kernel():
