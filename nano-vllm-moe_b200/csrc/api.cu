@@ -29,6 +29,8 @@ struct Tuning {
     int swap_enable = -1;     // 0 routes decode-sized W8A8 to the mma.sync streaming kernel instead
     int swap_min_m = -1;      // smallest M routed to the swapped-operand kernel
     int swap_preq_min_m = -1; // smallest M for which that kernel takes pre-quantised activations
+    int w8a16_swap_enable = -1; // 0 keeps W8A16 on the mma.sync streaming kernel for every M
+    int w8a16_swap_min_m = -1;
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -58,6 +60,13 @@ int validate_common(const void* x, int64_t ldx, const void* w, const float* w_sc
         return fail(FP8LIN_ERR_ALIGN, "x, w_nk, w_scale and bias must be 16-byte aligned");
     if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
     return FP8LIN_OK;
+}
+
+bool w8a16_swap_eligible(int64_t M) {
+    // measured: the mma.sync kernel wins up to 32 rows (27 vs 34 us on 3584 -> 37888 at M = 16,
+    // equal at 32), the tcgen05 kernel from 33 rows (39 vs 67 us at M = 64)
+    const int min_m = g_tune.w8a16_swap_min_m >= 0 ? g_tune.w8a16_swap_min_m : 33;
+    return g_tune.w8a16_swap_enable != 0 && M >= min_m && M <= 64;
 }
 
 bool swap_eligible(int64_t M) {
@@ -165,6 +174,17 @@ int fp8lin_w8a16(const void* x, int64_t ldx, const void* w_nk, const float* w_sc
                  void* stream) {
     int rc = validate_common(x, ldx, w_nk, w_scale, bias, y, ldy, M, K, N);
     if (rc != FP8LIN_OK || M == 0) return rc;
+    if (w8a16_swap_eligible(M) && workspace) {
+        SwapPlan sp = plan_swap_w8a16(M, K, N, g_tune.swap_splits);
+        UmmaArgs a;
+        a.xq = nullptr; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = nullptr;
+        a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y; a.partial = nullptr; a.counters = nullptr;
+        a.status = ws_view(workspace, workspace_bytes).status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ldy;
+        const char* why = nullptr;
+        cudaError_t e = launch_swap_w8a16(sp, a, x, ldx, (cudaStream_t)stream, &why);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 W8A16 decode kernel launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+        return FP8LIN_OK;
+    }
     return run_stream(FP8LIN_W8A16, x, ldx, w_nk, w_scale, nullptr, bias, y, ldy, M, K, N, workspace,
                       workspace_bytes, (cudaStream_t)stream);
 }
@@ -247,6 +267,11 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
         snprintf(buf, sizeof(buf), "umma_swap_w8a8_m%d_s%d%s", pl.mp, pl.splits, pl.preq ? "_preq" : "");
         return buf;
     }
+    if (scheme == FP8LIN_W8A16 && w8a16_swap_eligible(M)) {
+        SwapPlan pl = plan_swap_w8a16(M, K, N, g_tune.swap_splits);
+        snprintf(buf, sizeof(buf), "umma_swap_w8a16_m%d_s%d", pl.mp, pl.splits);
+        return buf;
+    }
     StreamPlan sp = plan_stream(scheme, M, K, N, g_tune.stream_splits);
     snprintf(buf, sizeof(buf), "stream_mma_%s_m%d_s%d", scheme == FP8LIN_W8A16 ? "w8a16" : "w8a8", sp.mt * 8, sp.splits);
     return buf;
@@ -262,6 +287,8 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "swap_enable")) g_tune.swap_enable = value;
     else if (!strcmp(knob, "swap_min_m")) g_tune.swap_min_m = value;
     else if (!strcmp(knob, "swap_preq_min_m")) g_tune.swap_preq_min_m = value;
+    else if (!strcmp(knob, "w8a16_swap_enable")) g_tune.w8a16_swap_enable = value;
+    else if (!strcmp(knob, "w8a16_swap_min_m")) g_tune.w8a16_swap_min_m = value;
     else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;

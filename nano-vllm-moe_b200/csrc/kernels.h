@@ -126,4 +126,9 @@ int grouped_chunk_rows(int64_t rows, int num_experts);
 cudaError_t launch_grouped_w8a8(bool gather, int mp, GroupedArgs a, const void* w_packed, int num_experts,
                                 const void* xq_sorted, int64_t xq_rows, cudaStream_t stream, const char** why);
 
+// ---- swapped-operand tcgen05 kernel for W8A16, 9 <= M <= 64 (umma_swap_w8a16.cu) ----
+SwapPlan plan_swap_w8a16(int64_t M, int64_t K, int64_t N, int force_splits);
+cudaError_t launch_swap_w8a16(const SwapPlan& plan, const UmmaArgs& a, const void* x, int64_t ldx,
+                              cudaStream_t stream, const char** why);
+
 }  // namespace fp8lin

@@ -22,7 +22,8 @@ SCHEMES = ["fp8_w8a16", "fp8_w8a8_static"]
 def _clean_tuning_and_status():
     Kn = kernels()
     yield
-    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m"):
+    for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable",
+                 "w8a16_swap_min_m"):
         Kn.set_tuning(knob, -1)
     torch.cuda.synchronize()
     assert Kn.read_status(torch.device("cuda", 0)) == 0
@@ -127,7 +128,7 @@ STREAM_SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("scheme", SCHEMES + ["fp8_w8a8_static/mma_sync"])
+@pytest.mark.parametrize("scheme", SCHEMES + ["fp8_w8a8_static/mma_sync", "fp8_w8a16/mma_sync"])
 @pytest.mark.parametrize("m,k,n", STREAM_SHAPES)
 def test_streaming_kernel_parity(scheme, m, k, n):
     """Decode-sized shapes: W8A16 on the mma.sync streaming kernel, W8A8 on the swapped-operand
@@ -135,8 +136,12 @@ def test_streaming_kernel_parity(scheme, m, k, n):
     does not take)."""
     if scheme.endswith("/mma_sync"):
         kernels().set_tuning("swap_enable", 0)
+        kernels().set_tuning("w8a16_swap_enable", 0)
         scheme = scheme.split("/")[0]
-        assert kernels().variant_name(1, m, k, n).startswith("stream_mma_w8a8")
+        assert kernels().variant_name(1 if "a8" in scheme[-10:] else 0, m, k, n).startswith("stream_mma_")
+    elif scheme == "fp8_w8a16":
+        kernels().set_tuning("w8a16_swap_min_m", 1)  # by default M <= 8 stays on the mma.sync kernel
+        assert kernels().variant_name(0, m, k, n).startswith("umma_swap_w8a16")
     elif scheme == "fp8_w8a8_static":
         kernels().set_tuning("swap_min_m", 1)        # by default M <= 8 goes to the mma.sync kernel
         assert kernels().variant_name(1, m, k, n).startswith("umma_swap_w8a8")
@@ -151,9 +156,25 @@ def test_streaming_kernel_parity(scheme, m, k, n):
         assert O.cosine(y_nb, oref) >= (0.9999 if scheme == "fp8_w8a16" else 0.999)
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("m", [1, 16, 17, 33, 64])
+def test_swapped_w8a16_kernel_split_variants(m, splits):
+    Kn = kernels()
+    Kn.set_tuning("w8a16_swap_min_m", 1)
+    Kn.set_tuning("swap_splits", splits)
+    c = O.make_case(1900 + m + splits, m, 2048, 640)
+    d = upload_case(c)
+    assert Kn.variant_name(0, m, 2048, 640).startswith("umma_swap_w8a16")
+    y1 = run_linear("fp8_w8a16", d)
+    y2 = run_linear("fp8_w8a16", d)
+    np.testing.assert_array_equal(y1, y2)
+    assert_parity(y1, oracle_linear("fp8_w8a16", c), f"swap w8a16 m={m} splits={splits}")
+
+
 @pytest.mark.parametrize("scheme", SCHEMES)
 def test_streaming_split_k_is_deterministic_and_equal(scheme):
     Kn = kernels()
+    Kn.set_tuning("w8a16_swap_enable", 0)
     c = O.make_case(77, 16, 3584, 512)
     d = upload_case(c)
     ref = oracle_linear(scheme, c)
