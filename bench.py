@@ -390,6 +390,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--peer-reduce", choices=["auto", "on", "off"], default="auto",
+                    help="row-parallel layers: reduce through peer-memory stores in the GEMM epilogue (on), "
+                         "NCCL all-reduce after the GEMM (off), or by local K (auto, the layer default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -443,6 +446,8 @@ def main():
             lay.bias.data = torch.empty_like(lay.bias.data, dtype=torch.bfloat16)
             lay.bias.weight_loader(lay.bias, bias)
             pkg.process_weights_after_loading(lay)
+            if kind == "row" and args.peer_reduce != "auto":
+                lay.peer_reduce = args.peer_reduce == "on"
             row.append(lay)
             del q, s
             if c == 0:

@@ -102,6 +102,21 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
                 int64_t M, int64_t K, int64_t N,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* Row-parallel W8A8 linear with the reduction folded into the GEMM's stores (no counterpart in
+ * the reference, which calls dist.all_reduce after the GEMM, nanovllm/layers/linear.py:258-262).
+ * fp8lin_w8a8_scatter computes this rank's bf16 partial output and its epilogue TMA-stores every
+ * output box to each of dst_ptrs[0..n_dst) -- HOST array of device pointers to bf16 [M][ld_dst]
+ * matrices, typically this rank's slot in every rank's peer-mapped buffer (NVLink stores, no
+ * load from peer memory).  After a cross-rank barrier, fp8lin_sum_slots adds the n_slots partial
+ * outputs of a local buffer (slot r at slots + r*slot_stride elements) in slot order in fp32 and
+ * rounds once to bf16 -- the same sum the all-reduce produces, with a fixed order. */
+int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const float* w_scale,
+                        const float* input_scale, const void* bias, int n_dst, void* const* dst_ptrs,
+                        int64_t ld_dst, int64_t M, int64_t K, int64_t N,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, void* y,
+                     int64_t ldy, int64_t M, int64_t N, void* stream);
+
 /* Decode-sized linear (M <= 64, either scheme) that needs no workspace from the
  * caller and allocates nothing.  It has no counterpart in the reference; it
  * exists for callers that cannot allocate: a server whose KV-cache pool has

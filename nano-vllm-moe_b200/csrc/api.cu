@@ -241,6 +241,48 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
     return FP8LIN_OK;
 }
 
+int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const float* w_scale, const float* input_scale,
+                        const void* bias, int n_dst, void* const* dst_ptrs, int64_t ld_dst, int64_t M, int64_t K, int64_t N,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+    if (n_dst < 1 || n_dst > 8 || !dst_ptrs) return fail(FP8LIN_ERR_ARG, "n_dst must be 1..8 and dst_ptrs non-NULL");
+    for (int d = 0; d < n_dst; ++d)
+        if (!dst_ptrs[d] || !aligned16(dst_ptrs[d])) return fail(FP8LIN_ERR_ALIGN, "destination %d is NULL or not 16-byte aligned", d);
+    int rc = validate_common(x, ldx, w_nk, w_scale, bias, dst_ptrs[0], ld_dst, M, K, N);
+    if (rc != FP8LIN_OK || M == 0) return rc;
+    if (!input_scale) return fail(FP8LIN_ERR_NULL, "input_scale must not be NULL");
+    if (N % 8 != 0 || ld_dst % 8 != 0) return fail(FP8LIN_ERR_SHAPE, "N and ld_dst must be multiples of 8");
+    cudaStream_t st = (cudaStream_t)stream;
+    UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, 1);      // the scatter epilogue exists in the non-split kernel only
+    pl.tail_tiles = 0;
+    WsView ws = ws_view(workspace, workspace_bytes);
+    const size_t xq_bytes = align_up((size_t)M * K, 256);
+    if (!workspace || ws.body_bytes < xq_bytes)
+        return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes", FP8LIN_WS_HEADER_BYTES + xq_bytes);
+    cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, ws.body, M, K, st);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
+    UmmaArgs a;
+    a.xq = ws.body; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
+    a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)dst_ptrs[0]; a.partial = nullptr; a.counters = ws.counters;
+    a.status = ws.status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ld_dst;
+    const char* why = nullptr;
+    e = launch_umma_w8a8(pl, a, st, &why, n_dst, dst_ptrs, ld_dst);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+    return FP8LIN_OK;
+}
+
+int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, void* y, int64_t ldy,
+                     int64_t M, int64_t N, void* stream) {
+    if (n_slots < 1 || M < 0 || N <= 0 || N % 8 != 0 || ld_slot % 8 != 0 || ldy % 8 != 0 || slot_stride % 8 != 0)
+        return fail(FP8LIN_ERR_SHAPE, "bad shape: N, ld_slot, ldy and slot_stride must be multiples of 8");
+    if (M == 0) return FP8LIN_OK;
+    if (!slots || !y) return fail(FP8LIN_ERR_NULL, "slots and y must not be NULL");
+    if (!aligned16(slots) || !aligned16(y)) return fail(FP8LIN_ERR_ALIGN, "slots and y must be 16-byte aligned");
+    cudaError_t e = launch_sum_slots((const __nv_bfloat16*)slots, n_slots, slot_stride, (__nv_bfloat16*)y, ldy, M, N, ld_slot,
+                                     (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "slot sum launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
 int fp8lin_quantize_activation(const void* x, int64_t ldx, const float* input_scale, void* xq, int64_t M, int64_t K,
                                void* stream) {
     if (M < 0 || K <= 0 || K % 16 != 0) return fail(FP8LIN_ERR_SHAPE, "bad shape M=%lld K=%lld", (long long)M, (long long)K);

@@ -45,6 +45,42 @@ cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* i
     return cudaLaunchKernelEx(&cfg, act_quant_kernel, x, ldx, input_scale, xq, M, K);
 }
 
+// y[m][n] = bf16( sum over slots r of slots[r][m][n] ), added in slot order in fp32: the reduction step
+// of a row-parallel linear whose ranks have scattered their bf16 partial outputs into every rank's slots.
+__global__ void __launch_bounds__(256)
+sum_slots_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, int64_t slot_stride, __nv_bfloat16* __restrict__ y,
+                 int64_t ldy, int64_t M, int64_t N, int64_t ld_slot) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t vec_per_row = N / 8;
+    const int64_t total = M * vec_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / vec_per_row;
+        const int64_t c = (i - m * vec_per_row) * 8;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < n_slots; ++r) {
+            // peers wrote these lines: read them past L1
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + r * slot_stride + m * ld_slot + c));
+            acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+            acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(y + m * ldy + c) = o;
+    }
+}
+
+cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t slot_stride, __nv_bfloat16* y, int64_t ldy,
+                             int64_t M, int64_t N, int64_t ld_slot, cudaStream_t stream) {
+    const int64_t total = M * (N / 8);
+    if (total == 0) return cudaSuccess;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    sum_slots_kernel<<<(unsigned)blocks, 256, 0, stream>>>(slots, n_slots, slot_stride, y, ldy, M, N, ld_slot);
+    return cudaGetLastError();
+}
+
 // Pack e4m3 weight bytes into the tiled layout (see pack_offset).  One CTA fills one
 // 128 x 128 tile through shared memory; `src_is_kn` selects the source orientation:
 // [K][N] (the reference's runtime buffer) or [N][K] (the checkpoint's layout).

@@ -79,7 +79,12 @@ struct UmmaPlan {
 
 UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_splits);
 // Returns cudaSuccess or an error; `why` (optional) receives a static description.
-cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why);
+// n_dst == 0: the result goes to args.y.  n_dst >= 1 (non-split plans only): the epilogue stores every
+// output box to each of dst_ptrs[0..n_dst) (bf16 [M][ld_dst] matrices; may be peer-GPU memory).
+cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why,
+                             int n_dst = 0, void* const* dst_ptrs = nullptr, int64_t ld_dst = 0);
+cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t slot_stride, __nv_bfloat16* y, int64_t ldy,
+                             int64_t M, int64_t N, int64_t ld_slot, cudaStream_t stream);
 
 // ---- swapped-operand tcgen05 kernel for M <= 64 (umma_swap.cu) -------------------
 struct SwapPlan {

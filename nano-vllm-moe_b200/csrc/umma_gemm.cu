@@ -73,6 +73,12 @@ __host__ __device__ constexpr uint32_t make_idesc() {
            | ((uint32_t)(kBM >> 4) << 24);
 }
 
+// Destinations of the epilogue's TMA stores (all describe a bf16 [M][N] matrix of the same shape).
+struct OutMaps {
+    CUtensorMap m[8];
+    int n;
+};
+
 struct UmmaSched {
     int m_tiles, n_tiles, splits, kblocks_total, kblocks_per_split;
     int tile_base, total_work;      // this launch covers tiles [tile_base, total_work)
@@ -94,7 +100,7 @@ __device__ __forceinline__ void decode_tile(const UmmaSched& s, int tile, int& t
 template <int BN, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_y, UmmaArgs p, UmmaSched sched) {
+                 const __grid_constant__ OutMaps outs, UmmaArgs p, UmmaSched sched) {
     using Cfg = UmmaCfg<BN>;
     constexpr int S = Cfg::kStages;
     extern __shared__ unsigned char smem_raw[];
@@ -292,7 +298,11 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0) tma_store_2d(&tmap_y, box, n0 + col, row0);
+                    if (lane == 0) {
+                        // one store per destination: the local output, or (row-parallel scatter) this
+                        // rank's slot in every rank's buffer, peers reached over NVLink
+                        for (int d = 0; d < outs.n; ++d) tma_store_2d(&outs.m[d], box, n0 + col, row0);
+                    }
                 } else {
                     // park the raw fp32 accumulators in this CTA's shared memory (over the idle ring)
                     const uint32_t dst0 = smem_base + (uint32_t)(q * 32 + lane) * Cfg::kPartPitch + (uint32_t)col * 4;
@@ -516,7 +526,7 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
 
 template <int BN, bool kSplit>
 static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb,
-                             const CUtensorMap& ty, cudaStream_t stream, int tile_base, int tile_end, int splits, int kps,
+                             const OutMaps& ty, cudaStream_t stream, int tile_base, int tile_end, int splits, int kps,
                              int grid) {
     using Cfg = UmmaCfg<BN>;
     auto kern = umma_w8a8_kernel<BN, kSplit>;
@@ -549,13 +559,27 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s);
 }
 
-cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why) {
-    CUtensorMap ta, tb, ty;
+cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why,
+                             int n_dst, void* const* dst_ptrs, int64_t ld_dst) {
+    CUtensorMap ta, tb;
+    OutMaps ty;
     const uint32_t piece = pl.bn == 256 ? 32 : (pl.bn / 2 < 64 ? pl.bn / 2 : 64);
-    if (!encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K, kBM) ||
-        !encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128,
-                      (uint32_t)(pl.bn < 128 ? pl.bn : 128)) ||
-        !encode_out_2d(&ty, a.y, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldy * 2, piece)) {
+    bool ok = encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K, kBM) &&
+              encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128,
+                           (uint32_t)(pl.bn < 128 ? pl.bn : 128));
+    if (n_dst <= 0) {
+        ty.n = 1;
+        ok = ok && encode_out_2d(&ty.m[0], a.y, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldy * 2, piece);
+    } else {
+        if (n_dst > 8 || pl.splits > 1) {
+            if (why) *why = "scatter epilogue needs 1..8 destinations and a non-split plan";
+            return cudaErrorInvalidValue;
+        }
+        ty.n = n_dst;
+        for (int d = 0; d < n_dst && ok; ++d)
+            ok = encode_out_2d(&ty.m[d], dst_ptrs[d], (uint64_t)a.M, (uint64_t)a.N, (uint64_t)ld_dst * 2, piece);
+    }
+    if (!ok) {
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }

@@ -184,10 +184,66 @@ class RowParallelLinear(LinearBase):
     overlap_min_rows = None
     overlap_chunks = 4
 
+    # Fold the all-reduce into the GEMM: every rank's epilogue stores its bf16 partial tile straight
+    # into its slot of every rank's peer-mapped buffer (NVLink stores issued while the GEMM runs),
+    # a symmetric-memory barrier follows, and each rank adds the slots locally in rank order.
+    # Needs torch symmetric memory on the TP group.  "auto" takes this path when the local GEMM is
+    # long enough to hide the NVLink stores (measured on 2 B200s: K/tp = 9472 -> 216 vs 243 us at
+    # M = 4096 and 638 vs 792 us at M = 16384; K/tp = 1792 -> no gain), True forces it, False never.
+    peer_reduce = "auto"
+    peer_reduce_min_rows = 512
+    peer_reduce_min_k = 4096
+
+    def _use_peer_reduce(self, x: torch.Tensor, rows: int) -> bool:
+        if self.peer_reduce is False or getattr(self, "_peer_failed", False):
+            return False
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and getattr(self, "_fp8_backend", None) == "fp8lin_w8a8"):
+            return False
+        if rows < self.peer_reduce_min_rows or self.output_size % 8:
+            return False
+        if self.peer_reduce == "auto" and self.input_size_per_partition < self.peer_reduce_min_k:
+            return False
+        # the peer buffers must exist before a stream capture starts
+        return getattr(self, "_peer_cap", 0) >= rows or not torch.cuda.is_current_stream_capturing()
+
+    def _peer_buffers(self, rows: int, device):
+        import torch.distributed._symmetric_memory as symm
+        cap = getattr(self, "_peer_cap", 0)
+        if cap < rows:
+            cap = max(rows, 2 * cap)
+            group = self.tp_group if self.tp_group is not None else dist.group.WORLD
+            buf = symm.empty((self.tp_size, cap, self.output_size), dtype=torch.bfloat16, device=device)
+            self._peer_handle = symm.rendezvous(buf, group)
+            self._peer_buf, self._peer_cap = buf, cap
+        return self._peer_buf, self._peer_handle, cap
+
+    def _forward_peer_reduce(self, x: torch.Tensor, bias, rows: int) -> torch.Tensor:
+        from ..quantization import kernels
+        x2 = x.reshape(rows, x.shape[-1])
+        buf, handle, cap = self._peer_buffers(rows, x.device)
+        slot_bytes = cap * self.output_size * 2
+        dst = [int(handle.buffer_ptrs[r]) + self.tp_rank * slot_bytes for r in range(self.tp_size)]
+        handle.barrier(channel=0)                       # nobody is still summing the previous call's slots
+        kernels.launch_w8a8_scatter(x2, self.qweight_packed, self.input_scale, self.weight_scale, bias, dst, self.output_size)
+        handle.barrier(channel=1)                       # every rank's partial tiles have landed everywhere
+        y = kernels.sum_slots(buf, rows, self.output_size)
+        return y.view(*x.shape[:-1], self.output_size)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         bias = self.bias if self.tp_rank == 0 else None
         reduce = self.tp_size > 1 and self.reduce_results
         rows = x.numel() // x.shape[-1] if x.dim() > 0 else 0
+        if reduce and self._use_peer_reduce(x, rows):
+            try:
+                return self._forward_peer_reduce(x, bias, rows)
+            except (RuntimeError, ImportError, AttributeError) as exc:
+                if self.peer_reduce is True or getattr(self, "_peer_cap", 0) > 0:
+                    raise
+                # symmetric memory is not available for this group (every rank fails alike in the
+                # collective rendezvous): remember it and use the all-reduce from now on
+                self._peer_failed = True
+                import warnings
+                warnings.warn(f"row-parallel peer reduction unavailable, using all-reduce: {exc}")
         if (reduce and self.quant_method is not None and x.is_cuda and x.dtype == torch.bfloat16
                 and self.overlap_min_rows is not None and rows >= self.overlap_min_rows
                 and not torch.cuda.is_current_stream_capturing()):

@@ -171,3 +171,30 @@ def quantize_activation(x: torch.Tensor, input_scale: torch.Tensor) -> torch.Ten
                                                     out.data_ptr(), m, k, _stream_ptr(x.device))
     _lib.raise_for(rc, "fp8lin_quantize_activation")
     return out
+
+
+def launch_w8a8_scatter(x: torch.Tensor, w_packed: torch.Tensor, input_scale: torch.Tensor, weight_scale: torch.Tensor,
+                        bias: torch.Tensor | None, dst_ptrs: list[int], ld_dst: int) -> None:
+    """This rank's partial output of a row-parallel linear, stored by the GEMM epilogue into every
+    destination (device pointers to bf16 [M, ld_dst] matrices, usually peer-mapped)."""
+    x, n, k = _check_linear_args(x, w_packed, weight_scale, bias)
+    m = x.shape[0]
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    with torch.cuda.device(x.device):
+        ws = workspace(x.device, workspace_bytes(_lib.W8A8_STATIC, m, k, n))
+        rc = _lib.load().fp8lin_w8a8_scatter(
+            x.data_ptr(), x.stride(0), w_packed.data_ptr(), weight_scale.data_ptr(), input_scale.data_ptr(),
+            bias.data_ptr() if bias is not None else None, len(dst_ptrs), arr, ld_dst, m, k, n,
+            ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
+    _lib.raise_for(rc, "fp8lin_w8a8_scatter")
+
+
+def sum_slots(slots: torch.Tensor, m: int, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """slots: bf16 [n_slots, rows >= m, n] -> bf16 [m, n], slots added in order in fp32."""
+    n_slots = slots.shape[0]
+    y = out if out is not None else torch.empty((m, n), dtype=torch.bfloat16, device=slots.device)
+    with torch.cuda.device(slots.device):
+        rc = _lib.load().fp8lin_sum_slots(slots.data_ptr(), n_slots, slots.stride(0), slots.stride(1), y.data_ptr(),
+                                          y.stride(0), m, n, _stream_ptr(slots.device))
+    _lib.raise_for(rc, "fp8lin_sum_slots")
+    return y

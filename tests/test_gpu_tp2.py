@@ -1,0 +1,72 @@
+"""Two-GPU tensor-parallel checks (skipped on boxes with one GPU): a row-parallel W8A8 layer through
+the NCCL all-reduce and through the peer-memory epilogue reduction, both against the oracle's
+row-parallel restatement (bias on rank 0, per-rank bf16 partials, fp32 sum in rank order)."""
+import importlib
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    from datetime import timedelta
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(seconds=90))
+    from oracle import fp8_oracle as O
+    pkg = importlib.import_module("nano-vllm-moe_b200")
+    m, k, n = 640, 1024, 512
+    c = O.make_case(2468, m, k, n)
+    with torch.device(dev):
+        lay = pkg.RowParallelLinear(k, n, bias=True, quant_method=pkg.Fp8Config("fp8_w8a8_static").get_quant_method(None, "down"))
+    lay.qweight.weight_loader(lay.qweight, torch.from_numpy(c["wq"]).to(dev))
+    lay.weight_scale.weight_loader(lay.weight_scale, torch.from_numpy(c["w_scale"]).to(dev))
+    lay.input_scale.weight_loader(lay.input_scale, torch.tensor(float(c["input_scale"])))
+    lay.bias.data = torch.from_numpy(c["bias"]).to(dev, torch.bfloat16)
+    pkg.process_weights_after_loading(lay)
+    ks = k // world
+    x = torch.from_numpy(np.ascontiguousarray(c["x"][:, rank * ks:(rank + 1) * ks])).to(dev, torch.bfloat16)
+    lay.peer_reduce = False
+    y_nccl = lay(x).float().cpu().numpy()
+    lay.peer_reduce = True
+    lay.peer_reduce_min_rows = 1
+    y_peer1 = lay(x).float().cpu().numpy()
+    y_peer2 = lay(x).float().cpu().numpy()          # second call reuses the slots
+    torch.cuda.synchronize()
+    ref = O.row_parallel(c["x"], c["wq"], c["w_scale"], c["input_scale"], c["bias"], world, "fp8_w8a8_static")
+    np.savez(Path(out_dir) / f"r{rank}.npz", nccl=y_nccl, peer1=y_peer1, peer2=y_peer2, ref=ref)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_row_parallel_nccl_and_peer_reduce(tmp_path):
+    import torch.multiprocessing as mp
+    from oracle import fp8_oracle as O
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for rank in range(2):
+        d = np.load(tmp_path / f"r{rank}.npz")
+        for key in ("nccl", "peer1", "peer2"):
+            ok, worst = O.check_close(d[key], d["ref"], ulps=2.0)     # two ranks: two bf16 roundings
+            assert ok, (rank, key, worst)
+        np.testing.assert_array_equal(d["peer1"], d["peer2"])
+    a = np.load(tmp_path / "r0.npz"); b = np.load(tmp_path / "r1.npz")
+    np.testing.assert_array_equal(a["peer1"], b["peer1"])              # every rank ends with the same bits
