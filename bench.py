@@ -52,6 +52,9 @@ for _m in (4096, 16384, 32640):
     WORKLOADS[f"c4_m{_m}"] = ("fp8_w8a8_static", [("qkv", _m, 3584, 4608, "col"), ("o_proj", _m, 3584, 3584, "row"),
                                                   ("gate_up", _m, 3584, 37888, "col"), ("down", _m, 18944, 3584, "row")])
 
+for _m in (256, 1024, 4096):       # W8A16 prefill: weights widened to f16 chunk by chunk + tcgen05 f16 GEMM
+    WORKLOADS[f"c4_w8a16_m{_m}"] = ("fp8_w8a16", [("qkv", _m, 3584, 4608, "col"), ("o_proj", _m, 3584, 3584, "row"),
+                                                  ("gate_up", _m, 3584, 37888, "col"), ("down", _m, 18944, 3584, "row")])
 for _t in (1, 64, 1024, 4096):
     WORKLOADS[f"c5_t{_t}"] = ("moe_w8a8", _t)
 MOE = {"hidden": 2048, "experts": 60, "inter": 1408, "top_k": 4}
@@ -467,8 +470,17 @@ def main():
     for c in range(copies):
         run_pass(c, xs_dev)
     torch.cuda.synchronize()
-    kernels_per_pass = sum(2 if Kn.variant_name(scheme_id, m, *shard_shape(k, n, kind, tp)).startswith("umma") else 1
-                           for _, m, k, n, kind in ops)
+    def launches_of(variant: str) -> int:
+        """Kernel launches one linear call makes, from the variant name the library reports."""
+        if variant.startswith("umma_w8a16_f16"):                 # x -> f16, then (widen weights, GEMM) per chunk
+            return 1 + 2 * int(variant.rsplit("_c", 1)[1])
+        if variant.startswith("umma_w8a8"):                      # activation quantiser + GEMM (+ split-K tail launch)
+            return 3 if "+tail" in variant else 2
+        if variant.startswith("umma_swap_w8a8"):
+            return 2 if variant.endswith("_preq") else 1
+        return 1
+
+    kernels_per_pass = sum(launches_of(Kn.variant_name(scheme_id, m, *shard_shape(k, n, kind, tp))) for _, m, k, n, kind in ops)
 
     # ---- device-resident timing: one CUDA graph per weight copy --------------------------------
     graphs = []
@@ -532,7 +544,8 @@ def main():
 
     # ---- per-shape microseconds and roofline (graph of 20 launches per weight copy) ----------------
     shapes = []
-    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    # W8A8 multiplies e4m3 operands (dense FP8 peak); W8A16's large-M route multiplies f16 operands
+    fp8_peak = 2.0 * peaks["bf16_tflops"] if scheme == "fp8_w8a8_static" else peaks["bf16_tflops"]
     for i, (label, m, k, n, kind) in enumerate(ops):
         kl, nl = shard_shape(k, n, kind, tp)
         x = xs_dev[i]
@@ -591,32 +604,72 @@ def main():
     roofline["algorithmic_bytes"] = algorithmic_bytes(dom["m"], dom["k"], dom["n"])
     roofline["kernel"] = dom["variant"]
     roofline["shape"] = [dom["m"], dom["k"], dom["n"]]
-    roofline["peak_source"] = (f"{peaks['source']}: HBM copy {peaks['hbm_gbs']} GB/s; dense-FP8 peak taken as 2 x "
-                               f"{peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s")
+    roofline["peak_source"] = (f"{peaks['source']}: HBM copy {peaks['hbm_gbs']} GB/s; " +
+                               (f"dense-FP8 peak taken as 2 x {peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s"
+                                if scheme == "fp8_w8a8_static" else
+                                f"tensor peak = {peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s (f16 operands)"))
 
     # ---- end to end through the layer API with host buffers ------------------------------------------
-    host_out = [torch.empty((m, shard_shape(k, n, kind, tp)[1]), dtype=torch.bfloat16).pin_memory()
-                for _, m, k, n, kind in ops]
-    dev_in = [torch.empty_like(x) for x in xs_dev]
+    # Every step copies that step's inputs from pinned host memory, runs the linears through the layer
+    # API and copies every output back to pinned host memory.  Copies and compute run on three streams
+    # (host->device, compute, device->host) chained by events, the largest output first, with two sets of
+    # buffers so that a step's input copies overlap the previous step's output copies (PCIe carries both
+    # directions at once); the timed region ends when the last output of the last step is on the host.
+    NBUF = 2
+    order = sorted(range(len(ops)), key=lambda j: -ops[j][1] * shard_shape(ops[j][2], ops[j][3], ops[j][4], tp)[1])
+    host_out = [[torch.empty((m, shard_shape(k, n, kind, tp)[1]), dtype=torch.bfloat16).pin_memory()
+                 for _, m, k, n, kind in ops] for _ in range(NBUF)]
+    dev_in = [[torch.empty_like(x) for x in xs_dev] for _ in range(NBUF)]
     h2d = sum(h.numel() * 2 for _, h in inputs)
-    d2h = sum(h.numel() * 2 for h in host_out)
+    d2h = sum(h.numel() * 2 for h in host_out[0])
+    s_in, s_comp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_in = [[torch.cuda.Event() for _ in ops] for _ in range(NBUF)]       # input j of buffer set b is on the device
+    ev_used = [[torch.cuda.Event() for _ in ops] for _ in range(NBUF)]     # ... and has been consumed
+    ev_done = [[torch.cuda.Event() for _ in ops] for _ in range(NBUF)]     # output j has been computed
+    ev_host = [[torch.cuda.Event() for _ in ops] for _ in range(NBUF)]     # ... and is on the host
+    seen = [False] * NBUF
 
     def e2e_step(i):
-        for d, (_, h) in zip(dev_in, inputs):
-            d.copy_(h, non_blocking=True)
-        outs = run_pass(i, dev_in)
-        for h, o in zip(host_out, outs):
-            h.copy_(o, non_blocking=True)
+        bset = i % NBUF
+        for j in order:
+            with torch.cuda.stream(s_in):
+                if seen[bset]:
+                    s_in.wait_event(ev_used[bset][j])
+                dev_in[bset][j].copy_(inputs[j][1], non_blocking=True)
+                ev_in[bset][j].record(s_in)
+            with torch.cuda.stream(s_comp):
+                s_comp.wait_event(ev_in[bset][j])
+                o = layers[i % copies][j](dev_in[bset][j])
+                ev_used[bset][j].record(s_comp)
+                ev_done[bset][j].record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[bset][j])
+                host_out[bset][j].copy_(o, non_blocking=True)    # the previous copy into this buffer is ahead in s_out
+                o.record_stream(s_out)
+                ev_host[bset][j].record(s_out)
+        seen[bset] = True
+
+    def e2e_join(ev):
+        """Record `ev` on the output stream once all three streams have drained."""
+        s_out.wait_stream(s_in)
+        s_out.wait_stream(s_comp)
+        ev.record(s_out)
 
     e2e_steps = max(10, min(args.steps, 50))
+    barrier()
     for i in range(3):
         e2e_step(i)
     barrier()
+    # the pipelined path returns what the plain call returns
+    torch.testing.assert_close(host_out[0][order[0]].to(dev), layers[2 % copies][order[0]](xs_dev[order[0]]), rtol=0, atol=0)
+    barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
+    a.record(s_out)
+    s_in.wait_event(a)
+    s_comp.wait_event(a)
     for i in range(e2e_steps):
         e2e_step(i)
-    b.record()
+    e2e_join(b)
     barrier()
     e2e_ms = a.elapsed_time(b) / e2e_steps
     if world > 1:
@@ -648,7 +701,8 @@ def main():
                        "launch": "cuda-graph replay" if use_graph else "eager"},
             "clocks": clocks, "shapes": shapes, "roofline": roofline,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h},
+                    "d2h_bytes_per_step": d2h,
+                    "pipeline": "pinned host buffers; H2D, compute and D2H on three streams, two steps in flight"},
             "gpu_launches": kernels_per_pass * args.steps, "device_status": status,
         }
         if cpu is not None:

@@ -31,6 +31,8 @@ struct Tuning {
     int swap_preq_min_m = -1; // smallest M for which that kernel takes pre-quantised activations
     int w8a16_swap_enable = -1; // 0 keeps W8A16 on the mma.sync streaming kernel for every M
     int w8a16_swap_min_m = -1;
+    int w8a16_umma_min_m = -1;  // smallest M for the dequantise-to-f16 + tcgen05 GEMM route (0 = never)
+    int w8a16_chunk_mb = -1;    // size of the f16 weight chunk that route keeps in L2
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -67,6 +69,59 @@ bool w8a16_swap_eligible(int64_t M) {
     // equal at 32), the tcgen05 kernel from 33 rows (39 vs 67 us at M = 64)
     const int min_m = g_tune.w8a16_swap_min_m >= 0 ? g_tune.w8a16_swap_min_m : 33;
     return g_tune.w8a16_swap_enable != 0 && M >= min_m && M <= 64;
+}
+
+// Large-M W8A16: channel chunks of the weights are widened to f16 into scratch (small enough to stay
+// in L2) and multiplied by the tcgen05 f16 GEMM; below this many rows the 64-row passes of the
+// mma.sync kernel are cheaper than the per-chunk launches.
+bool w8a16_umma_eligible(int64_t M, int64_t K, int64_t N, int64_t ldy, const void* y) {
+    // measured on 3584 -> 37888: 128 rows 237 vs 132 us (passes win), 256 rows 270 vs 261 us (equal;
+    // 32 vs 38 us on 3584 -> 4608), 1024 rows 319 vs 1032 us, 4096 rows 0.90 vs 4.1 ms
+    const int min_m = g_tune.w8a16_umma_min_m >= 0 ? g_tune.w8a16_umma_min_m : 256;
+    return min_m > 0 && M >= min_m && K % 8 == 0 && N % 8 == 0 && ldy % 8 == 0 && aligned16(y);
+}
+
+struct F16Chunks {
+    int64_t chunk_tiles;     // 128-channel tile rows per chunk (even: a chunk is a multiple of 256 channels)
+    int64_t n_chunks;
+    size_t x16_bytes, w16_bytes;
+};
+
+F16Chunks plan_f16_chunks(int64_t M, int64_t K, int64_t N) {
+    F16Chunks c;
+    const int64_t ntiles = fp8lin::pack_ntiles(N);
+    const size_t tile_row_bytes = (size_t)fp8lin::pack_kblocks(K) * 2 * fp8lin::kPackTileBytes;   // f16 bytes of 128 channels
+    const size_t budget = (size_t)(g_tune.w8a16_chunk_mb > 0 ? g_tune.w8a16_chunk_mb : 64) << 20;
+    // Chunks are counted in 256-channel column blocks (the GEMM's widest tile).  Every chunk is its own
+    // GEMM launch of m_tiles x blocks tiles over 148 SMs, so the chunk size decides how many rounds of
+    // tiles the whole call takes: try every size that fits the budget and keep the cheapest, a round
+    // costing one tile's main loop and a chunk a fixed launch/ramp overhead.
+    const int64_t nblocks = (ntiles + 1) / 2;
+    int64_t max_blocks = (int64_t)(budget / (2 * tile_row_bytes));
+    if (max_blocks < 1) max_blocks = 1;
+    if (max_blocks > nblocks) max_blocks = nblocks;
+    const int64_t m_tiles = (M + 127) / 128;
+    const double t_tile = (double)fp8lin::pack_kblocks(K) * 2 * 0.115;     // us per 128x256 tile (64-element K blocks)
+    auto rounds_of = [&](int64_t blocks) -> double {
+        const int64_t tiles = m_tiles * blocks;
+        if (tiles > 74) return (double)((tiles + 147) / 148);
+        int64_t splits = 148 / tiles;                                       // few tiles: cluster split-K
+        if (splits > 8) splits = 8;
+        return 1.0 / (double)splits + 0.15;
+    };
+    double best_cost = 1e30;
+    int64_t best_blocks = max_blocks;
+    for (int64_t b = max_blocks; b >= 1 && b * 4 >= max_blocks; --b) {
+        const int64_t full = nblocks / b, rest = nblocks - full * b;
+        const double cost = (double)full * (rounds_of(b) * t_tile + 8.0) + (rest ? rounds_of(rest) * t_tile + 8.0 : 0.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best_blocks = b; }
+    }
+    const int64_t per = 2 * best_blocks;
+    c.chunk_tiles = per;
+    c.n_chunks = (ntiles + per - 1) / per;
+    c.x16_bytes = align_up((size_t)M * K * 2, 256);
+    c.w16_bytes = (size_t)per * tile_row_bytes;
+    return c;
 }
 
 bool swap_eligible(int64_t M) {
@@ -146,6 +201,9 @@ size_t fp8lin_workspace_bytes(int scheme, int64_t M, int64_t K, int64_t N) {
         UmmaPlan up = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
         size_t u = align_up((size_t)M * K, 256) + up.partial_bytes;
         if (u > body) body = u;
+    } else if (w8a16_umma_eligible(M, K, N, 8, nullptr)) {
+        F16Chunks c = plan_f16_chunks(M, K, N);
+        if (c.x16_bytes + c.w16_bytes > body) body = c.x16_bytes + c.w16_bytes;
     }
     return FP8LIN_WS_HEADER_BYTES + align_up(body, 256);
 }
@@ -183,6 +241,38 @@ int fp8lin_w8a16(const void* x, int64_t ldx, const void* w_nk, const float* w_sc
         const char* why = nullptr;
         cudaError_t e = launch_swap_w8a16(sp, a, x, ldx, (cudaStream_t)stream, &why);
         if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 W8A16 decode kernel launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+        return FP8LIN_OK;
+    }
+    if (w8a16_umma_eligible(M, K, N, ldy, y)) {
+        cudaStream_t st = (cudaStream_t)stream;
+        const F16Chunks c = plan_f16_chunks(M, K, N);
+        WsView ws = ws_view(workspace, workspace_bytes);
+        if (!workspace || ws.body_bytes < c.x16_bytes + c.w16_bytes)
+            return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes",
+                        (size_t)FP8LIN_WS_HEADER_BYTES + c.x16_bytes + c.w16_bytes);
+        unsigned char* x16 = ws.body;
+        unsigned char* w16 = ws.body + c.x16_bytes;
+        cudaError_t e = launch_x_to_f16((const __nv_bfloat16*)x, ldx, x16, M, K, st);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "f16 activation pass launch: %s", cudaGetErrorString(e));
+        const int64_t kb = pack_kblocks(K);
+        for (int64_t ci = 0; ci < c.n_chunks; ++ci) {
+            const int64_t t0 = ci * c.chunk_tiles;
+            const int64_t n0 = t0 * kPackTile;
+            const int64_t nc = (N - n0) < c.chunk_tiles * kPackTile ? (N - n0) : c.chunk_tiles * kPackTile;
+            const int64_t tiles = pack_ntiles(nc);
+            e = launch_dequant_tiles_f16((const unsigned char*)w_nk + (size_t)t0 * kb * kPackTileBytes, w16,
+                                         tiles * kb * kPackTileBytes, st);
+            if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "f16 weight pass launch: %s", cudaGetErrorString(e));
+            UmmaPlan pl = plan_umma(M, 2 * kb * kPackTile, nc, g_tune.umma_bn, g_tune.umma_splits);
+            UmmaArgs a;
+            a.xq = x16; a.w = w16; a.w_scale = w_scale + n0; a.input_scale = nullptr;
+            a.bias = bias ? (const __nv_bfloat16*)bias + n0 : nullptr; a.y = (__nv_bfloat16*)y + n0;
+            a.partial = nullptr; a.counters = ws.counters; a.status = ws.status;
+            a.M = (int)M; a.K = (int)K; a.N = (int)nc; a.ldy = (int)ldy;
+            const char* why = nullptr;
+            e = launch_umma_f16(pl, a, st, &why);
+            if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 f16 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+        }
         return FP8LIN_OK;
     }
     return run_stream(FP8LIN_W8A16, x, ldx, w_nk, w_scale, nullptr, bias, y, ldy, M, K, N, workspace,
@@ -301,12 +391,20 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
     if (scheme == FP8LIN_W8A8_STATIC && M > max_m && N % 8 == 0) {
         UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
         if (pl.tail_tiles) snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s1+tail%dx%d", pl.bn, pl.tail_tiles, pl.tail_splits);
+        else if (pl.narrow_tiles) snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s1+half%d", pl.bn, pl.narrow_tiles);
         else snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s%d", pl.bn, pl.splits);
         return buf;
     }
     if (scheme == FP8LIN_W8A8_STATIC && swap_eligible(M)) {
         SwapPlan pl = plan_swap(M, K, N, g_tune.swap_splits, swap_prequant(M));
         snprintf(buf, sizeof(buf), "umma_swap_w8a8_m%d_s%d%s", pl.mp, pl.splits, pl.preq ? "_preq" : "");
+        return buf;
+    }
+    if (scheme == FP8LIN_W8A16 && w8a16_umma_eligible(M, K, N, 8, nullptr)) {
+        const F16Chunks c = plan_f16_chunks(M, K, N);
+        const int64_t full = c.chunk_tiles * kPackTile < N ? c.chunk_tiles * kPackTile : N;
+        UmmaPlan pl = plan_umma(M, 2 * pack_kblocks(K) * kPackTile, full, g_tune.umma_bn, g_tune.umma_splits);
+        snprintf(buf, sizeof(buf), "umma_w8a16_f16_128x%d_s%d_c%d", pl.bn, pl.splits, (int)c.n_chunks);
         return buf;
     }
     if (scheme == FP8LIN_W8A16 && w8a16_swap_eligible(M)) {
@@ -331,6 +429,8 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "swap_preq_min_m")) g_tune.swap_preq_min_m = value;
     else if (!strcmp(knob, "w8a16_swap_enable")) g_tune.w8a16_swap_enable = value;
     else if (!strcmp(knob, "w8a16_swap_min_m")) g_tune.w8a16_swap_min_m = value;
+    else if (!strcmp(knob, "w8a16_umma_min_m")) g_tune.w8a16_umma_min_m = value;
+    else if (!strcmp(knob, "w8a16_chunk_mb")) g_tune.w8a16_chunk_mb = value;
     else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;

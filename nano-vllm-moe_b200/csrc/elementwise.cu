@@ -81,6 +81,79 @@ cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t sl
     return cudaGetLastError();
 }
 
+// x (bf16, row pitch ldx) -> f16 [M][K] contiguous, round to nearest: the "A" operand of the
+// large-M W8A16 GEMM.  Eight elements per thread and iteration.
+__global__ void __launch_bounds__(256)
+x_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, __half* __restrict__ x16, int64_t M, int64_t K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t vec_per_row = K / 8;
+    const int64_t total = M * vec_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / vec_per_row;
+        const int64_t c = (i - r * vec_per_row) * 8;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + r * ldx + c));
+        *reinterpret_cast<uint4*>(x16 + r * K + c) = bf16x8_to_f16x8(v);
+    }
+}
+
+cudaError_t launch_x_to_f16(const __nv_bfloat16* x, int64_t ldx, void* x16, int64_t M, int64_t K, cudaStream_t stream) {
+    const int64_t total = M * (K / 8);
+    if (total == 0) return cudaSuccess;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.numAttrs = pdl_attribute(attr);
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, x_to_f16_kernel, x, ldx, (__half*)x16, M, K);
+}
+
+// Packed e4m3 tiles (128 channels x 128 K bytes, 16 KiB each) -> packed f16 tiles (128 channels x 64
+// elements = 128 bytes per row, 16 KiB each): source tile t becomes destination tiles 2t and 2t+1, so a
+// channel block keeps its tiles consecutive along K.  The conversion is exact (every e4m3 value is an
+// f16 value); the per-channel scale stays in the GEMM's epilogue.  A thread reads 16 bytes and writes 32.
+__global__ void __launch_bounds__(256)
+dequant_tiles_f16_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, int64_t src_bytes) {
+    pdl_launch_dependents();
+    pdl_wait();                    // the GEMM before this pass may still read the destination
+    const int64_t total = src_bytes / 16;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t off = i * 16;
+        const int64_t tile = off >> 14;
+        const int within = (int)(off & 16383);
+        const int r = within >> 7;
+        const int c = (within & 127) >> 4;            // 16-byte piece of the 128-byte row
+        const uint4 v = ld_stream16(src + off);
+        uint4 lo, hi;
+        lo.x = cvt_e4m3x2_to_f16x2((uint16_t)(v.x & 0xffffu)); lo.y = cvt_e4m3x2_to_f16x2((uint16_t)(v.x >> 16));
+        lo.z = cvt_e4m3x2_to_f16x2((uint16_t)(v.y & 0xffffu)); lo.w = cvt_e4m3x2_to_f16x2((uint16_t)(v.y >> 16));
+        hi.x = cvt_e4m3x2_to_f16x2((uint16_t)(v.z & 0xffffu)); hi.y = cvt_e4m3x2_to_f16x2((uint16_t)(v.z >> 16));
+        hi.z = cvt_e4m3x2_to_f16x2((uint16_t)(v.w & 0xffffu)); hi.w = cvt_e4m3x2_to_f16x2((uint16_t)(v.w >> 16));
+        uint4* out = reinterpret_cast<uint4*>(dst + ((2 * tile + (c >> 2)) << 14) + r * 128 + (c & 3) * 32);
+        out[0] = lo;
+        out[1] = hi;
+    }
+}
+
+cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_t src_bytes, cudaStream_t stream) {
+    const int64_t total = src_bytes / 16;
+    if (total == 0) return cudaSuccess;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.numAttrs = pdl_attribute(attr);
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, dequant_tiles_f16_kernel, src, (unsigned char*)dst, src_bytes);
+}
+
 // Pack e4m3 weight bytes into the tiled layout (see pack_offset).  One CTA fills one
 // 128 x 128 tile through shared memory; `src_is_kn` selects the source orientation:
 // [K][N] (the reference's runtime buffer) or [N][K] (the checkpoint's layout).

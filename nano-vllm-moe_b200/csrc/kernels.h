@@ -74,6 +74,7 @@ struct UmmaPlan {
     int grid;          // persistent CTAs
     int tail_tiles;    // last tiles finished by a second, cluster split-K launch (0 = none)
     int tail_splits, tail_kps;
+    int narrow_tiles;  // last tiles of a 256-wide persistent launch run as two 128-column halves each (0 = none)
     size_t partial_bytes;
 };
 
@@ -83,6 +84,11 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
 // output box to each of dst_ptrs[0..n_dst) (bf16 [M][ld_dst] matrices; may be peer-GPU memory).
 cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why,
                              int n_dst = 0, void* const* dst_ptrs = nullptr, int64_t ld_dst = 0);
+// Large-M W8A16: the same GEMM on f16 operands.  args.xq = activations as f16 [M][K] (launch_x_to_f16),
+// args.w = f16 weight tiles of the channels [0, N) (launch_dequant_tiles_f16), args.input_scale = nullptr.
+cudaError_t launch_umma_f16(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why);
+cudaError_t launch_x_to_f16(const __nv_bfloat16* x, int64_t ldx, void* x16, int64_t M, int64_t K, cudaStream_t stream);
+cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_t src_bytes, cudaStream_t stream);
 cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t slot_stride, __nv_bfloat16* y, int64_t ldy,
                              int64_t M, int64_t N, int64_t ld_slot, cudaStream_t stream);
 

@@ -75,6 +75,14 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
 }
 
+// Same, f16 operands from shared memory (K = 16 elements = 32 bytes per instruction).
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
+}
+
 // 32 lanes x 32 columns of fp32 from TMEM (lane i of the warp reads TMEM lane base+i); no wait.
 __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* v) {
     asm volatile(

@@ -52,11 +52,16 @@ struct UmmaCfg {
     static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 5 : 8);   // ring + staging + statics <= 227 KB
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kRingBytes = kStages * kStageBytes;
-    // columns per TMEM read / staging box of an epilogue warp (the 256-wide tile leaves
-    // shared memory for 32-column boxes only)
-    static constexpr int kPiece = BN == 256 ? 32 : (BN / 2 < 64 ? BN / 2 : 64);
+    // columns per TMEM read / staging box of an epilogue warp: 64 bf16 = one full 128-byte line per
+    // row (32-column boxes wrote every line in two halves, and DRAM write traffic was 2.8x the output)
+    static constexpr int kPiece = BN / 2 < 64 ? BN / 2 : 64;
     static constexpr int kBoxBytes = 32 * kPiece * 2;
-    static constexpr int kStagingBytes = kEpiWarps * kBoxBytes; // one 32-row box per epilogue warp
+    // One 32-row staging box per epilogue warp; the 256-wide tile has one per warp PAIR (the two warps that
+    // own the same 32 rows fill the two 32-column halves of a 64-column box).  With a box per warp the CTA
+    // came within 400 bytes of the SM's shared memory, no CTA of the preceding kernel could stay resident
+    // beside it, and the overlap of programmatic dependent launch was lost (measured 2-8 % per call).
+    static constexpr bool kPairBox = BN == 256;
+    static constexpr int kStagingBytes = (kPairBox ? kEpiWarps / 2 : kEpiWarps) * kBoxBytes;
     static constexpr int kSmemBytes = kRingBytes + kStagingBytes + 1024;
     // split-K: fp32 tile parked over the (then idle) ring; 16 bytes of padding per row
     // spread consecutive rows over the banks
@@ -67,7 +72,7 @@ struct UmmaCfg {
 template <int BN>
 __host__ __device__ constexpr uint32_t make_idesc() {
     return (1u << 4)                     // accumulator fp32
-           | (0u << 7) | (0u << 10)      // A, B = e4m3
+           | (0u << 7) | (0u << 10)      // A, B = e4m3 (kind::f8f6f4) or f16 (kind::f16): code 0 in both
            | (0u << 15) | (0u << 16)     // A, B K-major
            | ((uint32_t)(BN >> 3) << 17) // N
            | ((uint32_t)(kBM >> 4) << 24);
@@ -81,7 +86,11 @@ struct OutMaps {
 
 struct UmmaSched {
     int m_tiles, n_tiles, splits, kblocks_total, kblocks_per_split;
-    int tile_base, total_work;      // this launch covers tiles [tile_base, total_work)
+    int tile_base, total_work;      // this launch covers work items [tile_base, total_work)
+    // Work items below narrow_from are whole tiles (item index = tile index).  From narrow_from on
+    // (256-wide persistent launches only) two consecutive items are the 128-column halves of one tile,
+    // so that a last round of r <= 74 tiles keeps 2r SMs busy for half as long.
+    int narrow_from;
 };
 
 // tile index -> (tile_m, tile_n); 8 M-tiles share a weight column block before the next
@@ -97,9 +106,36 @@ __device__ __forceinline__ void decode_tile(const UmmaSched& s, int tile, int& t
     tn = r / gsize;
 }
 
-template <int BN, bool kSplit>
+struct WorkItem {
+    int tm;      // tile row
+    int n0;      // first output channel
+    int bn;      // channels of this item (BN, or 128 for a half tile)
+};
+
+template <int BN, bool kNarrow>
+__device__ __forceinline__ WorkItem decode_work(const UmmaSched& s, int w) {
+    WorkItem it;
+    int tile = w, part = 0;
+    it.bn = BN;
+    if (kNarrow && w >= s.narrow_from) {
+        const int u = w - s.narrow_from;
+        tile = s.narrow_from + (u >> 1);
+        part = u & 1;
+        it.bn = 128;
+    }
+    int tn;
+    decode_tile(s, tile, it.tm, tn);
+    it.n0 = tn * BN + part * 128;
+    return it;
+}
+
+// kF16 = false: e4m3 x e4m3 (W8A8; A = quantised activations, B = packed weights).
+// kF16 = true:  f16 x f16 (large-M W8A16; A = activations converted to f16, B = weight tiles widened to
+// f16 by dequant_tiles_f16_kernel into scratch).  A K block is 128 bytes of a row in both cases.
+// kNarrow (256-wide persistent launches only): the launch ends with half-width work items.
+template <int BN, bool kSplit, bool kF16 = false, bool kNarrow = false>
 __global__ void __launch_bounds__(kThreads, 1)
-umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ OutMaps outs, UmmaArgs p, UmmaSched sched) {
     using Cfg = UmmaCfg<BN>;
     constexpr int S = Cfg::kStages;
@@ -110,8 +146,11 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __shared__ __align__(8) uint64_t bar_tempty[2];
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile int s_abort;
-    __shared__ __align__(16) float s_scale[2][BN];   // in_scale * w_scale[n] for the tile in flight
-    __shared__ __align__(16) float s_bias[2][BN];
+    // in_scale * w_scale[n] and bias[n] of the tile whose epilogue runs (single copy, bias kept as
+    // bf16: the 256-wide tile needs the shared memory for its 4 KB staging boxes); the next tile's
+    // values wait in registers
+    __shared__ __align__(16) float s_scale[BN];
+    __shared__ __align__(16) __nv_bfloat16 s_bias[BN];
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5;
@@ -144,19 +183,22 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t it = 0;
             bool ok = true;
             bool waited = false;      // weight tiles of the first ring pass go out before the predecessor is done
+            if (kF16) pdl_wait();     // ... unless the predecessor is the pass that writes the f16 weight tiles
             for (int w = first_work; w < sched.total_work && ok; w += work_step) {
-                int tm, tn;
-                decode_tile(sched, w, tm, tn);
+                const WorkItem wk = decode_work<BN, kNarrow>(sched, w);
+                const int tm = wk.tm;
+                const int nsub = kNarrow ? (wk.bn >> 7) : (BN + 127) / 128;  // 128-row weight boxes per K block
+                const uint32_t stage_tx = kNarrow ? (uint32_t)(Cfg::kABytes + wk.bn * kBK) : (uint32_t)Cfg::kStageBytes;
                 const int kb0 = split_rank * sched.kblocks_per_split;
                 const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
                 if (!waited) {
                     const int first_kb = min(kb1 - kb0, S);
                     for (int i = 0; i < first_kb; ++i) {
                         const uint32_t full = smem_u32(&bar_full[i]);
-                        mbar_expect_tx(full, Cfg::kStageBytes);
+                        mbar_expect_tx(full, stage_tx);
 #pragma unroll
-                        for (int sub = 0; sub < (BN + 127) / 128; ++sub) {
-                            const int n_sub = tn * BN + sub * 128;
+                        for (int sub = 0; sub < nsub; ++sub) {
+                            const int n_sub = wk.n0 + sub * 128;
                             const int wrow = ((n_sub >> 7) * sched.kblocks_total + kb0 + i) * 128 + (n_sub & 127);
                             tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kABytes + sub * 128 * kBK, &tmap_b, 0, wrow, full);
                         }
@@ -175,14 +217,14 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         s_abort = 1; ok = false; break;
                     }
                     const uint32_t full = smem_u32(&bar_full[st]);
-                    mbar_expect_tx(full, Cfg::kStageBytes);
+                    mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_base + st * Cfg::kStageBytes;
                     tma_load_2d(sa, &tmap_a, kb * kBK, tm * kBM, full);
                     // packed weights: the tile of channel block cb and K block kb is rows
                     // [(cb*KB + kb)*128, +128) of a [tiles*128][128-byte] matrix
 #pragma unroll
-                    for (int sub = 0; sub < (BN + 127) / 128; ++sub) {
-                        const int n_sub = tn * BN + sub * 128;
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const int n_sub = wk.n0 + sub * 128;
                         const int wrow = ((n_sub >> 7) * sched.kblocks_total + kb) * 128 + (n_sub & 127);
                         tma_load_2d(sa + Cfg::kABytes + sub * 128 * kBK, &tmap_b, 0, wrow, full);
                     }
@@ -197,7 +239,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc<BN>();
+            constexpr uint32_t idesc_full = make_idesc<BN>();
             uint32_t it = 0;
             int tl = 0;
             bool ok = true;
@@ -206,6 +248,9 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
                 const int as = tl & 1;
                 const uint32_t aph = (tl >> 1) & 1;
+                // a half tile is the same instruction with N = 128
+                const uint32_t idesc = (kNarrow && w >= sched.narrow_from)
+                                           ? ((idesc_full & ~(0x3fu << 17)) | ((128u >> 3) << 17)) : idesc_full;
                 if (s_abort || !mbar_wait(smem_u32(&bar_tempty[as]), aph ^ 1, p.status, kDevTimeoutTmemEmpty)) {
                     s_abort = 1; ok = false; break;
                 }
@@ -224,7 +269,8 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                     for (int k = 0; k < kBK / 32; ++k) {
                         // advance 32 bytes along K inside the 128-byte swizzle span: +2 in 16-byte units
-                        umma_f8(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if (kF16) umma_f16_ss(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        else umma_f8(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&bar_empty[st]));
                 }
@@ -239,77 +285,163 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int q = warp & 3;
         const int h = ew >> 2;
         const int et = threadIdx.x - 64;                            // 0..255 among the epilogue threads
-        constexpr int kHalf = BN / 2;
         constexpr int kPiece = Cfg::kPiece;
-        const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
+        const float in_scale = p.input_scale ? fmaxf(__ldg(p.input_scale), 1e-12f) : 1.f;   // W8A16: weights' scale only
         const uint32_t box = smem_base + Cfg::kRingBytes + ew * Cfg::kBoxBytes;
         const uint32_t row_off = lane * (kPiece * 2);
         const uint32_t sw = kPiece == 64 ? (lane & 7) : ((lane >> 1) & 3);   // 128-byte / 64-byte swizzle
         int tl = 0;
         bool ok = true;
+        static_assert(BN <= kEpiWarps * 32, "one column per epilogue thread");
+        float next_scale = 0.f;
+        __nv_bfloat16 next_bias = __float2bfloat16(0.f);
+        auto fetch_columns = [&](int work) {            // thread et holds column et of that tile
+            const WorkItem f = decode_work<BN, kNarrow>(sched, work);
+            const int n = f.n0 + et;
+            const bool in = et < f.bn && n < p.N;
+            next_scale = in ? in_scale * __ldg(p.w_scale + n) : 0.f;
+            next_bias = (in && p.bias) ? p.bias[n] : __float2bfloat16(0.f);
+        };
+        if (first_work < sched.total_work) fetch_columns(first_work);
         for (int w = first_work; w < sched.total_work && ok; w += work_step, ++tl) {
-            int tm, tn;
-            decode_tile(sched, w, tm, tn);
+            const WorkItem wk = decode_work<BN, kNarrow>(sched, w);
+            const int tm = wk.tm;
             const int as = tl & 1;
             const uint32_t aph = (tl >> 1) & 1;
-            const int n0 = tn * BN;
-            // stage this tile's per-column multiplier and bias while the main loop runs
-            for (int i = et; i < BN; i += kEpiWarps * 32) {
-                const int n = n0 + i;
-                s_scale[as][i] = n < p.N ? in_scale * __ldg(p.w_scale + n) : 0.f;
-                s_bias[as][i] = (n < p.N && p.bias) ? __bfloat162float(p.bias[n]) : 0.f;
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            // (no s_abort shortcut here: the epilogue warps must take the same branch
-            //  because they meet at the named barrier above on the next tile)
-            if (!mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull)) {
-                s_abort = 1; ok = false; break;
+            const int n0 = wk.n0;
+            const int half_cols = kNarrow ? (wk.bn >> 1) : BN / 2;   // columns of this warp's half of the item
+            // every epilogue warp is done with the previous tile's multipliers before they are replaced
+            if (tl > 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (et < BN) { s_scale[et] = next_scale; s_bias[et] = next_bias; }
+            // the loads for the tile after this one land while this tile's epilogue runs
+            if (w + work_step < sched.total_work) fetch_columns(w + work_step);
+            if (kSplit) {
+                // one tile per CTA: nothing after this loop meets at a named barrier, so each warp may give
+                // up on its own, and the barrier stays off the path between the last MMA and the reduction
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (!mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull)) {
+                    s_abort = 1; ok = false; break;
+                }
+            } else {
+                const bool arrived = mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull);
+                // One barrier makes the multipliers visible and takes the vote: if the wait ran out in any
+                // warp, every epilogue warp leaves here together (they meet at named barriers again on the
+                // next tile, so they must agree).
+                uint32_t any_failed;
+                asm volatile(
+                    "{\n .reg .pred pin, pout;\n setp.ne.b32 pin, %1, 0;\n"
+                    " barrier.cta.red.or.pred pout, 1, 256, pin;\n selp.u32 %0, 1, 0, pout;\n}"
+                    : "=r"(any_failed) : "r"(arrived ? 0u : 1u) : "memory");
+                if (any_failed) { s_abort = 1; ok = false; break; }
             }
             tc_fence_after();
             const int row0 = tm * kBM + q * 32;
-            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + h * kHalf;
-
+            if (Cfg::kPairBox && !kSplit) {
+                // Piece = 64 columns of the item; warp h converts columns [32h, 32h + 32) of it into its half
+                // of the pair's box, warp 0 of the pair issues the store.
+                const int bn_cur = kNarrow ? wk.bn : BN;
+                const uint32_t pbox = smem_base + Cfg::kRingBytes + q * Cfg::kBoxBytes;
+                const uint32_t t_pair = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + h * 32;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kHalf; c0 += kPiece) {
-                const int col = h * kHalf + c0;                      // first column of this piece inside the tile
-                if (n0 + col >= p.N) break;                          // uniform: the rest is past N
-                uint32_t v[kPiece];
-                __syncwarp();
-                tmem_ld32_nowait(t_addr + c0, v);
-                if (kPiece == 64) tmem_ld32_nowait(t_addr + c0 + 32, v + 32);
-                tmem_ld_wait();
-                if (!kSplit) {
-                    uint32_t o[kPiece / 2];
-#pragma unroll
-                    for (int j = 0; j < kPiece; j += 4) {
-                        const float4 sc = *reinterpret_cast<const float4*>(&s_scale[as][col + j]);
-                        const float4 bi = *reinterpret_cast<const float4*>(&s_bias[as][col + j]);
-                        o[j / 2] = pack_bf16x2(fmaf(__uint_as_float(v[j]), sc.x, bi.x), fmaf(__uint_as_float(v[j + 1]), sc.y, bi.y));
-                        o[j / 2 + 1] = pack_bf16x2(fmaf(__uint_as_float(v[j + 2]), sc.z, bi.z), fmaf(__uint_as_float(v[j + 3]), sc.w, bi.w));
-                    }
-                    // the previous store out of this box must have finished reading it
-                    if (lane == 0) tma_store_wait_read();
+                for (int col = 0; col < bn_cur; col += 64) {
+                    if (n0 + col >= p.N) break;                      // same for both warps of the pair
+                    uint32_t v[32];
                     __syncwarp();
+                    tmem_ld32_nowait(t_pair + col, v);
+                    tmem_ld_wait();
+                    uint32_t o[16];
 #pragma unroll
-                    for (int j = 0; j < kPiece / 8; ++j) {
-                        const uint32_t dst = box + row_off + (((uint32_t)j ^ sw) << 4);
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 sc = *reinterpret_cast<const float4*>(&s_scale[col + h * 32 + j]);
+                        const uint2 bb = *reinterpret_cast<const uint2*>(&s_bias[col + h * 32 + j]);     // four bf16
+                        o[j / 2] = pack_bf16x2(fmaf(__uint_as_float(v[j]), sc.x, __uint_as_float(bb.x << 16)),
+                                               fmaf(__uint_as_float(v[j + 1]), sc.y, __uint_as_float(bb.x & 0xffff0000u)));
+                        o[j / 2 + 1] = pack_bf16x2(fmaf(__uint_as_float(v[j + 2]), sc.z, __uint_as_float(bb.y << 16)),
+                                                   fmaf(__uint_as_float(v[j + 3]), sc.w, __uint_as_float(bb.y & 0xffff0000u)));
+                    }
+                    // the pair's previous store must have finished reading the box
+                    if (h == 0 && lane == 0) tma_store_wait_read();
+                    asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t dst = pbox + lane * 128 + (((uint32_t)(h * 4 + j) ^ (uint32_t)(lane & 7)) << 4);
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[4 * j]), "r"(o[4 * j + 1]),
                                      "r"(o[4 * j + 2]), "r"(o[4 * j + 3]) : "memory");
                     }
+                    fence_async_smem();
+                    asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+                    if (h == 0 && lane == 0) {
+                        // one store per destination: the local output, or (row-parallel scatter) this
+                        // rank's slot in every rank's buffer, peers reached over NVLink
+                        for (int d = 0; d < outs.n; ++d) tma_store_2d(&outs.m[d], pbox, n0 + col, row0);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
+                continue;
+            }
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + h * half_cols;
+
+#pragma unroll 1
+            for (int c0 = 0; c0 < half_cols; c0 += kPiece) {
+                const int col = h * half_cols + c0;                      // first column of this piece inside the tile
+                if (n0 + col >= p.N) break;                          // uniform: the rest is past N
+                if (kSplit) {
+                    // park the raw fp32 accumulators in this CTA's shared memory (over the idle ring); this
+                    // is on the critical path of a one-tile CTA, so all TMEM loads of the piece go out together
+                    uint32_t v[kPiece];
+                    __syncwarp();
+                    tmem_ld32_nowait(t_addr + c0, v);
+                    if (kPiece == 64) tmem_ld32_nowait(t_addr + c0 + 32, v + 32);
+                    tmem_ld_wait();
+                    const uint32_t dst0 = smem_base + (uint32_t)(q * 32 + lane) * Cfg::kPartPitch + (uint32_t)col * 4;
+#pragma unroll
+                    for (int j = 0; j < kPiece; j += 4) {
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 4), "r"(v[j]), "r"(v[j + 1]),
+                                     "r"(v[j + 2]), "r"(v[j + 3]) : "memory");
+                    }
+                    continue;
+                }
+                // A piece (one staging box, one TMA store) is converted 32 columns at a time: registers
+                // for 32 accumulators only, and the store still writes whole 128-byte lines.
+#pragma unroll
+                for (int sp = 0; sp < kPiece / 32; ++sp) {
+                    uint32_t v[32];
+                    __syncwarp();
+                    tmem_ld32_nowait(t_addr + c0 + sp * 32, v);
+                    tmem_ld_wait();
+                    {
+                        uint32_t o[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 sc = *reinterpret_cast<const float4*>(&s_scale[col + sp * 32 + j]);
+                            const uint2 bb = *reinterpret_cast<const uint2*>(&s_bias[col + sp * 32 + j]);     // four bf16
+                            o[j / 2] = pack_bf16x2(fmaf(__uint_as_float(v[j]), sc.x, __uint_as_float(bb.x << 16)),
+                                                   fmaf(__uint_as_float(v[j + 1]), sc.y, __uint_as_float(bb.x & 0xffff0000u)));
+                            o[j / 2 + 1] = pack_bf16x2(fmaf(__uint_as_float(v[j + 2]), sc.z, __uint_as_float(bb.y << 16)),
+                                                       fmaf(__uint_as_float(v[j + 3]), sc.w, __uint_as_float(bb.y & 0xffff0000u)));
+                        }
+                        if (sp == 0) {
+                            // the previous store out of this box must have finished reading it
+                            if (lane == 0) tma_store_wait_read();
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t dst = box + row_off + (((uint32_t)(sp * 4 + j) ^ sw) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[4 * j]), "r"(o[4 * j + 1]),
+                                         "r"(o[4 * j + 2]), "r"(o[4 * j + 3]) : "memory");
+                        }
+                    }
+                }
+                if (!kSplit) {
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {
                         // one store per destination: the local output, or (row-parallel scatter) this
                         // rank's slot in every rank's buffer, peers reached over NVLink
                         for (int d = 0; d < outs.n; ++d) tma_store_2d(&outs.m[d], box, n0 + col, row0);
-                    }
-                } else {
-                    // park the raw fp32 accumulators in this CTA's shared memory (over the idle ring)
-                    const uint32_t dst0 = smem_base + (uint32_t)(q * 32 + lane) * Cfg::kPartPitch + (uint32_t)col * 4;
-#pragma unroll
-                    for (int j = 0; j < kPiece; j += 4) {
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 4), "r"(v[j]), "r"(v[j + 1]),
-                                     "r"(v[j + 2]), "r"(v[j + 3]) : "memory");
                     }
                 }
             }
@@ -349,11 +481,11 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int s = 0; s < 8; ++s) { a.x += u[s].x; a.y += u[s].y; a.z += u[s].z; a.w += u[s].w; }
-            const float4 sc = *reinterpret_cast<const float4*>(&s_scale[0][c]);
-            const float4 bi = *reinterpret_cast<const float4*>(&s_bias[0][c]);
+            const float4 sc = *reinterpret_cast<const float4*>(&s_scale[c]);
+            const uint2 bb = *reinterpret_cast<const uint2*>(&s_bias[c]);
             uint2 out;
-            out.x = pack_bf16x2(fmaf(a.x, sc.x, bi.x), fmaf(a.y, sc.y, bi.y));
-            out.y = pack_bf16x2(fmaf(a.z, sc.z, bi.z), fmaf(a.w, sc.w, bi.w));
+            out.x = pack_bf16x2(fmaf(a.x, sc.x, __uint_as_float(bb.x << 16)), fmaf(a.y, sc.y, __uint_as_float(bb.x & 0xffff0000u)));
+            out.y = pack_bf16x2(fmaf(a.z, sc.z, __uint_as_float(bb.y << 16)), fmaf(a.w, sc.w, __uint_as_float(bb.y & 0xffff0000u)));
             *reinterpret_cast<uint2*>(p.y + (size_t)row * p.ldy + n) = out;
         }
         cluster_sync_all();                                   // nobody exits while a peer still reads its tile
@@ -478,8 +610,8 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
         const long work = tiles * splits;
         long waves = (work + 147) / 148;
         if (splits > 1) {
-            const void* kern = bn == 256 ? (const void*)umma_w8a8_kernel<256, true>
-                             : bn == 128 ? (const void*)umma_w8a8_kernel<128, true> : (const void*)umma_w8a8_kernel<64, true>;
+            const void* kern = bn == 256 ? (const void*)umma_gemm_kernel<256, true>
+                             : bn == 128 ? (const void*)umma_gemm_kernel<128, true> : (const void*)umma_gemm_kernel<64, true>;
             const size_t smem = bn == 256 ? UmmaCfg<256>::kSmemBytes : bn == 128 ? UmmaCfg<128>::kSmemBytes : UmmaCfg<64>::kSmemBytes;
             int slots = max_active_clusters(kern, kThreads, smem, splits);
             if (slots < 1) slots = 1;
@@ -488,6 +620,8 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
         double rounds = (double)waves;
         if (splits == 1 && force_splits <= 0 && kblocks >= 64 && tiles > 148 && tiles % 148 != 0 && tiles % 148 <= 74)
             rounds = (double)(tiles / 148) + 0.4;      // the last partial round goes to the split-K tail launch
+        else if (bn == 256 && splits == 1 && force_splits <= 0 && tiles > 148 && tiles % 148 != 0 && tiles % 148 <= 74)
+            rounds = (double)(tiles / 148) + 0.62;     // ... or runs as half-width work items
         // main loop + fixed per-tile prologue/epilogue; split-K pays one cluster reduction
         const double cost = rounds * (kps * unit[i] + 3.0 * unit[i]) + (splits > 1 ? 2.0 : 0.0);
         if (cost < best_cost) {
@@ -501,7 +635,7 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
     // Wave quantisation: a persistent launch over q*148 + r tiles runs q + 1 rounds even when r is
     // small.  Then the last r tiles go to a second, cluster split-K launch (r * s CTAs <= 148) that
     // finishes them in about 1/s of a round.
-    best.tail_tiles = 0; best.tail_splits = 1; best.tail_kps = 0;
+    best.tail_tiles = 0; best.tail_splits = 1; best.tail_kps = 0; best.narrow_tiles = 0;
     const long tiles = (long)best.m_tiles * best.n_tiles;
     if (force_splits <= 0 && best.splits == 1 && tiles > 148 && kblocks >= 64) {   // a round must outlast a launch
         const int r = (int)(tiles % 148);
@@ -510,8 +644,8 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
             if (s > 8) s = 8;
             while (s > 1 && kblocks / s < 2) --s;
             if (s > 1) {
-                const void* kern = best.bn == 256 ? (const void*)umma_w8a8_kernel<256, true>
-                                 : best.bn == 128 ? (const void*)umma_w8a8_kernel<128, true> : (const void*)umma_w8a8_kernel<64, true>;
+                const void* kern = best.bn == 256 ? (const void*)umma_gemm_kernel<256, true>
+                                 : best.bn == 128 ? (const void*)umma_gemm_kernel<128, true> : (const void*)umma_gemm_kernel<64, true>;
                 const size_t smem = best.bn == 256 ? UmmaCfg<256>::kSmemBytes : best.bn == 128 ? UmmaCfg<128>::kSmemBytes : UmmaCfg<64>::kSmemBytes;
                 while (s > 1 && max_active_clusters(kern, kThreads, smem, s) < r) --s;
             }
@@ -521,15 +655,22 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
             }
         }
     }
+    // Short K: a second launch costs more than it saves; the last r <= 74 tiles of a 256-wide plan are
+    // instead cut into 2r half-width work items of the same persistent launch.
+    if (force_splits <= 0 && best.bn == 256 && best.splits == 1 && best.tail_tiles == 0 && tiles > 148) {
+        const int r = (int)(tiles % 148);
+        if (r > 0 && r <= 74) best.narrow_tiles = r;
+    }
     return best;
 }
 
-template <int BN, bool kSplit>
+template <int BN, bool kSplit, bool kF16, bool kNarrow = false>
 static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb,
                              const OutMaps& ty, cudaStream_t stream, int tile_base, int tile_end, int splits, int kps,
-                             int grid) {
+                             int grid, int narrow_tiles) {
     using Cfg = UmmaCfg<BN>;
-    auto kern = umma_w8a8_kernel<BN, kSplit>;
+    static_assert(!kNarrow || (BN == 256 && !kSplit), "half-width items exist in the 256-wide persistent kernel only");
+    auto kern = umma_gemm_kernel<BN, kSplit, kF16, kNarrow>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -538,8 +679,11 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     }
     UmmaSched s;
     s.m_tiles = pl.m_tiles; s.n_tiles = pl.n_tiles; s.splits = splits;
-    s.kblocks_total = (a.K + kBK - 1) / kBK; s.kblocks_per_split = kps;
-    s.tile_base = tile_base; s.total_work = tile_end;
+    // f16: every packed e4m3 tile became two f16 tiles, so the K-block count is even; a last block
+    // past the end of x reads zeros from the tensor map's out-of-bounds fill
+    s.kblocks_total = kF16 ? 2 * (int)pack_kblocks(a.K) : (a.K + kBK - 1) / kBK; s.kblocks_per_split = kps;
+    s.tile_base = tile_base; s.total_work = tile_end + narrow_tiles;      // r tiles become 2r items
+    s.narrow_from = tile_end - narrow_tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kThreads);
@@ -559,13 +703,14 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s);
 }
 
-cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why,
-                             int n_dst, void* const* dst_ptrs, int64_t ld_dst) {
+static cudaError_t launch_umma(bool f16, const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why,
+                               int n_dst, void* const* dst_ptrs, int64_t ld_dst) {
     CUtensorMap ta, tb;
     OutMaps ty;
-    const uint32_t piece = pl.bn == 256 ? 32 : (pl.bn / 2 < 64 ? pl.bn / 2 : 64);
-    bool ok = encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K, kBM) &&
-              encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128,
+    const uint32_t piece = pl.bn / 2 < 64 ? pl.bn / 2 : 64;      // UmmaCfg<BN>::kPiece
+    const uint64_t esz = f16 ? 2 : 1;                            // the operand matrices are described in bytes
+    bool ok = encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K * esz, kBM) &&
+              encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * esz * 128), 128,
                            (uint32_t)(pl.bn < 128 ? pl.bn : 128));
     if (n_dst <= 0) {
         ty.n = 1;
@@ -585,22 +730,38 @@ cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t
     }
     const int tiles = pl.m_tiles * pl.n_tiles;
     const int main_tiles = tiles - pl.tail_tiles;
-    auto go = [&](bool split, int base, int end, int splits, int kps, int grid) -> cudaError_t {
+    auto go = [&](bool split, int base, int end, int splits, int kps, int grid, int narrow = 0) -> cudaError_t {
+#define FP8LIN_GO(BN_, SPLIT_, F16_) launch_bn<BN_, SPLIT_, F16_>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow)
+#define FP8LIN_GO_BN(BN_) (f16 ? (split ? FP8LIN_GO(BN_, true, true) : FP8LIN_GO(BN_, false, true)) \
+                               : (split ? FP8LIN_GO(BN_, true, false) : FP8LIN_GO(BN_, false, false)))
+        if (narrow > 0)       // (only set for 256-wide non-split plans)
+            return f16 ? launch_bn<256, false, true, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow)
+                       : launch_bn<256, false, false, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow);
         switch (pl.bn) {
-            case 256: return split ? launch_bn<256, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid)
-                                   : launch_bn<256, false>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid);
-            case 128: return split ? launch_bn<128, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid)
-                                   : launch_bn<128, false>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid);
-            case 64: return split ? launch_bn<64, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid)
-                                  : launch_bn<64, false>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid);
+            case 256: return FP8LIN_GO_BN(256);
+            case 128: return FP8LIN_GO_BN(128);
+            case 64: return FP8LIN_GO_BN(64);
         }
+#undef FP8LIN_GO_BN
+#undef FP8LIN_GO
         if (why) *why = "unsupported tile width";
         return cudaErrorInvalidValue;
     };
     if (pl.splits > 1) return go(true, 0, tiles, pl.splits, pl.kblocks_per_split, pl.grid);
-    cudaError_t e = go(false, 0, main_tiles, 1, pl.kblocks_per_split, main_tiles < 148 ? main_tiles : 148);
+    const int narrow = pl.bn == 256 && pl.tail_tiles == 0 ? pl.narrow_tiles : 0;
+    const int main_work = main_tiles + narrow;
+    cudaError_t e = go(false, 0, main_tiles, 1, pl.kblocks_per_split, main_work < 148 ? main_work : 148, narrow);
     if (e != cudaSuccess || pl.tail_tiles == 0) return e;
     return go(true, main_tiles, tiles, pl.tail_splits, pl.tail_kps, pl.tail_tiles * pl.tail_splits);
+}
+
+cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why,
+                             int n_dst, void* const* dst_ptrs, int64_t ld_dst) {
+    return launch_umma(false, pl, a, stream, why, n_dst, dst_ptrs, ld_dst);
+}
+
+cudaError_t launch_umma_f16(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why) {
+    return launch_umma(true, pl, a, stream, why, 0, nullptr, 0);
 }
 
 }  // namespace fp8lin

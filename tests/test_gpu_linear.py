@@ -23,7 +23,7 @@ def _clean_tuning_and_status():
     Kn = kernels()
     yield
     for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable",
-                 "w8a16_swap_min_m"):
+                 "w8a16_swap_min_m", "w8a16_umma_min_m", "w8a16_chunk_mb"):
         Kn.set_tuning(knob, -1)
     torch.cuda.synchronize()
     assert Kn.read_status(torch.device("cuda", 0)) == 0
@@ -191,9 +191,10 @@ def test_streaming_split_k_is_deterministic_and_equal(scheme):
 
 @pytest.mark.parametrize("scheme", SCHEMES)
 def test_wide_m_passes_through_streaming_kernel(scheme):
-    # W8A16 has no tensor-core GEMM path yet: M > 64 is walked in 64-row passes
+    # the mma.sync kernel walks M > 64 in 64-row passes (W8A16: 65..255 rows by default)
     Kn = kernels()
     Kn.set_tuning("stream_max_m", 1 << 20)
+    Kn.set_tuning("w8a16_umma_min_m", 0)
     c = O.make_case(5, 150, 512, 264)
     y = run_linear(scheme, upload_case(c))
     assert_parity(y, oracle_linear(scheme, c), f"{scheme} 150 rows")
@@ -229,6 +230,20 @@ def test_tcgen05_gemm_parity(m, k, n):
     assert_parity(y, oracle_linear("fp8_w8a8_static", c), f"umma {m}x{k}x{n}")
     y2 = run_linear("fp8_w8a8_static", d)
     np.testing.assert_array_equal(y, y2)
+
+
+@pytest.mark.parametrize("m,k,n", [(1280, 256, 4000), (1024, 2048, 11008), (2500, 144, 2056)])
+def test_tcgen05_half_width_tail_items(m, k, n):
+    """When the tile count leaves a short last round, its tiles run as two 128-column halves each
+    (ragged N: the second half of the last column block is partly or wholly past N)."""
+    Kn = kernels()
+    c = O.make_case(808 + m + n, m, k, n)
+    d = upload_case(c)
+    assert "+half" in Kn.variant_name(1, m, k, n)
+    y = run_linear("fp8_w8a8_static", d)
+    assert_parity(y, oracle_linear("fp8_w8a8_static", c), f"umma half-width tail {m}x{k}x{n}")
+    Kn.set_tuning("umma_bn", 128)                       # same arithmetic on whole 128-wide tiles
+    np.testing.assert_array_equal(y, run_linear("fp8_w8a8_static", d))
 
 
 @pytest.mark.parametrize("bn", [64, 128, 256])
@@ -270,6 +285,46 @@ def test_swapped_kernel_with_and_without_prequantised_rows(m, preq_min):
     assert_parity(y, oracle_linear("fp8_w8a8_static", c), f"swap preq_min={preq_min} m={m}")
     Kn.set_tuning("swap_preq_min_m", 65 if preq_min == 1 else 1)
     np.testing.assert_array_equal(y, run_linear("fp8_w8a8_static", d))
+
+
+W8A16_UMMA_SHAPES = [(129, 448, 576), (256, 3584, 4608), (300, 2368, 1000), (513, 704, 72), (1024, 2048, 11008), (200, 16, 264)]
+
+
+@pytest.mark.parametrize("m,k,n", W8A16_UMMA_SHAPES)
+def test_w8a16_large_m_f16_gemm_parity(m, k, n):
+    """Large M (by default from 256 rows): weights widened to f16 chunk by chunk, tcgen05 f16 GEMM; against the oracle and the
+    mma.sync passes (same operand values, so only the accumulation order differs)."""
+    Kn = kernels()
+    c = O.make_case(5150 + m + k + n, m, k, n)
+    d = upload_case(c)
+    assert Kn.variant_name(0, m, k, n).startswith("umma_w8a16_f16") == (m >= 256)     # default threshold
+    Kn.set_tuning("w8a16_umma_min_m", 1)
+    assert Kn.variant_name(0, m, k, n).startswith("umma_w8a16_f16")
+    y = run_linear("fp8_w8a16", d)
+    assert_parity(y, oracle_linear("fp8_w8a16", c), f"w8a16 f16 gemm {m}x{k}x{n}")
+    np.testing.assert_array_equal(y, run_linear("fp8_w8a16", d))
+    Kn.set_tuning("w8a16_umma_min_m", 0)
+    assert Kn.variant_name(0, m, k, n).startswith("stream_mma_w8a16")
+    assert_parity(y, run_linear("fp8_w8a16", d), "f16 gemm vs mma.sync passes")
+
+
+@pytest.mark.parametrize("chunk_mb,bn,splits", [(1, -1, -1), (1, 64, 1), (2, 128, 3), (1, 256, 2)])
+def test_w8a16_large_m_chunks_and_tiles(chunk_mb, bn, splits):
+    """Small chunks (several dequantise + GEMM rounds over one scratch buffer, the last chunk ragged) and
+    forced tile widths / split-K factors."""
+    Kn = kernels()
+    Kn.set_tuning("w8a16_chunk_mb", chunk_mb)
+    Kn.set_tuning("umma_bn", bn)
+    Kn.set_tuning("umma_splits", splits)
+    m, k, n = 260, 1408, 1928
+    c = O.make_case(77 + chunk_mb + bn, m, k, n)
+    d = upload_case(c)
+    name = Kn.variant_name(0, m, k, n)
+    assert name.startswith("umma_w8a16_f16") and not name.endswith("_c1")
+    y = run_linear("fp8_w8a16", d)
+    assert_parity(y, oracle_linear("fp8_w8a16", c), f"w8a16 chunks {name}")
+    y0 = run_linear("fp8_w8a16", d, bias=False)
+    assert_parity(y0, oracle_linear("fp8_w8a16", c, bias=False), f"w8a16 chunks no bias {name}")
 
 
 def test_tcgen05_matches_streaming_kernel():
