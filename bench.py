@@ -474,8 +474,8 @@ def main():
         """Kernel launches one linear call makes, from the variant name the library reports."""
         if variant.startswith("umma_w8a16_f16"):                 # x -> f16, then (widen weights, GEMM) per chunk
             return 1 + 2 * int(variant.rsplit("_c", 1)[1])
-        if variant.startswith("umma_w8a8"):                      # activation quantiser + GEMM (+ split-K tail launch)
-            return 3 if "+tail" in variant else 2
+        if variant.startswith("umma_w8a8") or variant.startswith("umma_pair_w8a8"):
+            return 3 if "+tail" in variant else 2                # activation quantiser + GEMM (+ split-K tail launch)
         if variant.startswith("umma_swap_w8a8"):
             return 2 if variant.endswith("_preq") else 1
         return 1

@@ -33,6 +33,7 @@ struct Tuning {
     int w8a16_swap_min_m = -1;
     int w8a16_umma_min_m = -1;  // smallest M for the dequantise-to-f16 + tcgen05 GEMM route (0 = never)
     int w8a16_chunk_mb = -1;    // size of the f16 weight chunk that route keeps in L2
+    int umma_pair = -1;         // 1 = large-M GEMMs on CTA pairs (256 x 256 tiles), 0 = never
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -122,6 +123,22 @@ F16Chunks plan_f16_chunks(int64_t M, int64_t K, int64_t N) {
     c.x16_bytes = align_up((size_t)M * K * 2, 256);
     c.w16_bytes = (size_t)per * tile_row_bytes;
     return c;
+}
+
+// CTA-pair GEMM (256 x 256 tiles over two SMs) instead of the one-CTA kernel.
+// Measured (W8A8, same bits as the one-CTA kernel): 4096 x 3584 -> 37888 449 vs 470 us, 16384 rows 1911 vs
+// 1980 us; but 4096 x 18944 -> 3584 (224 pair tiles = 3.03 rounds of 74 pairs) 294 vs 260 us and
+// 1024 x 2048 -> 11008 28.7 vs 26.1 us.  So: only when there are at least four rounds of pair tiles and the
+// last round is nearly full, and no worse filled than the one-CTA kernel's.
+bool pair_eligible(int64_t M, int64_t N) {
+    if (g_tune.umma_pair >= 0) return g_tune.umma_pair != 0 && M > 64;
+    const int64_t nt = (N + 255) / 256;
+    const int64_t pt = ((M + 255) / 256) * nt;
+    const int64_t tiles = ((M + 127) / 128) * nt;
+    if (pt < 4 * 74) return false;
+    const double pair_fill = (double)pt / (double)(((pt + 73) / 74) * 74);
+    const double one_fill = (double)tiles / (double)(((tiles + 147) / 148) * 148);
+    return pair_fill >= 0.95 && pair_fill >= one_fill - 1e-9;
 }
 
 bool swap_eligible(int64_t M) {
@@ -270,7 +287,7 @@ int fp8lin_w8a16(const void* x, int64_t ldx, const void* w_nk, const float* w_sc
             a.partial = nullptr; a.counters = ws.counters; a.status = ws.status;
             a.M = (int)M; a.K = (int)K; a.N = (int)nc; a.ldy = (int)ldy;
             const char* why = nullptr;
-            e = launch_umma_f16(pl, a, st, &why);
+            e = pair_eligible(M, nc) ? launch_umma_pair(true, a, st, &why) : launch_umma_f16(pl, a, st, &why);
             if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 f16 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
         }
         return FP8LIN_OK;
@@ -326,7 +343,7 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
     a.partial = (float*)(ws.body + xq_bytes); a.counters = ws.counters; a.status = ws.status;
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ldy;
     const char* why = nullptr;
-    e = launch_umma_w8a8(pl, a, st, &why);
+    e = pair_eligible(M, N) ? launch_umma_pair(false, a, st, &why) : launch_umma_w8a8(pl, a, st, &why);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     return FP8LIN_OK;
 }
@@ -388,6 +405,7 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
     static thread_local char buf[64];
     if (M <= 0 || K <= 0 || N <= 0) return "none";
     const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
+    if (scheme == FP8LIN_W8A8_STATIC && M > max_m && N % 8 == 0 && pair_eligible(M, N)) return "umma_pair_w8a8_256x256";
     if (scheme == FP8LIN_W8A8_STATIC && M > max_m && N % 8 == 0) {
         UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
         if (pl.tail_tiles) snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s1+tail%dx%d", pl.bn, pl.tail_tiles, pl.tail_splits);
@@ -431,6 +449,7 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "w8a16_swap_min_m")) g_tune.w8a16_swap_min_m = value;
     else if (!strcmp(knob, "w8a16_umma_min_m")) g_tune.w8a16_umma_min_m = value;
     else if (!strcmp(knob, "w8a16_chunk_mb")) g_tune.w8a16_chunk_mb = value;
+    else if (!strcmp(knob, "umma_pair")) g_tune.umma_pair = value;
     else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;

@@ -89,6 +89,10 @@ cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStr
 cudaError_t launch_umma_f16(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why);
 cudaError_t launch_x_to_f16(const __nv_bfloat16* x, int64_t ldx, void* x16, int64_t M, int64_t K, cudaStream_t stream);
 cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_t src_bytes, cudaStream_t stream);
+// The same GEMM on CTA pairs (umma_gemm2.cu): 256 x 256 tiles, one MMA across two CTAs.  f16 selects the
+// operand type as above; destinations as launch_umma_w8a8.
+cudaError_t launch_umma_pair(bool f16, const UmmaArgs& args, cudaStream_t stream, const char** why, int n_dst = 0,
+                             void* const* dst_ptrs = nullptr, int64_t ld_dst = 0);
 cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t slot_stride, __nv_bfloat16* y, int64_t ldy,
                              int64_t M, int64_t N, int64_t ld_slot, cudaStream_t stream);
 

@@ -78,12 +78,6 @@ __host__ __device__ constexpr uint32_t make_idesc() {
            | ((uint32_t)(kBM >> 4) << 24);
 }
 
-// Destinations of the epilogue's TMA stores (all describe a bf16 [M][N] matrix of the same shape).
-struct OutMaps {
-    CUtensorMap m[8];
-    int n;
-};
-
 struct UmmaSched {
     int m_tiles, n_tiles, splits, kblocks_total, kblocks_per_split;
     int tile_base, total_work;      // this launch covers work items [tile_base, total_work)
@@ -568,8 +562,8 @@ bool encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
 
 // Output map: bf16 [rows][cols] with a row pitch in bytes, box = box_cols x 32 rows,
 // swizzle span = the box's row length (128 or 64 bytes).
-static bool encode_out_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
-                          uint32_t box_cols) {
+bool encode_out_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                   uint32_t box_cols) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {cols, rows};

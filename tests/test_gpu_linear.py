@@ -23,7 +23,7 @@ def _clean_tuning_and_status():
     Kn = kernels()
     yield
     for knob in ("stream_splits", "stream_max_m", "umma_bn", "umma_splits", "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable",
-                 "w8a16_swap_min_m", "w8a16_umma_min_m", "w8a16_chunk_mb"):
+                 "w8a16_swap_min_m", "w8a16_umma_min_m", "w8a16_chunk_mb", "umma_pair"):
         Kn.set_tuning(knob, -1)
     torch.cuda.synchronize()
     assert Kn.read_status(torch.device("cuda", 0)) == 0
@@ -244,6 +244,35 @@ def test_tcgen05_half_width_tail_items(m, k, n):
     assert_parity(y, oracle_linear("fp8_w8a8_static", c), f"umma half-width tail {m}x{k}x{n}")
     Kn.set_tuning("umma_bn", 128)                       # same arithmetic on whole 128-wide tiles
     np.testing.assert_array_equal(y, run_linear("fp8_w8a8_static", d))
+
+
+PAIR_SHAPES = [(256, 256, 256), (130, 448, 576), (300, 2368, 1000), (1024, 2048, 11008), (4096, 3584, 4608), (65, 16, 8)]
+
+
+@pytest.mark.parametrize("m,k,n", PAIR_SHAPES)
+def test_tcgen05_cta_pair_gemm_parity(m, k, n):
+    """256 x 256 tiles on CTA pairs (one MMA across two SMs): ragged M (the second CTA's rows partly or
+    wholly past M), ragged N and K, against the oracle and the one-CTA kernel."""
+    Kn = kernels()
+    c = O.make_case(6060 + m + k + n, m, k, n)
+    d = upload_case(c)
+    y1 = run_linear("fp8_w8a8_static", d)
+    Kn.set_tuning("umma_pair", 1)
+    assert Kn.variant_name(1, m, k, n).startswith("umma_pair_w8a8")
+    y = run_linear("fp8_w8a8_static", d)
+    assert_parity(y, oracle_linear("fp8_w8a8_static", c), f"cta pair {m}x{k}x{n}")
+    np.testing.assert_array_equal(y, run_linear("fp8_w8a8_static", d))
+    assert_parity(y, y1, "cta pair vs one-CTA kernel", ulps=1.0)
+
+
+def test_w8a16_large_m_on_cta_pairs():
+    Kn = kernels()
+    Kn.set_tuning("umma_pair", 1)
+    Kn.set_tuning("w8a16_chunk_mb", 1)
+    m, k, n = 520, 1408, 1928
+    c = O.make_case(6161, m, k, n)
+    y = run_linear("fp8_w8a16", upload_case(c))
+    assert_parity(y, oracle_linear("fp8_w8a16", c), "w8a16 f16 gemm on cta pairs")
 
 
 @pytest.mark.parametrize("bn", [64, 128, 256])
