@@ -72,7 +72,9 @@ int fp8lin_pack_weight_nk(const void* qweight_nk, void* w_packed, int64_t K, int
 
 /* ---- scratch --------------------------------------------------------------
  * Bytes of caller-owned scratch a linear call of this shape needs (split-K
- * partial sums, quantised activations, tile counters).  Scratch must be
+ * partial sums, quantised activations, tile counters; W8A16 from 256 rows: the
+ * activations as f16 plus one chunk, at most 64 MiB, of weights widened to f16).
+ * Scratch must be
  * 256-byte aligned, ZERO-FILLED ONCE after allocation (the first
  * FP8LIN_WS_HEADER_BYTES hold counters that every kernel leaves at zero), and
  * must not be shared by calls that can run concurrently (one per stream). */
@@ -83,7 +85,9 @@ size_t fp8lin_workspace_bytes(int scheme, int64_t M, int64_t K, int64_t N);
  * y[M,N] = bf16( (x . W^T) * w_scale[n] + bias[n] )
  * Replaces launch_w8a16_gemm (nanovllm/quantization/kernels/fp8.py:79-109) and
  * w8a16_cuda_forward (nanovllm/quantization/csrc/w8a16_ext.cpp:3-11).
- * bias may be NULL. */
+ * bias may be NULL.  From 256 rows on (and for 33..64 rows) the call needs the
+ * workspace that fp8lin_workspace_bytes(FP8LIN_W8A16, M, K, N) reports; below
+ * that only when the shape is split along K. */
 int fp8lin_w8a16(const void* x, int64_t ldx, const void* w_nk, const float* w_scale,
                  const void* bias, void* y, int64_t ldy,
                  int64_t M, int64_t K, int64_t N,
@@ -179,8 +183,10 @@ int fp8lin_moe_combine(const void* routed, void* y, int64_t T, int top_k, int64_
  * for labelling bench rows and ncu captures.  Host-only, returns a static string. */
 const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);
 
-/* Bench/ncu studies only: force a tuning knob ("stream_splits", "stream_max_m",
- * "umma_bn", "umma_splits", ...; value < 0 restores the default).  Not thread safe. */
+/* Bench/ncu studies only: force a tuning knob (value < 0 restores the default).  Not thread safe.
+ * Knobs: "stream_splits", "stream_max_m", "umma_bn", "umma_splits", "umma_pair" (CTA-pair GEMM on/off),
+ * "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable", "w8a16_swap_min_m",
+ * "w8a16_umma_min_m" (rows from which W8A16 takes the f16 GEMM route; 0 = never), "w8a16_chunk_mb", "pdl". */
 int fp8lin_set_tuning(const char* knob, int value);
 
 /* Blocking: copies the device status word out of `workspace` (after syncing
