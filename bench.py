@@ -55,6 +55,9 @@ for _m in (4096, 16384, 32640):
 for _m in (256, 1024, 4096):       # W8A16 prefill: weights widened to f16 chunk by chunk + tcgen05 f16 GEMM
     WORKLOADS[f"c4_w8a16_m{_m}"] = ("fp8_w8a16", [("qkv", _m, 3584, 4608, "col"), ("o_proj", _m, 3584, 3584, "row"),
                                                   ("gate_up", _m, 3584, 37888, "col"), ("down", _m, 18944, 3584, "row")])
+for _m in (16, 64, 1024, 4096):    # fused MLP block (gate_up -> silu * up -> quantise -> down), 7B sizes
+    WORKLOADS[f"c6_mlp_m{_m}"] = ("mlp_w8a8", _m)
+MLP = {"hidden": 3584, "inter": 18944}
 for _t in (1, 64, 1024, 4096):
     WORKLOADS[f"c5_t{_t}"] = ("moe_w8a8", _t)
 MOE = {"hidden": 2048, "experts": 60, "inter": 1408, "top_k": 4}
@@ -208,6 +211,201 @@ def make_expert_weights(E, H, I, seed, device):
         q, s = make_weights(H, 2 * I, seed + 2 * e, device); qs13.append(q); ss13.append(s)
         q, s = make_weights(I, H, seed + 2 * e + 1, device); qs2.append(q); ss2.append(s)
     return torch.stack(qs13), torch.stack(ss13), torch.stack(qs2), torch.stack(ss2)
+
+
+def bench_mlp(args, M):
+    """One step = the MLP block of a 7B-sized dense layer on M rows: y = down(silu(gate(x)) * up(x)), both
+    projections W8A8-static, through ``fp8lin_mlp_w8a8``.  ``three_step_ms`` times the same block as the
+    reference runs it (gate_up linear, silu * up as a separate elementwise op, down linear) on this
+    build's linears.  With N > 1 ranks the intermediate size is split (column-parallel gate_up,
+    row-parallel down + all-reduce)."""
+    import torch.distributed as dist
+    H, I_full = MLP["hidden"], MLP["inter"]
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    flops = 6.0 * M * H * I_full
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        from oracle import torch_ref
+        torch.set_num_threads(os.cpu_count() or 1)
+        g = torch.Generator().manual_seed(SEED)
+        ms_ = min(M, 128)                      # bounded sample of the rows, scaled linearly
+        x = torch.randn((ms_, H), generator=g).to(torch.bfloat16)
+        wgu = torch.randint(0, 120, (2 * I_full, H), generator=g, dtype=torch.uint8)
+        wd = torch.randint(0, 120, (H, I_full), generator=g, dtype=torch.uint8)
+        sgu = torch.full((2 * I_full,), 1e-4); sd = torch.full((H,), 1e-4)
+        times = []
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            gu = torch_ref.dequant_matmul(x, wgu, sgu)
+            a_, b_ = gu.chunk(2, -1)
+            torch_ref.dequant_matmul(torch.nn.functional.silu(a_) * b_, wd, sd)
+            dt = time.perf_counter() - t0
+            if i >= args.warmup:
+                times.append(dt)
+            if sum(times) > 60:
+                break
+        sec = sum(times) / len(times) * (M / ms_)
+        val = flops / sec / 1e12
+        print(json.dumps({"impl": "reference", "metric": "fp8_linear_throughput", "value": val, "unit": "TFLOP/s",
+                          "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": sec * 1e3,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "bf16 (cpu dequant-then-matmul)", "data": "synthetic",
+                          "config": {"workload": args.workload, "rows": M, **MLP},
+                          "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                           "sample": f"{ms_} of {M} rows per pass, time scaled linearly"},
+                          "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=120))
+    if (I_full // world) % 128:
+        if rank == 0:
+            print(json.dumps({"metric": "fp8_linear_throughput", "unavailable":
+                              f"intermediate size {I_full} / {world} ranks is not a multiple of 128"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    I = I_full // world
+    Kn = importlib.import_module("nano-vllm-moe_b200.quantization.kernels")
+    peaks = load_peaks()
+    copies = 2 if world == 1 else 2 * world           # (2 * I + I) * H bytes per copy: >= 2 x L2 in total
+    sets = []
+    for c in range(copies):
+        qgu, sgu = make_weights(H, 2 * I, SEED + 31 * c + rank, dev)
+        qd, sd = make_weights(I, H, SEED + 31 * c + 7 + rank, dev)
+        w_gu = Kn.pack_weight_nk(qgu); w_d = Kn.pack_weight_nk(qd)
+        w_il, s_il, _ = Kn.interleave_gate_up(w_gu, sgu, None, I)
+        sets.append({"w_gu": w_gu, "s_gu": sgu, "w_il": w_il, "s_il": s_il, "w_d": w_d, "s_d": sd})
+        del qgu, qd
+    x, _, in_gu = make_inputs(M, H, 2 * I, SEED + 1, dev)
+    in_d = torch.tensor(4.0 / 448.0, dtype=torch.float32, device=dev)
+
+    def fused(c, xin=None):
+        w = sets[c % copies]
+        y = Kn.launch_mlp_w8a8(x if xin is None else xin, w["w_il"], w["s_il"], in_gu, None, w["w_d"], w["s_d"], in_d, None)
+        if world > 1:
+            dist.all_reduce(y)
+        return y
+
+    def three_steps(c):
+        w = sets[c % copies]
+        gu = Kn.launch_w8a8_gemm(x, w["w_gu"], in_gu, w["s_gu"], None)
+        a_, b_ = gu.chunk(2, -1)
+        y = Kn.launch_w8a8_gemm(torch.nn.functional.silu(a_) * b_, w["w_d"], in_d, w["s_d"], None)
+        if world > 1:
+            dist.all_reduce(y)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for c in range(copies):
+            fn(c)
+        torch.cuda.synchronize()
+        graphs = []
+        if not args.no_graph:
+            side = torch.cuda.Stream(dev)
+            try:
+                with torch.cuda.stream(side):
+                    for c in range(copies):
+                        gph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(gph, stream=side):
+                            fn(c)
+                        graphs.append(gph)
+            except Exception as e:  # noqa: BLE001
+                print(f"[bench] graph capture failed, eager launches: {e!r}", file=sys.stderr)
+                graphs = []
+        run = (lambda i: graphs[i % copies].replay()) if graphs else (lambda i: fn(i))
+        for i in range(warmup):
+            run(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            run(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, bool(graphs)
+
+    steps = min(args.steps, 400 if M <= 64 else 60)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    time.sleep(1.0)
+    ms3, _ = timed(three_steps, max(10, steps // 2), args.warmup)
+    mark0 = sampler.mark()
+    ms, graphed = timed(fused, steps, args.warmup)
+    clocks = sampler.stop(mark0, sampler.mark()) if rank == 0 else None
+    # end to end with host buffers
+    hx = x.cpu().pin_memory()
+    hy = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
+    dx = torch.empty_like(x)
+
+    def e2e_step(i):
+        dx.copy_(hx, non_blocking=True)
+        hy.copy_(fused(i, dx), non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(10, min(steps, 50))
+    a.record()
+    for i in range(n_e2e):
+        e2e_step(i)
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b) / n_e2e
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    status = Kn.read_status(dev)
+    if rank == 0:
+        by = 3.0 * H * I + 2.0 * M * H * 2 + 4.0 * (2 * I + H)            # both weights once, x in, y out, scales
+        t_hbm = by / (peaks["hbm_gbs"] * 1e9)
+        fp8_peak = 2.0 * peaks["bf16_tflops"]
+        t_tc = (flops / world) / (fp8_peak * 1e12)
+        bound = "hbm" if t_hbm >= t_tc else "tensor"
+        ach = by / (ms * 1e-3) / 1e9 if bound == "hbm" else (flops / world) / (ms * 1e-3) / 1e12
+        peak = peaks["hbm_gbs"] if bound == "hbm" else fp8_peak
+        launches = 3 if M > 64 else 4          # quantise x, fused gate_up, down  |  (quantise,) gate_up, silu pass, down
+        line = {
+            "metric": "fp8_linear_throughput", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 -> bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "rows": M, **MLP, "parallelism": f"tp{world}" if world > 1 else "single",
+                       "l2": f"weights cycled over {copies} copies ({copies * 3 * H * I / 1e6:.0f} MB > 126 MB L2)",
+                       "launch": "cuda-graph replay" if graphed else "eager"},
+            "clocks": clocks, "three_step_ms": ms3, "fused_over_three_step": ms3 / ms,
+            "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+                         "frac": ach / peak, "traffic": None, "algorithmic_bytes": by,
+                         "kernel": "umma_pair_gemm_kernel<e4m3, mlp epilogue> + down GEMM" if M > 64 else "decode kernels + silu pass",
+                         "peak_source": f"{peaks['source']}: HBM copy {peaks['hbm_gbs']} GB/s; dense-FP8 peak taken as 2 x "
+                                        f"{peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s"},
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2},
+            "gpu_launches": launches * steps, "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def bench_moe(args, T):
@@ -401,6 +599,8 @@ def main():
 
     if args.workload.startswith("c5"):
         return bench_moe(args, WORKLOADS[args.workload][1])
+    if WORKLOADS[args.workload][0] == "mlp_w8a8":
+        return bench_mlp(args, WORKLOADS[args.workload][1])
     scheme, ops = WORKLOADS[args.workload]
     flops = sum(2 * m * k * n for _, m, k, n, _ in ops)
     if args.impl == "reference":

@@ -179,6 +179,25 @@ int fp8lin_moe_experts_w8a8(const void* x, int64_t ldx, int x_div, const int32_t
  * NoEPPrepareFinalize.finalize (no_ep.py:45) / TorchAllToAllPrepareFinalize.finalize (:90). */
 int fp8lin_moe_combine(const void* routed, void* y, int64_t T, int top_k, int64_t H, void* stream);
 
+/* ---- fused MLP (W8A8-static) ----------------------------------------------------
+ * y[M,N] = down( silu(gate(x)) * up(x) ): replaces the three steps of the reference's MLP block,
+ * gate_up_proj -> SiluAndMul -> down_proj (nanovllm/models/qwen2.py:110-114,
+ * nanovllm/layers/activation.py:11-14), with the two linears on FP8 weights.  The bf16 gate_up
+ * result is never written for M > 64: the gate_up GEMM's epilogue computes h = bf16(silu(g) * u)
+ * from g, u rounded to bf16 and quantises it with the down projection's activation scale; the down
+ * GEMM reads those e4m3 rows directly.  Same roundings as the three separate steps.
+ *   w_gate_up      packed tiles of the merged [2I][H] weight with the 128-channel tile rows
+ *                  INTERLEAVED: gate rows 0..127, up rows 0..127, gate rows 128..255, ...
+ *                  (a permutation of the 16 KiB x ceil(H/128) tile rows of fp8lin_pack_weight_nk's
+ *                  output); gate_up_scale / gate_up_bias [2I] permuted the same way
+ *   w_down         packed tiles of the [N][I] down weight; I % 128 == 0
+ * Scratch: fp8lin_mlp_workspace_bytes(M, H, I, N), rules as for the linears. */
+size_t fp8lin_mlp_workspace_bytes(int64_t M, int64_t H, int64_t I, int64_t N);
+int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const float* gate_up_scale,
+                    const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
+                    const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
+                    int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Which kernel variant a shape is routed to ("stream_mma_w8a8_m16", "umma_w8a8_128x256", ...),
  * for labelling bench rows and ncu captures.  Host-only, returns a static string. */
 const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);

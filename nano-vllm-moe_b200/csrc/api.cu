@@ -377,6 +377,98 @@ int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const floa
     return FP8LIN_OK;
 }
 
+// ---- fused MLP: y = down( silu(gate(x)) * up(x) ), both projections W8A8-static -----------------------
+namespace {
+
+struct MlpLayout {
+    size_t inner;       // scratch of the gate_up linear itself (quantised x, split-K partials)
+    size_t gu_off, hq_off, total;
+};
+
+MlpLayout mlp_layout(int64_t M, int64_t H, int64_t I) {
+    MlpLayout l;
+    size_t inner = fp8lin_workspace_bytes(FP8LIN_W8A8_STATIC, M, H, 2 * I) - FP8LIN_WS_HEADER_BYTES;
+    const size_t xq = align_up((size_t)M * H, 256);
+    if (xq > inner) inner = xq;
+    l.inner = align_up(inner, 256);
+    l.gu_off = l.inner;
+    const size_t gu = M <= kDefaultStreamMaxM ? align_up((size_t)M * 2 * I * 2, 256) : 0;   // bf16 gate_up result, small batches only
+    l.hq_off = l.gu_off + gu;
+    l.total = l.hq_off + align_up((size_t)M * I, 256);
+    return l;
+}
+
+// W8A8 linear whose activations are already e4m3 (row pitch K): the second half of the fused MLP.
+int run_w8a8_prequantised(const unsigned char* xq, const void* w, const float* w_scale, const float* input_scale,
+                          const void* bias, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N, const WsView& ws,
+                          cudaStream_t st) {
+    UmmaArgs a;
+    a.xq = xq; a.w = (const unsigned char*)w; a.w_scale = w_scale; a.input_scale = input_scale;
+    a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y; a.partial = nullptr; a.counters = ws.counters;
+    a.status = ws.status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ldy;
+    const char* why = nullptr;
+    cudaError_t e;
+    if (M <= 64) {
+        SwapPlan sp = plan_swap(M, K, N, g_tune.swap_splits, true);
+        e = launch_swap_w8a8(sp, a, nullptr, 0, st, &why);
+    } else if (pair_eligible(M, N)) {
+        e = launch_umma_pair(false, a, st, &why);
+    } else {
+        UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, g_tune.umma_splits);
+        e = launch_umma_w8a8(pl, a, st, &why);
+    }
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "down projection launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+    return FP8LIN_OK;
+}
+
+}  // namespace
+
+size_t fp8lin_mlp_workspace_bytes(int64_t M, int64_t H, int64_t I, int64_t N) {
+    (void)N;
+    if (M <= 0 || H <= 0 || I <= 0) return FP8LIN_WS_HEADER_BYTES;
+    return FP8LIN_WS_HEADER_BYTES + mlp_layout(M, H, I).total;
+}
+
+int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const float* gate_up_scale,
+                    const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
+                    const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
+                    int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    if (I <= 0 || I % 128 != 0) return fail(FP8LIN_ERR_SHAPE, "the intermediate size must be a positive multiple of 128 (got %lld)", (long long)I);
+    int rc = validate_common(x, ldx, w_gate_up, gate_up_scale, gate_up_bias, y, 2 * I, M, H, 2 * I);   // (its output is internal)
+    if (rc != FP8LIN_OK) return rc;
+    rc = validate_common(x, I, w_down, down_scale, down_bias, y, ldy, M, I, N);      // (the down input is internal, pitch I)
+    if (rc != FP8LIN_OK || M == 0) return rc;
+    if (!gate_up_input_scale || !down_input_scale) return fail(FP8LIN_ERR_NULL, "both input scales are required");
+    if (N % 8 != 0 || ldy % 8 != 0) return fail(FP8LIN_ERR_SHAPE, "N and ldy must be multiples of 8");
+    const MlpLayout l = mlp_layout(M, H, I);
+    WsView ws = ws_view(workspace, workspace_bytes);
+    if (!workspace || ws.body_bytes < l.total)
+        return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes", (size_t)FP8LIN_WS_HEADER_BYTES + l.total);
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned char* hq = ws.body + l.hq_off;
+    if (M <= kDefaultStreamMaxM) {
+        // small batches: gate_up through the decode kernels into a bf16 buffer, one pass for silu * up + quantise
+        __nv_bfloat16* gu = (__nv_bfloat16*)(ws.body + l.gu_off);
+        rc = fp8lin_w8a8(x, ldx, w_gate_up, gate_up_scale, gate_up_input_scale, gate_up_bias, gu, 2 * I, M, H, 2 * I, workspace,
+                         FP8LIN_WS_HEADER_BYTES + l.inner, stream);
+        if (rc != FP8LIN_OK) return rc;
+        cudaError_t e = launch_silu_mul_quant_interleaved(gu, down_input_scale, hq, M, I, st);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "silu-multiply pass launch: %s", cudaGetErrorString(e));
+    } else {
+        unsigned char* xq = ws.body;
+        cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, gate_up_input_scale, xq, M, H, st);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
+        UmmaArgs a;
+        a.xq = xq; a.w = (const unsigned char*)w_gate_up; a.w_scale = gate_up_scale; a.input_scale = gate_up_input_scale;
+        a.bias = (const __nv_bfloat16*)gate_up_bias; a.y = nullptr; a.partial = nullptr; a.counters = ws.counters;
+        a.status = ws.status; a.M = (int)M; a.K = (int)H; a.N = (int)(2 * I); a.ldy = 0;
+        const char* why = nullptr;
+        e = launch_umma_pair_mlp(a, hq, down_input_scale, st, &why);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "fused gate_up launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
+    }
+    return run_w8a8_prequantised(hq, w_down, down_scale, down_input_scale, down_bias, y, ldy, M, I, N, ws, st);
+}
+
 int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, void* y, int64_t ldy,
                      int64_t M, int64_t N, void* stream) {
     if (n_slots < 1 || M < 0 || N <= 0 || N % 8 != 0 || ld_slot % 8 != 0 || ldy % 8 != 0 || slot_stride % 8 != 0)

@@ -154,6 +154,52 @@ cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_
     return cudaLaunchKernelEx(&cfg, dequant_tiles_f16_kernel, src, (unsigned char*)dst, src_bytes);
 }
 
+// Small-batch half of the fused MLP: gu = bf16 [M][2I] as the gate_up GEMM wrote it with interleaved
+// weights (columns [256t, 256t+128) = gate channels 128t.., [256t+128, 256t+256) = up channels 128t..);
+// hq[m][i] = e4m3( bf16(silu(g) * u) / h_scale ), the pre-quantised input of the down projection.
+__global__ void __launch_bounds__(256)
+silu_mul_quant_interleaved_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ h_scale,
+                                  unsigned char* __restrict__ hq, int64_t M, int64_t I) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const ExactDiv div_scale(fmaxf(__ldg(h_scale), 1e-12f));
+    const int64_t vec_per_row = I / 8;
+    const int64_t total = M * vec_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / vec_per_row;
+        const int64_t c = (i - r * vec_per_row) * 8;
+        const int64_t gcol = (c >> 7) * 256 + (c & 127);
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gu + r * 2 * I + gcol));
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(gu + r * 2 * I + gcol + 128));
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint4 h;
+        uint32_t* hw = reinterpret_cast<uint32_t*>(&h);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
+            const float s0 = g0 / (1.f + expf(-g0)), s1 = g1 / (1.f + expf(-g1));
+            hw[j] = pack_bf16x2(s0 * bf16_lo(uw[j]), s1 * bf16_hi(uw[j]));
+        }
+        *reinterpret_cast<uint2*>(hq + r * I + c) = quant8_e4m3(h, div_scale);
+    }
+}
+
+cudaError_t launch_silu_mul_quant_interleaved(const __nv_bfloat16* gu, const float* h_scale, unsigned char* hq, int64_t M,
+                                              int64_t I, cudaStream_t stream) {
+    const int64_t total = M * (I / 8);
+    if (total == 0) return cudaSuccess;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.numAttrs = pdl_attribute(attr);
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, silu_mul_quant_interleaved_kernel, gu, h_scale, hq, M, I);
+}
+
 // Pack e4m3 weight bytes into the tiled layout (see pack_offset).  One CTA fills one
 // 128 x 128 tile through shared memory; `src_is_kn` selects the source orientation:
 // [K][N] (the reference's runtime buffer) or [N][K] (the checkpoint's layout).

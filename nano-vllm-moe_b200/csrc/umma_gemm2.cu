@@ -61,10 +61,16 @@ __device__ __forceinline__ void decode_pair_tile(const PairSched& s, int tile, i
     tn = r / gsize;
 }
 
-template <bool kF16>
+// kMlp: the weight is a gate_up projection packed with its 128-channel tile rows interleaved (gate tile t,
+// up tile t, gate tile t+1, ...; scale and bias permuted alike), so the 256 columns of a tile are 128 gate
+// channels followed by the 128 up channels of the same indices.  The epilogue then produces what the down
+// projection consumes instead of the bf16 tile: h = bf16(silu(g) * u) from g, u rounded to bf16 (the values
+// the unfused path materialises), quantised to e4m3 with the down projection's static scale `h_scale`;
+// 128 bytes per row and tile go to the e4m3 matrix [M][N/2] described by outs.m[0].
+template <bool kF16, bool kMlp>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ OutMaps outs, UmmaArgs p, PairSched sched) {
+                      const __grid_constant__ OutMaps outs, UmmaArgs p, PairSched sched, const float* h_scale) {
     constexpr int S = kStages;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[S];
@@ -220,6 +226,65 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (any_failed) { s_abort = 1; ok = false; break; }
             tc_fence_after();
             const int row0 = (2 * tmp + (int)rank) * kBM + q * 32;
+            if (kMlp) {
+                // warp h owns output bytes [64h, 64h + 64) of the tile's 128: two steps of 32 columns, each from
+                // 32 gate accumulators (columns c..) and the 32 up accumulators 128 columns further on
+                const ExactDiv div_h(fmaxf(__ldg(h_scale), 1e-12f));
+                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * kBN;
+                if (n0 < p.N) {
+#pragma unroll 1
+                    for (int sp = 0; sp < 2; ++sp) {
+                        const int c = 64 * h + 32 * sp;
+                        uint32_t g[32], u[32];
+                        __syncwarp();
+                        tmem_ld32_nowait(t_row + c, g);
+                        tmem_ld32_nowait(t_row + 128 + c, u);
+                        tmem_ld_wait();
+                        uint32_t hw[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const float2 sg = *reinterpret_cast<const float2*>(&s_scale[c + j]);
+                            const float2 su = *reinterpret_cast<const float2*>(&s_scale[128 + c + j]);
+                            const uint32_t bg = *reinterpret_cast<const uint32_t*>(&s_bias[c + j]);
+                            const uint32_t bu = *reinterpret_cast<const uint32_t*>(&s_bias[128 + c + j]);
+                            // gate and up as the bf16 values a separate gate_up GEMM would have stored
+                            const uint32_t gp = pack_bf16x2(fmaf(__uint_as_float(g[j]), sg.x, bf16_lo(bg)),
+                                                            fmaf(__uint_as_float(g[j + 1]), sg.y, bf16_hi(bg)));
+                            const uint32_t up = pack_bf16x2(fmaf(__uint_as_float(u[j]), su.x, bf16_lo(bu)),
+                                                            fmaf(__uint_as_float(u[j + 1]), su.y, bf16_hi(bu)));
+                            const float g0 = bf16_lo(gp), g1 = bf16_hi(gp);
+                            const float s0 = g0 / (1.f + expf(-g0)), s1 = g1 / (1.f + expf(-g1));
+                            hw[j / 2] = pack_bf16x2(s0 * bf16_lo(up), s1 * bf16_hi(up));
+                        }
+                        uint2 qv[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            qv[j] = quant8_e4m3(make_uint4(hw[4 * j], hw[4 * j + 1], hw[4 * j + 2], hw[4 * j + 3]), div_h);
+                        if (sp == 0) {
+                            if (h == 0 && lane == 0) tma_store_wait_read();      // the previous store has read the box
+                            asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+                        }
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const uint32_t chunk = (uint32_t)(4 * h + 2 * sp + j);
+                            const uint32_t dst = pbox + lane * 128 + ((chunk ^ (uint32_t)(lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(qv[2 * j].x), "r"(qv[2 * j].y),
+                                         "r"(qv[2 * j + 1].x), "r"(qv[2 * j + 1].y) : "memory");
+                        }
+                    }
+                    fence_async_smem();
+                    asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+                    if (h == 0 && lane == 0) tma_store_2d(&outs.m[0], pbox, n0 >> 1, row0);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t te = smem_u32(&bar_tempty[as]);
+                    if (leader) mbar_arrive(te);
+                    else mbar_arrive_cluster(map_to_cta(te, 0));
+                }
+                continue;
+            }
             const uint32_t t_pair = tmem_base + ((uint32_t)(q * 32) << 16) + as * kBN + h * 32;
 #pragma unroll 1
             for (int col = 0; col < kBN; col += 64) {
@@ -275,10 +340,10 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
 }
 
-template <bool kF16>
+template <bool kF16, bool kMlp>
 cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& ty,
-                        cudaStream_t stream, const char** why) {
-    auto kern = umma_pair_gemm_kernel<kF16>;
+                        cudaStream_t stream, const char** why, const float* h_scale = nullptr) {
+    auto kern = umma_pair_gemm_kernel<kF16, kMlp>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -310,7 +375,7 @@ cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensor
     ++na;
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s);
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s, h_scale);
 }
 
 }  // namespace
@@ -338,7 +403,29 @@ cudaError_t launch_umma_pair(bool f16, const UmmaArgs& a, cudaStream_t stream, c
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }
-    return f16 ? launch_pair<true>(a, ta, tb, ty, stream, why) : launch_pair<false>(a, ta, tb, ty, stream, why);
+    return f16 ? launch_pair<true, false>(a, ta, tb, ty, stream, why) : launch_pair<false, false>(a, ta, tb, ty, stream, why);
+}
+
+// gate_up GEMM with the SiLU-multiply-quantise epilogue: a.w = interleaved gate/up tiles, a.N = 2 * I (a multiple
+// of 256), a.w_scale / a.bias permuted like the tiles; hq = e4m3 [M][I] (row pitch I), h_scale = the down
+// projection's activation scale.  a.y is unused.
+cudaError_t launch_umma_pair_mlp(const UmmaArgs& a, unsigned char* hq, const float* h_scale, cudaStream_t stream,
+                                 const char** why) {
+    if (a.N % 256 != 0) {
+        if (why) *why = "the intermediate size must be a multiple of 128";
+        return cudaErrorInvalidValue;
+    }
+    CUtensorMap ta, tb;
+    OutMaps ty;
+    ty.n = 1;
+    const bool ok = encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K, kBM) &&
+                    encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128, 128) &&
+                    encode_u8_2d(&ty.m[0], hq, (uint64_t)a.M, (uint64_t)(a.N / 2), 32);
+    if (!ok) {
+        if (why) *why = "cuTensorMapEncodeTiled failed";
+        return cudaErrorInvalidValue;
+    }
+    return launch_pair<false, true>(a, ta, tb, ty, stream, why, h_scale);
 }
 
 }  // namespace fp8lin

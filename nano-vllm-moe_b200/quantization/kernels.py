@@ -198,3 +198,44 @@ def sum_slots(slots: torch.Tensor, m: int, n: int, out: torch.Tensor | None = No
                                           y.stride(0), m, n, _stream_ptr(slots.device))
     _lib.raise_for(rc, "fp8lin_sum_slots")
     return y
+
+
+def interleave_gate_up(w_packed: torch.Tensor, weight_scale: torch.Tensor, bias: torch.Tensor | None, inter: int):
+    """Reorder a packed merged gate_up weight ([2*inter, K]: gate rows, then up rows) so that its
+    128-channel tile rows alternate gate / up, and permute scale and bias alike: the layout the
+    fused MLP call takes.  A pure permutation of whole tile rows (no repacking)."""
+    if inter % 128:
+        raise ValueError(f"the intermediate size must be a multiple of 128 (got {inter})")
+    t = inter // 128
+    w = w_packed.view(2, t, -1).transpose(0, 1).contiguous().view(-1)
+    s = weight_scale.view(2, t, 128).transpose(0, 1).contiguous().view(-1)
+    b = bias.view(2, t, 128).transpose(0, 1).contiguous().view(-1) if bias is not None else None
+    return w, s, b
+
+
+def launch_mlp_w8a8(x: torch.Tensor, w_gate_up_il: torch.Tensor, gate_up_scale_il: torch.Tensor,
+                    gate_up_input_scale: torch.Tensor, gate_up_bias_il: torch.Tensor | None, w_down: torch.Tensor,
+                    down_scale: torch.Tensor, down_input_scale: torch.Tensor, down_bias: torch.Tensor | None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 ``down(silu(gate(x)) * up(x))`` with both projections W8A8-static; operands as produced by
+    ``interleave_gate_up`` (gate_up) and ``pack_weight_nk`` / ``prepack_weight`` (down)."""
+    x, n2, h = _check_linear_args(x, w_gate_up_il, gate_up_scale_il, gate_up_bias_il)
+    inter = n2 // 2
+    n = down_scale.numel()
+    _require_cuda(w_down, down_scale, gate_up_input_scale, down_input_scale)
+    if w_down.numel() != packed_bytes(inter, n):
+        raise ValueError("w_down does not match the intermediate size of the gate_up weight")
+    if down_bias is not None and (down_bias.dtype != torch.bfloat16 or down_bias.numel() != n):
+        raise ValueError("down_bias must be bf16 [N]")
+    m = x.shape[0]
+    y = out if out is not None else torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        lib = _lib.load()
+        ws = workspace(x.device, lib.fp8lin_mlp_workspace_bytes(m, h, inter, n))
+        rc = lib.fp8lin_mlp_w8a8(
+            x.data_ptr(), x.stride(0), w_gate_up_il.data_ptr(), gate_up_scale_il.data_ptr(), gate_up_input_scale.data_ptr(),
+            gate_up_bias_il.data_ptr() if gate_up_bias_il is not None else None, w_down.data_ptr(), down_scale.data_ptr(),
+            down_input_scale.data_ptr(), down_bias.data_ptr() if down_bias is not None else None, y.data_ptr(), y.stride(0),
+            m, h, inter, n, ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
+    _lib.raise_for(rc, "fp8lin_mlp_w8a8")
+    return y

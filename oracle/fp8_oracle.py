@@ -298,6 +298,20 @@ def silu_mul(gate_up: np.ndarray) -> np.ndarray:
     return bf16_round((s * u).astype(np.float32))
 
 
+def mlp_w8a8(x, gu_q, gu_scale, gu_in_scale, gu_bias, down_q, down_scale, down_in_scale, down_bias):
+    """Dense MLP block on W8A8-static linears; restates Qwen2MLP.forward
+    (nanovllm/models/qwen2.py:110-114): gate_up_proj -> SiluAndMul
+    (nanovllm/layers/activation.py:11-14, compiled: one rounding) -> down_proj.
+
+    gu_q [2I,H] codes (gate rows then up rows), down_q [N,I] codes; scales per
+    output channel, one activation scale per linear.  gate_up is rounded to
+    bf16 (the tensor the reference materialises), h = bf16(silu(g) * u), and
+    the down projection quantises h with its own static scale.
+    """
+    gu = linear_w8a8(x, gu_q, gu_scale, gu_in_scale, gu_bias)
+    return linear_w8a8(silu_mul(gu), down_q, down_scale, down_in_scale, down_bias)
+
+
 def moe_experts_w8a8(x, topk_ids, topk_weights, w13_q, w13_scale, w13_in_scale,
                      w2_q, w2_scale, w2_in_scale):
     """Routed expert FFN on FP8 operands; restates EagerExperts.apply

@@ -171,6 +171,47 @@ def test_workspace_and_variant_queries(pkg):
     assert lib.fp8lin_variant_name(L.W8A16, 1, 2048, 2048).decode().startswith("stream_mma_w8a16_m8")
 
 
+def test_routing_of_large_shapes(pkg):
+    """Which kernel family a shape goes to is a pure host function: check the rules that need no device."""
+    lib = pkg._lib.load()
+    L = pkg._lib
+    name = lambda s, m, k, n: lib.fp8lin_variant_name(s, m, k, n).decode()          # noqa: E731
+    assert name(L.W8A8_STATIC, 4096, 3584, 37888) == "umma_pair_w8a8_256x256"         # 16 x 148 pair tiles: 32 full rounds
+    assert name(L.W8A8_STATIC, 4096, 18944, 3584).startswith("umma_w8a8_128x256_s1+tail")   # 224 pair tiles = 3.03 rounds
+    assert name(L.W8A8_STATIC, 1024, 2048, 11008) == "umma_w8a8_128x256_s1+half48"    # 344 tiles: last 48 as halves
+    assert name(L.W8A16, 255, 3584, 4608).startswith("stream_mma_w8a16")
+    assert name(L.W8A16, 256, 3584, 4608).startswith("umma_w8a16_f16")
+    assert name(L.W8A16, 4096, 3584, 37888).endswith("_c5")                            # five chunks of <= 64 MB of f16
+    assert name(L.W8A16, 40, 3584, 4608).startswith("umma_swap_w8a16_m64")
+    # W8A16 from 256 rows needs the f16 scratch: activations + one chunk
+    need = lib.fp8lin_workspace_bytes(L.W8A16, 4096, 3584, 37888)
+    assert need >= L.WS_HEADER_BYTES + 4096 * 3584 * 2 and need <= L.WS_HEADER_BYTES + 4096 * 3584 * 2 + (65 << 20)
+    # fused MLP scratch: quantised x and h for large M, plus the bf16 gate_up tensor for decode sizes
+    big = lib.fp8lin_mlp_workspace_bytes(4096, 3584, 18944, 3584)
+    assert big >= L.WS_HEADER_BYTES + 4096 * (3584 + 18944)
+    small = lib.fp8lin_mlp_workspace_bytes(16, 3584, 18944, 3584)
+    assert small >= L.WS_HEADER_BYTES + 16 * 18944 * 5
+
+
+def test_gate_up_interleave_is_a_tile_row_permutation():
+    """interleave_gate_up(pack(W)) == pack(W with its 128-row blocks alternating gate / up)."""
+    from importlib import import_module
+    from oracle import fp8_oracle as O
+    K = import_module("nano-vllm-moe_b200.quantization.kernels")
+    rng = np.random.default_rng(3)
+    inter, k = 384, 200
+    wq = rng.integers(0, 255, size=(2 * inter, k), dtype=np.uint8)
+    scale = rng.random(2 * inter).astype(np.float32)
+    bias = torch.from_numpy(rng.random(2 * inter).astype(np.float32)).to(torch.bfloat16)
+    order = np.concatenate([np.r_[g * 128:(g + 1) * 128, inter + g * 128:inter + (g + 1) * 128] for g in range(inter // 128)])
+    w_il, s_il, b_il = K.interleave_gate_up(torch.from_numpy(O.pack_tiles(wq)), torch.from_numpy(scale), bias, inter)
+    np.testing.assert_array_equal(w_il.numpy(), O.pack_tiles(wq[order]))
+    np.testing.assert_array_equal(s_il.numpy(), scale[order])
+    assert torch.equal(b_il, bias[torch.from_numpy(order)])
+    with pytest.raises(ValueError):
+        K.interleave_gate_up(torch.from_numpy(O.pack_tiles(wq)), torch.from_numpy(scale), None, 200)
+
+
 def test_kernels_refuse_cpu_tensors(pkg):
     from importlib import import_module
     K = import_module("nano-vllm-moe_b200.quantization.kernels")
