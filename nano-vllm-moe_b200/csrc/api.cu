@@ -141,11 +141,14 @@ bool pair_eligible(int64_t M, int64_t N) {
     return pair_fill >= 0.95 && pair_fill >= one_fill - 1e-9;
 }
 
-bool swap_eligible(int64_t M) {
+bool swap_eligible(int64_t M, int64_t K, int64_t N) {
     const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
     // up to 8 rows the mma.sync streaming kernel (several small CTAs per SM) starts and drains
-    // faster than the one-CTA-per-SM tcgen05 pipeline; measured cross-over is between 8 and 16 rows
-    const int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 9;
+    // faster than the one-CTA-per-SM tcgen05 pipeline; measured cross-over is between 8 and 16 rows.
+    // Exception: a long K over few channel tiles (18944 -> 3584, 68 MB), where the 8-slice cluster
+    // split-K of the tcgen05 kernel streams faster from the first row on (M = 4: 16.9 vs 19.1 us).
+    int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 9;
+    if (g_tune.swap_min_m < 0 && K >= 8192 && N <= 4736 && K * N >= (32ll << 20)) min_m = 1;
     return g_tune.swap_enable != 0 && M >= min_m && M <= 64 && M <= max_m;
 }
 
@@ -303,7 +306,7 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
     if (rc != FP8LIN_OK || M == 0) return rc;
     if (!input_scale) return fail(FP8LIN_ERR_NULL, "input_scale must not be NULL");
     cudaStream_t st = (cudaStream_t)stream;
-    if (swap_eligible(M)) {
+    if (swap_eligible(M, K, N)) {
         const bool preq = swap_prequant(M);
         SwapPlan sp = plan_swap(M, K, N, g_tune.swap_splits, preq);
         WsView wsv = ws_view(workspace, workspace_bytes);
@@ -505,7 +508,7 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
         else snprintf(buf, sizeof(buf), "umma_w8a8_128x%d_s%d", pl.bn, pl.splits);
         return buf;
     }
-    if (scheme == FP8LIN_W8A8_STATIC && swap_eligible(M)) {
+    if (scheme == FP8LIN_W8A8_STATIC && swap_eligible(M, K, N)) {
         SwapPlan pl = plan_swap(M, K, N, g_tune.swap_splits, swap_prequant(M));
         snprintf(buf, sizeof(buf), "umma_swap_w8a8_m%d_s%d%s", pl.mp, pl.splits, pl.preq ? "_preq" : "");
         return buf;

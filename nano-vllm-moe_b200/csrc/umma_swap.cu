@@ -386,6 +386,16 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq)
         const double cost = waves * kps + (s > 1 ? 8.0 : 6.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
+    // Long K over few channel tiles (18944 -> 3584: 28 tiles x 148 K blocks), two CTAs per SM: measured
+    // 20.0 / 19.1 / 18.3 us with 6 / 7 / 8 slices although fewer 8-CTA clusters are resident at once --
+    // shorter slices ramp and drain faster than the wave model above credits.  Take the most slices
+    // that still leave 16 K blocks each.
+    if (force_splits <= 0 && pl.mp == 16 && kblocks >= 64 && pl.n_tiles * 8 <= 2 * 148) {
+        for (int s = 8; s > best_s; --s) {
+            const int kps = (kblocks + s - 1) / s;
+            if (kps >= 16 && (kblocks + kps - 1) / kps == s) { best_s = s; break; }
+        }
+    }
     pl.splits = best_s;
     pl.kblocks_per_split = (kblocks + best_s - 1) / best_s;
     const int resident = 148 * (pl.mp == 16 ? 2 : 1);
