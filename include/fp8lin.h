@@ -179,6 +179,19 @@ int fp8lin_moe_experts_w8a8(const void* x, int64_t ldx, int x_div, const int32_t
  * NoEPPrepareFinalize.finalize (no_ep.py:45) / TorchAllToAllPrepareFinalize.finalize (:90). */
 int fp8lin_moe_combine(const void* routed, void* y, int64_t T, int top_k, int64_t H, void* stream);
 
+/* ---- exporter arithmetic -----------------------------------------------------------------
+ * fp8lin_quantize_weight replaces quantize_fp8_per_output_channel of the checkpoint exporter
+ * (scripts/quantization/quantize.py:51-55): w [N][K] (bf16, or fp32 when w_is_f32; row pitch ldw
+ * elements) -> qweight_nk u8 [N][K] e4m3 codes and weight_scale[n] = max(amax_k |w|, 1e-8) / 448;
+ * codes = RNE(clamp(w / scale, +-448)) with a true division, so they equal the exporter's bit for
+ * bit.  K even.
+ * fp8lin_abs_max folds max |x| of a bf16 activation batch into *amax (one float on the device,
+ * start it at 0): the per-linear maximum the exporter's calibration hooks track
+ * (scripts/quantization/quantize.py:154-164 and :200-203); input_scale = max(amax, 1e-8) / 448. */
+int fp8lin_quantize_weight(const void* w, int w_is_f32, int64_t ldw, void* qweight_nk, float* weight_scale, int64_t N,
+                           int64_t K, void* stream);
+int fp8lin_abs_max(const void* x, int64_t ldx, int64_t M, int64_t K, float* amax, void* stream);
+
 /* ---- fused MLP (W8A8-static) ----------------------------------------------------
  * y[M,N] = down( silu(gate(x)) * up(x) ): replaces the three steps of the reference's MLP block,
  * gate_up_proj -> SiluAndMul -> down_proj (nanovllm/models/qwen2.py:110-114,

@@ -485,6 +485,29 @@ int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_
     return FP8LIN_OK;
 }
 
+int fp8lin_quantize_weight(const void* w, int w_is_f32, int64_t ldw, void* qweight_nk, float* weight_scale, int64_t N,
+                           int64_t K, void* stream) {
+    if (N < 0 || K <= 0 || K % 2 != 0 || ldw < K) return fail(FP8LIN_ERR_SHAPE, "bad shape N=%lld K=%lld ldw=%lld (K must be even)", (long long)N, (long long)K, (long long)ldw);
+    if (N == 0) return FP8LIN_OK;
+    if (!w || !qweight_nk || !weight_scale) return fail(FP8LIN_ERR_NULL, "w, qweight_nk and weight_scale must not be NULL");
+    if ((reinterpret_cast<uintptr_t>(qweight_nk) & 1) != 0) return fail(FP8LIN_ERR_ALIGN, "qweight_nk must be 2-byte aligned");
+    if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
+    cudaError_t e = launch_quantize_weight(w, w_is_f32 != 0, ldw, (unsigned char*)qweight_nk, weight_scale, N, K, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "weight quantiser launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+int fp8lin_abs_max(const void* x, int64_t ldx, int64_t M, int64_t K, float* amax, void* stream) {
+    if (M < 0 || K <= 0 || K % 8 != 0 || ldx < K || ldx % 8 != 0) return fail(FP8LIN_ERR_SHAPE, "bad shape M=%lld K=%lld ldx=%lld (multiples of 8)", (long long)M, (long long)K, (long long)ldx);
+    if (M == 0) return FP8LIN_OK;
+    if (!x || !amax) return fail(FP8LIN_ERR_NULL, "x and amax must not be NULL");
+    if (!aligned16(x)) return fail(FP8LIN_ERR_ALIGN, "x must be 16-byte aligned");
+    if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
+    cudaError_t e = launch_abs_max((const __nv_bfloat16*)x, ldx, M, K, amax, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "abs-max launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
 int fp8lin_quantize_activation(const void* x, int64_t ldx, const float* input_scale, void* xq, int64_t M, int64_t K,
                                void* stream) {
     if (M < 0 || K <= 0 || K % 16 != 0) return fail(FP8LIN_ERR_SHAPE, "bad shape M=%lld K=%lld", (long long)M, (long long)K);

@@ -200,6 +200,88 @@ cudaError_t launch_silu_mul_quant_interleaved(const __nv_bfloat16* gu, const flo
     return cudaLaunchKernelEx(&cfg, silu_mul_quant_interleaved_kernel, gu, h_scale, hq, M, I);
 }
 
+// ---- exporter arithmetic ------------------------------------------------------------------------
+// Per-output-channel weight quantisation of the checkpoint exporter: scale[n] = max(amax_k |w[n][k]|, 1e-8) / 448,
+// q[n][k] = e4m3(clamp(w[n][k] / scale[n], +-448)), true division, round to nearest even.  One CTA per
+// channel: a pass for the maximum (the row then sits in L2), a pass that quantises.  kF32: fp32 source.
+template <bool kF32>
+__global__ void __launch_bounds__(256)
+quantize_weight_kernel(const void* __restrict__ w_, int64_t ldw, unsigned char* __restrict__ q, float* __restrict__ scale,
+                       int64_t K) {
+    __shared__ float s_red[8];
+    const int64_t n = blockIdx.x;
+    const float* wf = reinterpret_cast<const float*>(w_) + n * ldw;
+    const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w_) + n * ldw;
+    // bf16 rows that allow it are read 16 bytes at a time
+    const bool vec = !kF32 && K % 8 == 0 && ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(w_) & 15) == 0;
+    float amax = 0.f;
+    if (vec) {
+        for (int64_t k = 8 * (int64_t)threadIdx.x; k < K; k += 8 * 256) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(wb + k));
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf16_lo(v.x)), fabsf(bf16_hi(v.x))), fmaxf(fabsf(bf16_lo(v.y)), fabsf(bf16_hi(v.y)))));
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf16_lo(v.z)), fabsf(bf16_hi(v.z))), fmaxf(fabsf(bf16_lo(v.w)), fabsf(bf16_hi(v.w)))));
+        }
+    } else {
+        for (int64_t k = threadIdx.x; k < K; k += 256)
+            amax = fmaxf(amax, fabsf(kF32 ? wf[k] : __bfloat162float(wb[k])));
+    }
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = s_red[0];
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_red[i]);
+    const float s = __fdiv_rn(fmaxf(amax, 1e-8f), 448.f);
+    if (threadIdx.x == 0) scale[n] = s;
+    const ExactDiv d(s);
+    unsigned char* out = q + n * K;
+    if (vec) {
+        for (int64_t k = 8 * (int64_t)threadIdx.x; k < K; k += 8 * 256)
+            *reinterpret_cast<uint2*>(out + k) = quant8_e4m3(__ldg(reinterpret_cast<const uint4*>(wb + k)), d);
+        return;
+    }
+    for (int64_t k = 2 * (int64_t)threadIdx.x; k < K; k += 512) {          // K is even: two codes per store
+        const float a = kF32 ? wf[k] : __bfloat162float(wb[k]);
+        const float b = kF32 ? wf[k + 1] : __bfloat162float(wb[k + 1]);
+        *reinterpret_cast<uint16_t*>(out + k) = cvt_e4m3x2(d(a), d(b));
+    }
+}
+
+cudaError_t launch_quantize_weight(const void* w, bool w_is_f32, int64_t ldw, unsigned char* q, float* scale, int64_t N,
+                                   int64_t K, cudaStream_t stream) {
+    if (N == 0 || K == 0) return cudaSuccess;
+    if (w_is_f32) quantize_weight_kernel<true><<<(unsigned)N, 256, 0, stream>>>(w, ldw, q, scale, K);
+    else quantize_weight_kernel<false><<<(unsigned)N, 256, 0, stream>>>(w, ldw, q, scale, K);
+    return cudaGetLastError();
+}
+
+// Running maximum of |x| for the static activation scale of the exporter's calibration:
+// *amax = max(*amax, max |x[m][k]|).  Non-negative floats order like their bit patterns, so the
+// update is an integer atomicMax.
+__global__ void __launch_bounds__(256)
+abs_max_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int64_t M, int64_t K, float* __restrict__ amax) {
+    const int64_t vec_per_row = K / 8;
+    const int64_t total = M * vec_per_row;
+    float m = 0.f;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / vec_per_row;
+        const int64_t c = (i - r * vec_per_row) * 8;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + r * ldx + c));
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(bf16_lo(v.x)), fabsf(bf16_hi(v.x))), fmaxf(fabsf(bf16_lo(v.y)), fabsf(bf16_hi(v.y)))));
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(bf16_lo(v.z)), fabsf(bf16_hi(v.z))), fmaxf(fabsf(bf16_lo(v.w)), fabsf(bf16_hi(v.w)))));
+    }
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(m));
+}
+
+cudaError_t launch_abs_max(const __nv_bfloat16* x, int64_t ldx, int64_t M, int64_t K, float* amax, cudaStream_t stream) {
+    const int64_t total = M * (K / 8);
+    if (total == 0) return cudaSuccess;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    abs_max_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, M, K, amax);
+    return cudaGetLastError();
+}
+
 // Pack e4m3 weight bytes into the tiled layout (see pack_offset).  One CTA fills one
 // 128 x 128 tile through shared memory; `src_is_kn` selects the source orientation:
 // [K][N] (the reference's runtime buffer) or [N][K] (the checkpoint's layout).

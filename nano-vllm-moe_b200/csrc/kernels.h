@@ -48,6 +48,9 @@ cudaError_t launch_stream(int scheme, const StreamPlan& plan, StreamArgs args, c
 // ---- elementwise helpers (elementwise.cu) ------------------------------------
 cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* input_scale,
                              unsigned char* xq, int64_t M, int64_t K, cudaStream_t stream);
+cudaError_t launch_quantize_weight(const void* w, bool w_is_f32, int64_t ldw, unsigned char* q, float* scale, int64_t N,
+                                   int64_t K, cudaStream_t stream);
+cudaError_t launch_abs_max(const __nv_bfloat16* x, int64_t ldx, int64_t M, int64_t K, float* amax, cudaStream_t stream);
 cudaError_t launch_pack_tiles(const unsigned char* src, unsigned char* dst, int64_t K, int64_t N, bool src_is_kn,
                               cudaStream_t stream);
 

@@ -137,7 +137,7 @@ def quantize_weight_per_channel(weight_nk: np.ndarray) -> tuple[np.ndarray, np.n
 
 def input_scale_from_amax(amax: float) -> np.float32:
     """Static activation scale = max(amax, 1e-8) / 448 (quantize.py:200-203)."""
-    return np.float32(np.float32(max(float(amax), 1e-8)) / np.float32(FP8_MAX))
+    return np.float32(max(float(amax), 1e-8) / FP8_MAX)      # in double, rounded once, as the exporter does
 
 
 def quantize_activation(x: np.ndarray, input_scale) -> np.ndarray:

@@ -18,6 +18,9 @@ What is recorded, and which reference code produced it:
                     known-answer patterns; the dequant-then-matmul formula of
                     scripts/quantization/w8a16_linear_microbench.py:47-48; and the
                     epilogue algebra of kernels/fp8.py:331-338 evaluated with torch
+  checkpoint.npz    scripts/quantization/quantize.py should_quantize + quantize_fp8_per_output_channel over a
+                    tiny state dict, written as safetensors and loaded by nanovllm/utils/loader.py
+                    load_model into a block built from the reference's own layer classes (tp=1 and tp=2)
   moe.npz           executor/moe/router.py SoftmaxTopKRouter, experts/eager_experts.py
                     EagerExperts, prepare_finalize/no_ep.py NoEPPrepareFinalize,
                     utils/moe.py moe_align_block_size
@@ -243,9 +246,115 @@ def gen_moe():
     np.savez_compressed(HERE / "moe.npz", **out)
 
 
+def _tiny_block(layers_mod, cfg, nn):
+    """model.layers.0.{self_attn.{qkv_proj,o_proj}, mlp.{gate_up_proj,down_proj}} + model.norm, the
+    fused-module naming of the reference's Qwen2 (models/qwen2.py:193-199)."""
+    hidden, heads, kv_heads, head_dim, inter = 64, 4, 2, 16, 96
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.qkv_proj = layers_mod.QKVParallelLinear(hidden, head_dim, heads, kv_heads, bias=True,
+                                                         quant_method=cfg.get_quant_method(self, "self_attn.qkv_proj"))
+            self.o_proj = layers_mod.RowParallelLinear(heads * head_dim, hidden,
+                                                       quant_method=cfg.get_quant_method(self, "self_attn.o_proj"))
+
+    class Mlp(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_up_proj = layers_mod.MergedColumnParallelLinear(hidden, [inter, inter],
+                                                                      quant_method=cfg.get_quant_method(self, "mlp.gate_up_proj"))
+            self.down_proj = layers_mod.RowParallelLinear(inter, hidden, quant_method=cfg.get_quant_method(self, "mlp.down_proj"))
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.self_attn, self.mlp = Attn(), Mlp()
+            self.input_layernorm = nn.LayerNorm(hidden)
+
+    class Inner(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Layer()])
+            self.norm = nn.LayerNorm(hidden)
+
+    class Model(nn.Module):
+        packed_modules_mapping = {"q_proj": ("qkv_proj", "q"), "k_proj": ("qkv_proj", "k"), "v_proj": ("qkv_proj", "v"),
+                                  "gate_proj": ("gate_up_proj", 0), "up_proj": ("gate_up_proj", 1)}
+
+        def __init__(self):
+            super().__init__()
+            self.model = Inner()
+
+    return Model()
+
+
+def tiny_state_dict():
+    """Seeded plain checkpoint of the tiny block (HF naming: separate q/k/v and gate/up)."""
+    rng = np.random.default_rng(11)
+    hidden, inter = 64, 96
+    w = lambda n, k: O.bf16_round((rng.standard_normal((n, k)) * 0.05).astype(np.float32))          # noqa: E731
+    pre = "model.layers.0."
+    return {
+        pre + "self_attn.q_proj.weight": w(64, hidden), pre + "self_attn.k_proj.weight": w(32, hidden),
+        pre + "self_attn.v_proj.weight": w(32, hidden), pre + "self_attn.o_proj.weight": w(hidden, 64),
+        pre + "self_attn.q_proj.bias": w(1, 64)[0], pre + "self_attn.k_proj.bias": w(1, 32)[0],
+        pre + "self_attn.v_proj.bias": w(1, 32)[0],
+        pre + "mlp.gate_proj.weight": w(inter, hidden), pre + "mlp.up_proj.weight": w(inter, hidden),
+        pre + "mlp.down_proj.weight": w(hidden, inter),
+        pre + "input_layernorm.weight": w(1, hidden)[0], "model.norm.weight": w(1, hidden)[0],
+        "model.embed_tokens.weight": w(40, hidden), "lm_head.weight": w(40, hidden),
+        "model.layers.0.unknown_extra.weight": w(4, 4),
+    }
+
+
+def gen_checkpoint():
+    import tempfile
+    import warnings
+
+    import quantize as ref_export
+    from nanovllm.layers import linear as ref_layers
+    from nanovllm.quantization.fp8 import Fp8Config
+    from nanovllm.utils.loader import load_model
+    from safetensors.torch import save_file
+    from torch import nn
+
+    state = tiny_state_dict()
+    out = {}
+    tensors = {}
+    in_scales = {}
+    for i, (name, arr) in enumerate(state.items()):
+        t = torch.from_numpy(arr).to(torch.bfloat16)
+        if ref_export.should_quantize(name, t):
+            base = name[: -len(".weight")]
+            q, s = ref_export.quantize_fp8_per_output_channel(t)
+            tensors[base + ".qweight"], tensors[base + ".weight_scale"] = q, s
+            in_scales[base] = torch.tensor(0.01 + 0.001 * i, dtype=torch.float32)
+            tensors[base + ".input_scale"] = in_scales[base]
+        else:
+            tensors[name] = t
+    for name, t in tensors.items():
+        out["ckpt/" + name] = f32(t) if t.dtype == torch.bfloat16 else t.numpy()
+    with tempfile.TemporaryDirectory() as tmp:
+        save_file({k: v.contiguous() for k, v in tensors.items()}, os.path.join(tmp, "model.safetensors"))
+        for tp in (1, 2):
+            for rank in range(tp):
+                with _FakeDist(tp, rank):
+                    model = _tiny_block(ref_layers, Fp8Config("fp8_w8a8_static"), nn)
+                    with warnings.catch_warnings(record=True) as caught:
+                        warnings.simplefilter("always")
+                        load_model(model, tmp)
+                    named = dict(model.named_parameters())
+                    named.update(dict(model.named_buffers()))
+                    for name, t in named.items():
+                        out[f"tp{tp}_r{rank}/" + name] = f32(t) if t.dtype in (torch.bfloat16, torch.float32) else t.numpy()
+                    out[f"tp{tp}_r{rank}/__warned__"] = np.array([str(w.message) for w in caught])
+    np.savez_compressed(HERE / "checkpoint.npz", **out)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     torch.set_num_threads(1)
-    gen_codec(); gen_act_quant(); gen_weight_quant(); gen_loaders(); gen_linear(); gen_moe()
+    gen_codec(); gen_act_quant(); gen_weight_quant(); gen_loaders(); gen_linear(); gen_moe(); gen_checkpoint()
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)
