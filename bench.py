@@ -473,7 +473,12 @@ def bench_moe(args, T):
     in13 = (calib.float().abs().amax() / 448.0).reshape(())
     wts = moe.Fp8ExpertWeights.from_checkpoint_layout(q13, s13, in13, q2, s2, torch.tensor(4.0 / 448.0))
     del q13, q2
-    pf = moe.TorchAllToAllPrepareFinalize(cfg) if world > 1 else moe.NoEPPrepareFinalize(cfg)
+    if world == 1:
+        pf = moe.NoEPPrepareFinalize(cfg)
+    elif args.ep_dispatch == "dynamic":      # the reference's exchange: variable splits, counts read back on the host
+        pf = moe.TorchAllToAllPrepareFinalize(cfg)
+    else:                                    # fixed-capacity blocks: no host round trip, graph-capturable
+        pf = moe.FixedCapacityAllToAllPrepareFinalize(cfg)
     kern = moe.MoEKernel(prepare_finalize=pf, experts=moe.Fp8Experts(), parallel_config=cfg)
     router = moe.SoftmaxTopKRouter(K, False)
     sets = 8   # inputs are cycled so that small batches do not keep hitting the same L2-resident experts
@@ -487,7 +492,7 @@ def bench_moe(args, T):
     for i in range(sets):
         run(i)
     torch.cuda.synchronize()
-    graphs, use_graph = [], (world == 1 and not args.no_graph)
+    graphs, use_graph = [], (not args.no_graph and pf.supports_cuda_graph)
     if use_graph:
         side = torch.cuda.Stream(dev)
         with torch.cuda.stream(side):
@@ -564,7 +569,9 @@ def bench_moe(args, T):
             "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 -> bf16", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_rank": T, **MOE, "parallelism": f"ep{world}" if world > 1 else "single",
                        "l2": f"expert weights {el * 3 * H * I / 1e6:.0f} MB per rank > 126 MB L2; inputs cycled over {sets} sets",
-                       "launch": "cuda-graph replay" if use_graph else "eager"},
+                       "launch": "cuda-graph replay" if use_graph else "eager",
+                       "ep_dispatch": ("fixed-capacity all-to-all" if args.ep_dispatch == "fixed" else
+                                       "variable-split all-to-all, host-side counts") if world > 1 else None},
             "clocks": clocks,
             "shapes": [{"layer": "moe_ffn", "tokens": T, "us": ms * 1e3, "tflops": flops_rank / (ms * 1e-3) / 1e12,
                         "gbs": by / world / (ms * 1e-3) / 1e9, "bound": bound, "frac": ach / peak}],
@@ -575,6 +582,7 @@ def bench_moe(args, T):
                     "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
             "gpu_launches": 6 * args.steps, "device_status": status}), flush=True)
     if world > 1:
+        graphs.clear()               # captured graphs hold NCCL work
         torch.cuda.synchronize()
         dist.barrier()
         sys.stdout.flush()
@@ -591,6 +599,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--ep-dispatch", choices=["fixed", "dynamic"], default="fixed",
+                    help="MoE workloads on N > 1 ranks: fixed-capacity all-to-all (graph-capturable) or the "
+                         "reference's variable-split exchange with host-side counts")
     ap.add_argument("--peer-reduce", choices=["auto", "on", "off"], default="auto",
                     help="row-parallel layers: reduce through peer-memory stores in the GEMM epilogue (on), "
                          "NCCL all-reduce after the GEMM (off), or by local K (auto, the layer default)")

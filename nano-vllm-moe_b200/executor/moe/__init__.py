@@ -2,8 +2,9 @@
 from .config import MoEParallelConfig, make_moe_parallel_config
 from .experts import Fp8Experts, Fp8ExpertWeights
 from .kernel import MoEKernel
-from .prepare_finalize import NoEPPrepareFinalize, PrepareResult, TorchAllToAllPrepareFinalize
+from .prepare_finalize import (FixedCapacityAllToAllPrepareFinalize, NoEPPrepareFinalize, PrepareResult,
+                               TorchAllToAllPrepareFinalize)
 from .router import MoERouter, SoftmaxTopKRouter
 
 __all__ = ["MoEParallelConfig", "make_moe_parallel_config", "Fp8Experts", "Fp8ExpertWeights", "MoEKernel",
-           "NoEPPrepareFinalize", "TorchAllToAllPrepareFinalize", "PrepareResult", "MoERouter", "SoftmaxTopKRouter"]
+           "NoEPPrepareFinalize", "TorchAllToAllPrepareFinalize", "FixedCapacityAllToAllPrepareFinalize", "PrepareResult", "MoERouter", "SoftmaxTopKRouter"]

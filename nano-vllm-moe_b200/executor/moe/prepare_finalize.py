@@ -103,3 +103,83 @@ class TorchAllToAllPrepareFinalize:
         if reduce_tp and cfg.tp_size > 1:
             dist.all_reduce(out, group=cfg.tp_group)
         return out
+
+
+class FixedCapacityAllToAllPrepareFinalize:
+    """Expert parallel without host round trips: every rank sends every other rank a block of exactly
+    ``capacity`` row slots (rows for that rank first, padding after), so all split sizes are known
+    when the call is made, nothing is read back to the host, and the whole dispatch -> experts ->
+    combine sequence can be captured in a CUDA graph.  This is the step the reference leaves open
+    (todo.md:48; torch_alltoall.py:11-12 marks its own exchange as not graph-capturable because of the
+    ``.tolist()`` split sizes).
+
+    Padding slots carry local expert id -1: the expert kernels skip ids outside the local range and
+    leave those output rows zero.  ``capacity`` defaults to all ``T * k`` routed rows of the sending
+    rank, which can never overflow; a smaller ``capacity_factor`` (slots = factor * T * k / ep_size,
+    rounded up) moves fewer bytes, and rows that do not fit are dropped (they add zero); the number of
+    dropped rows of the last call is kept on the device in ``last_overflow`` for the caller to inspect
+    outside the hot path.
+    """
+    supports_cuda_graph = True
+    uses_dynamic_alltoall = False
+
+    def __init__(self, parallel_config: MoEParallelConfig, capacity_factor: float | None = None) -> None:
+        if parallel_config.ep_size <= 1:
+            raise ValueError("FixedCapacityAllToAllPrepareFinalize requires ep_size > 1")
+        if capacity_factor is not None and capacity_factor <= 0:
+            raise ValueError("capacity_factor must be positive")
+        self.parallel_config = parallel_config
+        self.capacity_factor = capacity_factor
+        self.last_overflow: torch.Tensor | None = None
+
+    def capacity(self, routed_rows: int) -> int:
+        if self.capacity_factor is None:
+            return routed_rows
+        ep = self.parallel_config.ep_size
+        return max(1, min(routed_rows, -(-int(self.capacity_factor * routed_rows) // ep)))
+
+    def prepare(self, x, topk_weights, topk_ids) -> PrepareResult:
+        cfg = self.parallel_config
+        ep, dev = cfg.ep_size, x.device
+        top_k = topk_ids.shape[-1]
+        rows = topk_ids.numel()
+        cap = self.capacity(rows)
+        flat_ids = topk_ids.reshape(-1).to(torch.long)
+        target = torch.div(flat_ids, cfg.local_num_experts, rounding_mode="floor").clamp_(0, ep - 1)
+        perm = torch.argsort(target, stable=True)                       # routed rows grouped by destination rank
+        tgt_sorted = target[perm]
+        counts = (tgt_sorted[:, None] == torch.arange(ep, device=dev)[None, :]).sum(dim=0)      # no host sync
+        starts = torch.cumsum(counts, 0) - counts
+        pos = torch.arange(rows, device=dev) - starts[tgt_sorted]       # position inside the destination's block
+        fits = pos < cap
+        self.last_overflow = (~fits).sum()
+        slot = torch.where(fits, tgt_sorted * cap + pos, torch.full_like(pos, ep * cap))      # overflow -> spill row
+        send_x = torch.zeros((ep * cap + 1, x.shape[1]), dtype=x.dtype, device=dev)
+        send_ids = torch.full((ep * cap + 1,), -1, dtype=torch.long, device=dev)
+        send_w = torch.zeros((ep * cap + 1,), dtype=torch.float32, device=dev)
+        send_x[slot] = x[torch.div(perm, top_k, rounding_mode="floor")]
+        send_ids[slot] = (flat_ids % cfg.local_num_experts)[perm]
+        send_w[slot] = topk_weights.reshape(-1).to(torch.float32)[perm]
+        send_ids[ep * cap:].fill_(-1)                                    # whatever overflowed into the spill row is padding
+        recv_x = torch.empty((ep * cap, x.shape[1]), dtype=x.dtype, device=dev)
+        recv_ids = torch.empty((ep * cap,), dtype=torch.long, device=dev)
+        recv_w = torch.empty((ep * cap,), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(recv_x, send_x[: ep * cap], group=cfg.ep_group)           # equal splits: cap rows per rank
+        dist.all_to_all_single(recv_ids, send_ids[: ep * cap], group=cfg.ep_group)
+        dist.all_to_all_single(recv_w, send_w[: ep * cap], group=cfg.ep_group)
+        return PrepareResult(recv_x, recv_ids, recv_w, {"top_k": top_k, "x_div": 1, "perm": perm, "slot": slot, "fits": fits,
+                                                         "cap": cap})
+
+    def finalize(self, expert_out, prepared, *, output_shape, model_dtype, reduce_tp=True):
+        cfg = self.parallel_config
+        tokens, hidden = output_shape
+        ctx = prepared.ctx
+        ep, cap = cfg.ep_size, ctx["cap"]
+        back = torch.zeros((ep * cap + 1, hidden), dtype=model_dtype, device=expert_out.device)     # last row: zeros for dropped rows
+        dist.all_to_all_single(back[: ep * cap], expert_out.to(model_dtype).contiguous(), group=cfg.ep_group)
+        routed = torch.empty((tokens * ctx["top_k"], hidden), dtype=model_dtype, device=expert_out.device)
+        routed[ctx["perm"]] = back[ctx["slot"]]
+        out = _sum_over_slots(routed, tokens, ctx["top_k"], hidden, model_dtype)
+        if reduce_tp and cfg.tp_size > 1:
+            dist.all_reduce(out, group=cfg.tp_group)
+        return out

@@ -23,7 +23,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, routing, result_dir):
+def _worker(rank, world, port, routing, result_dir, flavour="dynamic"):
     sys.path.insert(0, str(ROOT))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -32,7 +32,12 @@ def _worker(rank, world, port, routing, result_dir):
     E, k, T, H = 8, 2, 12, 16
     cfg = moe.make_moe_parallel_config(tp_group=None, ep_group=dist.group.WORLD, global_num_experts=E, intermediate_size=32)
     assert cfg.local_num_experts == E // world and cfg.ep_rank == rank
-    pf = moe.TorchAllToAllPrepareFinalize(cfg)
+    if flavour == "dynamic":
+        pf = moe.TorchAllToAllPrepareFinalize(cfg)
+    elif flavour == "fixed":
+        pf = moe.FixedCapacityAllToAllPrepareFinalize(cfg)
+    else:                                                  # tight capacity: rows that do not fit are dropped
+        pf = moe.FixedCapacityAllToAllPrepareFinalize(cfg, capacity_factor=1.0)
     g = torch.Generator().manual_seed(100 + rank)
     x = torch.randn((T, H), generator=g)
     if routing == "balanced":
@@ -45,23 +50,54 @@ def _worker(rank, world, port, routing, result_dir):
     prep = pf.prepare(x, w, ids)
     # every received row must belong to one of this rank's experts
     assert prep.topk_ids.numel() == prep.hidden_states.shape[0] == prep.topk_weights.numel()
-    assert ((prep.topk_ids >= 0) & (prep.topk_ids < cfg.local_num_experts)).all()
+    valid = prep.topk_ids >= 0
+    if flavour == "dynamic":
+        assert valid.all()
+    else:
+        assert prep.hidden_states.shape[0] == world * pf.capacity(T * k)           # fixed shapes, padding marked -1
+        assert (prep.topk_ids[~valid] == -1).all()
+    assert (prep.topk_ids[valid] < cfg.local_num_experts).all()
     local_out = prep.hidden_states * (prep.topk_ids[:, None].float() + 1.0) * prep.topk_weights[:, None] + 100.0 * rank
+    local_out = torch.where(valid[:, None], local_out, torch.zeros_like(local_out))   # what the expert kernels do with id -1
     y = pf.finalize(local_out, prep, output_shape=(T, H), model_dtype=torch.float32, reduce_tp=False)
     owner = ids // cfg.local_num_experts
     local = ids % cfg.local_num_experts
-    want = (x[:, None, :] * (local[..., None].float() + 1.0) * w[..., None] + 100.0 * owner[..., None].float()).sum(dim=1)
-    np.save(Path(result_dir) / f"ok_{routing}_{rank}.npy", np.array([float((y - want).abs().max())]))
+    terms = x[:, None, :] * (local[..., None].float() + 1.0) * w[..., None] + 100.0 * owner[..., None].float()
+    dropped = 0
+    if flavour == "tight":
+        # a routed row is kept iff fewer than `capacity` earlier routed rows of this rank go to the same owner
+        cap = pf.capacity(T * k)
+        flat_owner = owner.reshape(-1)
+        seen = torch.zeros(world, dtype=torch.long)
+        keep = torch.zeros(T * k, dtype=torch.bool)
+        for r in range(T * k):
+            keep[r] = seen[flat_owner[r]] < cap
+            seen[flat_owner[r]] += 1
+        terms = terms * keep.view(T, k, 1)
+        dropped = int((~keep).sum())
+        assert int(pf.last_overflow) == dropped
+    elif flavour == "fixed":
+        assert int(pf.last_overflow) == 0
+    want = terms.sum(dim=1)
+    np.save(Path(result_dir) / f"ok_{routing}_{rank}.npy", np.array([float((y - want).abs().max()), float(dropped)]))
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("flavour", ["dynamic", "fixed", "tight"])
 @pytest.mark.parametrize("routing", ["balanced", "skewed", "random"])
-def test_alltoall_dispatch_combine_closed_form(tmp_path, routing):
+def test_alltoall_dispatch_combine_closed_form(tmp_path, routing, flavour):
+    """dynamic = variable splits with host-side counts (the reference's exchange); fixed = fixed-capacity
+    blocks, no host round trip; tight = the same with capacity for a balanced load only (skewed routing
+    overflows and the dropped rows must be exactly the late ones)."""
     port = _free_port()
-    mp.spawn(_worker, args=(2, port, routing, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, routing, str(tmp_path), flavour), nprocs=2, join=True)
+    dropped = 0.0
     for rank in range(2):
-        err = float(np.load(tmp_path / f"ok_{routing}_{rank}.npy")[0])
-        assert err < 1e-5, (routing, rank, err)
+        err, d = np.load(tmp_path / f"ok_{routing}_{rank}.npy")
+        assert err < 1e-5, (routing, flavour, rank, err)
+        dropped += d
+    if flavour == "tight" and routing == "skewed":
+        assert dropped > 0
 
 
 def _row_parallel_worker(rank, world, port, result_dir):

@@ -71,3 +71,73 @@ def test_row_parallel_nccl_and_peer_reduce(tmp_path, world):
             assert ok, (rank, key, worst)
         np.testing.assert_array_equal(d["peer1"], d["peer2"])
         np.testing.assert_array_equal(outs[0]["peer1"], d["peer1"])            # every rank ends with the same bits
+
+
+def _ep_worker(rank, world, port, out_dir):
+    """Expert parallel on real kernels: the variable-split exchange, the fixed-capacity exchange (eager and
+    replayed from a CUDA graph) and, on the same tokens, one rank holding every expert must agree bit for bit
+    (a routed row's arithmetic does not depend on which rank or position it is computed at)."""
+    import torch.distributed as dist
+    from datetime import timedelta
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(seconds=90))
+    moe = importlib.import_module("nano-vllm-moe_b200.executor.moe")
+    E, K, T, H, I = 8, 2, 96, 256, 128
+    g = torch.Generator(device=dev).manual_seed(77)                      # the same full expert set on every rank
+    def codes(*shape):
+        w = torch.randn(shape, generator=g, device=dev) * 0.05
+        s = w.abs().amax(dim=-1).clamp(min=1e-8) / 448.0
+        return (w / s[..., None]).to(torch.float8_e4m3fn).view(torch.uint8), s
+    q13, s13 = codes(E, 2 * I, H)
+    q2, s2 = codes(E, H, I)
+    in13, in2 = torch.tensor(4.0 / 448.0), torch.tensor(2.0 / 448.0)
+    gr = torch.Generator(device=dev).manual_seed(1000 + rank)            # every rank brings its own tokens
+    x = torch.randn((T, H), generator=gr, device=dev).to(torch.bfloat16)
+    ids = torch.randint(0, E, (T, K), generator=gr, device=dev)
+    w = torch.rand((T, K), generator=gr, device=dev)
+    full_cfg = moe.make_moe_parallel_config(tp_group=None, ep_group=None, global_num_experts=E, intermediate_size=I)
+    full = moe.MoEKernel(prepare_finalize=moe.NoEPPrepareFinalize(full_cfg), experts=moe.Fp8Experts(), parallel_config=full_cfg)
+    y_full = full(x, w, ids, moe.Fp8ExpertWeights.from_checkpoint_layout(q13, s13, in13, q2, s2, in2), model_dtype=torch.bfloat16)
+    cfg = moe.make_moe_parallel_config(tp_group=None, ep_group=dist.group.WORLD, global_num_experts=E, intermediate_size=I)
+    el = cfg.local_num_experts
+    mine = slice(rank * el, (rank + 1) * el)
+    wts = moe.Fp8ExpertWeights.from_checkpoint_layout(q13[mine], s13[mine], in13, q2[mine], s2[mine], in2)
+    outs = {"full": y_full}
+    for name, pf in (("dynamic", moe.TorchAllToAllPrepareFinalize(cfg)), ("fixed", moe.FixedCapacityAllToAllPrepareFinalize(cfg))):
+        kern = moe.MoEKernel(prepare_finalize=pf, experts=moe.Fp8Experts(), parallel_config=cfg)
+        outs[name] = kern(x, w, ids, wts, model_dtype=torch.bfloat16)
+        if name == "fixed":
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream(dev)
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                kern(x, w, ids, wts, model_dtype=torch.bfloat16)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(gph, stream=side):
+                    y_graph = kern(x, w, ids, wts, model_dtype=torch.bfloat16)
+            gph.replay()
+            torch.cuda.synchronize()
+            outs["fixed_graph"] = y_graph.clone()
+            assert int(pf.last_overflow) == 0
+            del gph
+    torch.cuda.synchronize()
+    np.savez(Path(out_dir) / f"ep{rank}.npz", **{k: v.float().cpu().numpy() for k, v in outs.items()})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_exchanges_agree_on_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_ep_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for rank in range(2):
+        d = np.load(tmp_path / f"ep{rank}.npz")
+        assert np.abs(d["full"]).max() > 0
+        for key in ("dynamic", "fixed", "fixed_graph"):
+            np.testing.assert_array_equal(d[key], d["full"], err_msg=f"rank {rank} {key}")
