@@ -876,15 +876,20 @@ def main():
     # the pipelined path returns what the plain call returns
     torch.testing.assert_close(host_out[0][order[0]].to(dev), layers[2 % copies][order[0]](xs_dev[order[0]]), rtol=0, atol=0)
     barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(s_out)
-    s_in.wait_event(a)
-    s_comp.wait_event(a)
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e2e_join(b)
-    barrier()
-    e2e_ms = a.elapsed_time(b) / e2e_steps
+    # three timed windows, the median reported: host<->device copies share the PCIe switch and the host's
+    # memory with whatever else runs on the machine
+    windows = []
+    for _ in range(3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(s_out)
+        s_in.wait_event(a)
+        s_comp.wait_event(a)
+        for i in range(e2e_steps):
+            e2e_step(i)
+        e2e_join(b)
+        barrier()
+        windows.append(a.elapsed_time(b) / e2e_steps)
+    e2e_ms = sorted(windows)[1]
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -915,7 +920,8 @@ def main():
             "clocks": clocks, "shapes": shapes, "roofline": roofline,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h,
-                    "pipeline": "pinned host buffers; H2D, compute and D2H on three streams, two steps in flight"},
+                    "pipeline": "pinned host buffers; H2D, compute and D2H on three streams, two steps in flight",
+                    "windows_ms": windows},
             "gpu_launches": kernels_per_pass * args.steps, "device_status": status,
         }
         if cpu is not None:
