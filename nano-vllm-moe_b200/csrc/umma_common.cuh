@@ -173,6 +173,20 @@ __host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n, uint32_t a_fm
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Opt a kernel in to `bytes` of dynamic shared memory once per device (function attributes are per device).
+struct SmemOptIn {
+    bool done[64] = {};
+};
+inline cudaError_t ensure_dynamic_smem(const void* kernel, int bytes, SmemOptIn& state) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && state.done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) state.done[dev] = true;
+    return e;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

@@ -665,11 +665,10 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     using Cfg = UmmaCfg<BN>;
     static_assert(!kNarrow || (BN == 256 && !kSplit), "half-width items exist in the 256-wide persistent kernel only");
     auto kern = umma_gemm_kernel<BN, kSplit, kF16, kNarrow>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    static SmemOptIn opted;
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kSmemBytes, opted);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     UmmaSched s;
     s.m_tiles = pl.m_tiles; s.n_tiles = pl.n_tiles; s.splits = splits;

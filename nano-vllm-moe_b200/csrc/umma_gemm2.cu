@@ -344,11 +344,10 @@ template <bool kF16, bool kMlp>
 cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& ty,
                         cudaStream_t stream, const char** why, const float* h_scale = nullptr) {
     auto kern = umma_pair_gemm_kernel<kF16, kMlp>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    static SmemOptIn opted;
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, kSmemBytes, opted);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     PairSched s;
     s.mp_tiles = (a.M + 2 * kBM - 1) / (2 * kBM);

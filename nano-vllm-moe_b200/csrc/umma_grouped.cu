@@ -262,11 +262,10 @@ template <int MP, bool kGather>
 static cudaError_t launch_grouped(const GroupedArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
     using Cfg = GroupedCfg<MP>;
     auto kern = grouped_w8a8_kernel<MP, kGather>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    static SmemOptIn opted;
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kSmemBytes, opted);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(148);

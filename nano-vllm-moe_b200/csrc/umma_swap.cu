@@ -408,11 +408,10 @@ static cudaError_t launch_swap(const SwapPlan& pl, const UmmaArgs& a, const CUte
                                cudaStream_t stream) {
     using Cfg = SwapCfg<MP, kPreQ>;
     auto kern = swap_w8a8_kernel<MP, kSplit, kPreQ>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    static SmemOptIn opted;
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kSmemBytes, opted);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     SwapSched s;
     s.n_tiles = pl.n_tiles; s.splits = pl.splits;

@@ -404,11 +404,10 @@ static cudaError_t launch_swap16(const SwapPlan& pl, const UmmaArgs& a, const CU
                                  cudaStream_t stream) {
     using Cfg = Swap16Cfg<MP>;
     auto kern = swap_w8a16_kernel<MP, kSplit>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    static SmemOptIn opted;
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kSmemBytes, opted);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     Swap16Sched s;
     s.n_tiles = pl.n_tiles; s.splits = pl.splits;
