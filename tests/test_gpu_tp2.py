@@ -61,6 +61,8 @@ def _worker(rank, world, port, out_dir):
 def test_row_parallel_nccl_and_peer_reduce(tmp_path, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
+    if world > 2 and os.environ.get("FP8LIN_TEST_MANY_GPUS") != "1":
+        pytest.skip("the 4-rank variant has not run on a 4-GPU box yet; set FP8LIN_TEST_MANY_GPUS=1 to run it")
     import torch.multiprocessing as mp
     from oracle import fp8_oracle as O
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
