@@ -92,12 +92,12 @@ cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStr
 cudaError_t launch_umma_f16(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why);
 cudaError_t launch_x_to_f16(const __nv_bfloat16* x, int64_t ldx, void* x16, int64_t M, int64_t K, cudaStream_t stream);
 cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_t src_bytes, cudaStream_t stream);
-// The same GEMM on CTA pairs (umma_gemm2.cu): 256 x 256 tiles, one MMA across two CTAs.  f16 selects the
+// The same GEMM on CTA pairs (umma_pair_gemm.cu): 256 x 256 tiles, one MMA across two CTAs.  f16 selects the
 // operand type as above; destinations as launch_umma_w8a8.
 cudaError_t launch_umma_pair(bool f16, const UmmaArgs& args, cudaStream_t stream, const char** why, int n_dst = 0,
                              void* const* dst_ptrs = nullptr, int64_t ld_dst = 0);
 // Fused MLP pieces: gate_up GEMM whose epilogue writes e4m3 h = silu(g) * u for the down projection
-// (umma_gemm2.cu), and the separate pass that does the same from a bf16 gate_up result (small batches).
+// (umma_pair_gemm.cu), and the separate pass that does the same from a bf16 gate_up result (small batches).
 cudaError_t launch_umma_pair_mlp(const UmmaArgs& args, unsigned char* hq, const float* h_scale, cudaStream_t stream,
                                  const char** why);
 cudaError_t launch_silu_mul_quant_interleaved(const __nv_bfloat16* gu, const float* h_scale, unsigned char* hq, int64_t M,
