@@ -133,7 +133,9 @@ def export_state_dict(tensors: dict[str, torch.Tensor], scheme: str, input_scale
 
 
 def quantization_config(scheme: str) -> dict:
-    """The ``quantization_config`` block of ``config.json`` (quantize.py:83-91)."""
+    """The ``quantization_config`` block of ``config.json`` (quantize.py:83-91).  One value differs on
+    purpose: the exporter marks ``fp8_w8a8_static`` as ``"export_contract_only"`` because the reference had
+    no runtime for it when the exporter was written; here both schemes run, so both say ``"implemented"``."""
     w8a16 = scheme == "fp8_w8a16"
     return {
         "format": scheme,
