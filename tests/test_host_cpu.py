@@ -212,6 +212,17 @@ def test_gate_up_interleave_is_a_tile_row_permutation():
         K.interleave_gate_up(torch.from_numpy(O.pack_tiles(wq)), torch.from_numpy(scale), None, 200)
 
 
+def test_fused_mlp_wrapper_checks_its_layers(pkg):
+    cfg = pkg.Fp8Config("fp8_w8a8_static")
+    gate_up = pkg.MergedColumnParallelLinear(64, [128, 128], quant_method=cfg.get_quant_method(None, "mlp.gate_up_proj"))
+    down = pkg.RowParallelLinear(128, 64, quant_method=cfg.get_quant_method(None, "mlp.down_proj"))
+    with pytest.raises(ValueError, match="process_weights_after_loading"):
+        pkg.FusedFp8MLP(gate_up, down)                     # not prepacked (CPU-resident layers never are)
+    plain = pkg.RowParallelLinear(128, 64)
+    with pytest.raises(ValueError):
+        pkg.FusedFp8MLP(gate_up, plain)                    # unquantised projection
+
+
 def test_kernels_refuse_cpu_tensors(pkg):
     from importlib import import_module
     K = import_module("nano-vllm-moe_b200.quantization.kernels")
