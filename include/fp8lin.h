@@ -60,6 +60,10 @@ enum { FP8LIN_W8A16 = 0, FP8LIN_W8A8_STATIC = 1 };
 
 int fp8lin_version(void);
 const char* fp8lin_last_error(void);
+/* Number of kernel launches this library has made in this process (all devices, all streams).
+ * A measurement aid with no counterpart in the reference: difference it around a call (or around
+ * the capture of a CUDA graph) to know how many kernels that call enqueues. */
+unsigned long long fp8lin_launch_count(void);
 
 /* ---- weight prepack -------------------------------------------------------
  * Replaces the derived copies the reference builds in
@@ -126,13 +130,17 @@ int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_
  * exists for callers that cannot allocate: a server whose KV-cache pool has
  * taken all free HBM, or a latency-critical loop that must not risk the stall
  * an allocation can cause.  Its split-K scratch is a fixed 16 MiB (+64 KiB
- * header) array inside the library image, one copy per GPU, held from library
- * load to process exit.  Shapes whose split-K partial sums exceed 16 MiB, or
- * M > 64, are refused with FP8LIN_ERR_WORKSPACE.  The first call on each GPU
- * looks up the array's device address (cudaGetSymbolAddress) -- make that
- * first call outside any stream capture.  All calls on a GPU share the array:
- * calls that may overlap in time (different streams or threads) race on it and
- * must be serialised by the caller.  input_scale is ignored for FP8LIN_W8A16. */
+ * header) array inside the library image, one copy per GPU.  CUDA loads that
+ * part of the image lazily: a GPU sets its copy aside at the first call of this
+ * function on that GPU and holds it until the process exits.  Make that first
+ * call (any small shape) early on every GPU -- before the process gives the
+ * remaining HBM to a pool, else the call fails with FP8LIN_ERR_WORKSPACE -- and
+ * outside any stream capture: it looks up the array's device address with
+ * cudaGetSymbolAddress.  Shapes whose split-K partial sums exceed 16 MiB, or
+ * M > 64, are refused with FP8LIN_ERR_WORKSPACE.  All calls on a GPU share the
+ * array: calls that may overlap in time (different streams or threads) race on
+ * it and must be serialised by the caller.  input_scale is ignored for
+ * FP8LIN_W8A16. */
 int fp8lin_linear_static_scratch(int scheme, const void* x, int64_t ldx, const void* w_nk,
                                  const float* w_scale, const float* input_scale, const void* bias,
                                  void* y, int64_t ldy, int64_t M, int64_t K, int64_t N, void* stream);
@@ -156,6 +164,18 @@ int fp8lin_quantize_activation(const void* x, int64_t ldx, const float* input_sc
  * renormalisation; topk_w f32 [T][k], topk_ids i32 [T][k]. */
 int fp8lin_moe_route(const void* logits, int logits_dtype, int64_t ld, int64_t T, int E, int top_k,
                      int renormalize, float* topk_w, int32_t* topk_ids, void* stream);
+
+/* Grouping of routed rows by expert, the first step of fp8lin_moe_experts_w8a8, also callable on its
+ * own; replaces moe_align_block_size (nanovllm/utils/moe.py:4-52).  ids: int32 [rows] expert id per
+ * routed row (ids outside [0, E) are dropped: another expert-parallel rank owns them).  Outputs, all
+ * device memory: expert_offsets int32 [E + 1] (first sorted position of every expert), sorted_rows
+ * int32 [rows] (routed-row index at each sorted position; rows of one expert are adjacent, their
+ * order inside an expert is unspecified), chunks int32 [(E + rows/16 + 2)][4] = {expert, first sorted
+ * position, rows in the chunk, 0} with at most chunk_rows (16, 32, 64 or 128) rows each, meta int32 [2] =
+ * {number of chunks, number of kept rows}.  E <= 3071.  Unlike the reference's block list the chunks
+ * are not padded: a short chunk simply says how many rows it has. */
+int fp8lin_moe_align(const int32_t* ids, int64_t rows, int E, int chunk_rows, int32_t* expert_offsets,
+                     int32_t* sorted_rows, int32_t* chunks, int32_t* meta, void* stream);
 
 /* Scratch for fp8lin_moe_experts_w8a8 (zero-filled once, like the linear workspace). */
 size_t fp8lin_moe_workspace_bytes(int64_t rows, int E, int64_t H, int64_t I);

@@ -22,6 +22,7 @@ OK, ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_ARCH, ERR_LAUNCH, ERR_DEV
 SIGNATURES = {
     "fp8lin_version": (c_int, []),
     "fp8lin_last_error": (c_char_p, []),
+    "fp8lin_launch_count": (ctypes.c_ulonglong, []),
     "fp8lin_packed_bytes": (c_size_t, [c_int64, c_int64]),
     "fp8lin_prepack_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "fp8lin_pack_weight_nk": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
@@ -42,6 +43,7 @@ SIGNATURES = {
                                              c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "fp8lin_quantize_activation": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "fp8lin_moe_route": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fp8lin_moe_align": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "fp8lin_moe_workspace_bytes": (c_size_t, [c_int64, c_int, c_int64, c_int64]),
     "fp8lin_moe_experts_w8a8": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,

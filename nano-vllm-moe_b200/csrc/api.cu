@@ -1,5 +1,6 @@
 // extern "C" surface of libfp8lin.so (declared in include/fp8lin.h).
 #include <stdarg.h>
+#include <atomic>
 #include <stdio.h>
 #include <string.h>
 
@@ -167,6 +168,9 @@ bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
 }  // namespace
 
 namespace fp8lin {
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+bool device_is_sm100() { return check_arch() != 0; }
 static int g_pdl = 1;
 void set_pdl_enabled(int on) { g_pdl = on; }
 int pdl_attribute(cudaLaunchAttribute* attr) {
@@ -187,6 +191,7 @@ int set_error(int code, const char* fmt, ...) {
 extern "C" {
 
 int fp8lin_version(void) { return FP8LIN_VERSION; }
+unsigned long long fp8lin_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* fp8lin_last_error(void) { return g_err; }
 
 size_t fp8lin_packed_bytes(int64_t K, int64_t N) {
@@ -610,6 +615,20 @@ int fp8lin_moe_route(const void* logits, int logits_dtype, int64_t ld, int64_t T
     return FP8LIN_OK;
 }
 
+int fp8lin_moe_align(const int32_t* ids, int64_t rows, int E, int chunk_rows, int32_t* expert_offsets, int32_t* sorted_rows,
+                     int32_t* chunks, int32_t* meta, void* stream) {
+    if (rows < 0 || rows > (1ll << 24) || E <= 0 || E > 3071)
+        return fail(FP8LIN_ERR_SHAPE, "bad grouping shape rows=%lld E=%d (E <= 3071)", (long long)rows, E);
+    if (chunk_rows != 16 && chunk_rows != 32 && chunk_rows != 64 && chunk_rows != 128)
+        return fail(FP8LIN_ERR_ARG, "chunk_rows must be 16, 32, 64 or 128");
+    if (!ids || !expert_offsets || !sorted_rows || !chunks || !meta) return fail(FP8LIN_ERR_NULL, "a required pointer is NULL");
+    if (!aligned16(chunks)) return fail(FP8LIN_ERR_ALIGN, "chunks must be 16-byte aligned");
+    cudaError_t e = launch_moe_align(ids, (int)rows, E, chunk_rows, expert_offsets, sorted_rows, (int4*)chunks, meta,
+                                     (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "row grouping launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
 size_t fp8lin_moe_workspace_bytes(int64_t rows, int E, int64_t H, int64_t I) {
     if (rows < 0 || E <= 0 || H <= 0 || I <= 0) return FP8LIN_WS_HEADER_BYTES;
     return moe_ws_layout(rows, E, H, I).total;
@@ -620,8 +639,9 @@ int fp8lin_moe_experts_w8a8(const void* x, int64_t ldx, int x_div, const int32_t
                             const void* w2_packed, const float* w2_scale, const float* w2_input_scale,
                             int E, int64_t H, int64_t I, void* out_routed, int64_t ld_out,
                             void* workspace, size_t workspace_bytes, void* stream) {
-    if (rows < 0 || E <= 0 || E > 4096 || H <= 0 || I <= 0 || H % 16 != 0 || I % 16 != 0 || x_div <= 0)
-        return fail(FP8LIN_ERR_SHAPE, "bad MoE shape rows=%lld E=%d H=%lld I=%lld (H, I multiples of 16)", (long long)rows, E,
+    // E <= 3071: the row-grouping kernel keeps 4E + 2 counters in 48 KB of shared memory
+    if (rows < 0 || E <= 0 || E > 3071 || H <= 0 || I <= 0 || H % 16 != 0 || I % 16 != 0 || x_div <= 0)
+        return fail(FP8LIN_ERR_SHAPE, "bad MoE shape rows=%lld E=%d H=%lld I=%lld (E <= 3071; H, I multiples of 16)", (long long)rows, E,
                     (long long)H, (long long)I);
     if (rows == 0) return FP8LIN_OK;
     if (rows > (1ll << 24)) return fail(FP8LIN_ERR_SHAPE, "too many routed rows");

@@ -42,7 +42,7 @@ cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* i
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = pdl_attribute(attr);
     cfg.attrs = attr;
-    return cudaLaunchKernelEx(&cfg, act_quant_kernel, x, ldx, input_scale, xq, M, K);
+    return counted(cudaLaunchKernelEx(&cfg, act_quant_kernel, x, ldx, input_scale, xq, M, K));
 }
 
 // y[m][n] = bf16( sum over slots r of slots[r][m][n] ), added in slot order in fp32: the reduction step
@@ -78,7 +78,7 @@ cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t sl
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     sum_slots_kernel<<<(unsigned)blocks, 256, 0, stream>>>(slots, n_slots, slot_stride, y, ldy, M, N, ld_slot);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 // x (bf16, row pitch ldx) -> f16 [M][K] contiguous, round to nearest: the "A" operand of the
@@ -109,7 +109,7 @@ cudaError_t launch_x_to_f16(const __nv_bfloat16* x, int64_t ldx, void* x16, int6
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = pdl_attribute(attr);
     cfg.attrs = attr;
-    return cudaLaunchKernelEx(&cfg, x_to_f16_kernel, x, ldx, (__half*)x16, M, K);
+    return counted(cudaLaunchKernelEx(&cfg, x_to_f16_kernel, x, ldx, (__half*)x16, M, K));
 }
 
 // Packed e4m3 tiles (128 channels x 128 K bytes, 16 KiB each) -> packed f16 tiles (128 channels x 64
@@ -151,7 +151,7 @@ cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = pdl_attribute(attr);
     cfg.attrs = attr;
-    return cudaLaunchKernelEx(&cfg, dequant_tiles_f16_kernel, src, (unsigned char*)dst, src_bytes);
+    return counted(cudaLaunchKernelEx(&cfg, dequant_tiles_f16_kernel, src, (unsigned char*)dst, src_bytes));
 }
 
 // Small-batch half of the fused MLP: gu = bf16 [M][2I] as the gate_up GEMM wrote it with interleaved
@@ -197,7 +197,7 @@ cudaError_t launch_silu_mul_quant_interleaved(const __nv_bfloat16* gu, const flo
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = pdl_attribute(attr);
     cfg.attrs = attr;
-    return cudaLaunchKernelEx(&cfg, silu_mul_quant_interleaved_kernel, gu, h_scale, hq, M, I);
+    return counted(cudaLaunchKernelEx(&cfg, silu_mul_quant_interleaved_kernel, gu, h_scale, hq, M, I));
 }
 
 // ---- exporter arithmetic ------------------------------------------------------------------------
@@ -212,8 +212,9 @@ quantize_weight_kernel(const void* __restrict__ w_, int64_t ldw, unsigned char* 
     const int64_t n = blockIdx.x;
     const float* wf = reinterpret_cast<const float*>(w_) + n * ldw;
     const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w_) + n * ldw;
-    // bf16 rows that allow it are read 16 bytes at a time
-    const bool vec = !kF32 && K % 8 == 0 && ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(w_) & 15) == 0;
+    // bf16 rows that allow it are read 16 bytes and written 8 bytes at a time
+    const bool vec = !kF32 && K % 8 == 0 && ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(w_) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(q) & 7) == 0;
     float amax = 0.f;
     if (vec) {
         for (int64_t k = 8 * (int64_t)threadIdx.x; k < K; k += 8 * 256) {
@@ -251,7 +252,7 @@ cudaError_t launch_quantize_weight(const void* w, bool w_is_f32, int64_t ldw, un
     if (N == 0 || K == 0) return cudaSuccess;
     if (w_is_f32) quantize_weight_kernel<true><<<(unsigned)N, 256, 0, stream>>>(w, ldw, q, scale, K);
     else quantize_weight_kernel<false><<<(unsigned)N, 256, 0, stream>>>(w, ldw, q, scale, K);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 // Running maximum of |x| for the static activation scale of the exporter's calibration:
@@ -279,7 +280,7 @@ cudaError_t launch_abs_max(const __nv_bfloat16* x, int64_t ldx, int64_t M, int64
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     abs_max_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, M, K, amax);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 // Pack e4m3 weight bytes into the tiled layout (see pack_offset).  One CTA fills one
@@ -321,7 +322,7 @@ cudaError_t launch_pack_tiles(const unsigned char* src, unsigned char* dst, int6
     if (K == 0 || N == 0) return cudaSuccess;
     dim3 grid((unsigned)pack_ntiles(N), (unsigned)pack_kblocks(K));
     pack_tiles_kernel<<<grid, 256, 0, stream>>>(src, dst, K, N, src_is_kn ? 1 : 0);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 }  // namespace fp8lin

@@ -14,8 +14,18 @@ int set_error(int code, const char* fmt, ...);
 
 // Fills the attribute that makes a launch a programmatic dependent of the previous kernel in
 // its stream; returns the number of attributes written (0 when disabled by the tuning knob).
+// Whether the current device is an sm_100 part (cached per process; defined in api.cu).
+bool device_is_sm100();
 int pdl_attribute(cudaLaunchAttribute* attr);
 void set_pdl_enabled(int on);
+
+// Every kernel launch the library makes passes its result through counted(): successful launches
+// are tallied for fp8lin_launch_count() (defined in api.cu).
+void note_launch();
+inline cudaError_t counted(cudaError_t e) {
+    if (e == cudaSuccess) note_launch();
+    return e;
+}
 
 // ---- weight-streaming kernel (stream_kernel.cu) ------------------------------
 struct StreamArgs {

@@ -76,7 +76,7 @@ cudaError_t launch_moe_route(const void* logits, int logits_bf16, int64_t ld, in
     else
         moe_route_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)logits, ld, T, E, top_k, renormalize,
                                                                  out_w, out_ids);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 // ---- grouping of routed rows by expert ------------------------------------------------------
@@ -131,7 +131,7 @@ cudaError_t launch_moe_align(const int* ids, int rows, int E, int chunk_rows, in
                              int4* chunks, int* meta, cudaStream_t stream) {
     const size_t smem = (size_t)(4 * E + 2) * sizeof(int);
     moe_align_kernel<<<1, 1024, smem, stream>>>(ids, rows, E, chunk_rows, expert_offsets, sorted_rows, chunks, meta);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 // (Within an expert the rows land in the arrival order of the atomics.  Every routed row is an
@@ -167,12 +167,13 @@ cudaError_t launch_moe_gather_quant(const __nv_bfloat16* x, int64_t ldx, int x_d
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (blocks < 1) blocks = 1;
     moe_gather_quant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, x_div, sorted_rows, meta, input_scale, xq, H);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 // ---- h = silu(gate) * up, quantised for the down projection ----------------------------------
-// gu: bf16 [rows][2I] (gate | up), hq: e4m3 [rows][I].  h is rounded to bf16 first (it is the
-// tensor the reference materialises), then divided by the static scale.
+// gu: bf16 [rows][2I] (gate | up), hq: e4m3 [rows][I].  The reference's experts evaluate
+// F.silu(gate) * up as two eager bf16 ops (experts/eager_experts.py:33): silu(gate) is rounded to
+// bf16, the product is rounded to bf16 again; that tensor is then divided by the static scale.
 __global__ void __launch_bounds__(256)
 silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ input_scale,
                       unsigned char* __restrict__ hq, const int* __restrict__ meta, int I) {
@@ -193,8 +194,8 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float g0 = bf16_lo(gw[j]), g1 = bf16_hi(gw[j]);
-            const float s0 = g0 / (1.f + expf(-g0)), s1 = g1 / (1.f + expf(-g1));
-            hw[j] = pack_bf16x2(s0 * bf16_lo(uw[j]), s1 * bf16_hi(uw[j]));
+            const uint32_t sp = pack_bf16x2(g0 / (1.f + expf(-g0)), g1 / (1.f + expf(-g1)));
+            hw[j] = pack_bf16x2(bf16_lo(sp) * bf16_lo(uw[j]), bf16_hi(sp) * bf16_hi(uw[j]));
         }
         *reinterpret_cast<uint2*>(hq + r * I + c) = quant8_e4m3(h, div_scale);
     }
@@ -206,7 +207,7 @@ cudaError_t launch_silu_mul_quant(const __nv_bfloat16* gu, const float* input_sc
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (blocks < 1) blocks = 1;
     silu_mul_quant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(gu, input_scale, hq, meta, I);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 // ---- combine: y[t] = bf16( sum over the k routed rows of token t ) ---------------------------
@@ -239,7 +240,7 @@ cudaError_t launch_moe_combine(const __nv_bfloat16* routed, __nv_bfloat16* y, in
     int64_t blocks = ((int64_t)T * (H / 8) + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     moe_combine_kernel<<<(unsigned)blocks, 256, 0, stream>>>(routed, y, T, top_k, H);
-    return cudaGetLastError();
+    return counted(cudaGetLastError());
 }
 
 }  // namespace fp8lin

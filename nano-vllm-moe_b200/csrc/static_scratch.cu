@@ -5,8 +5,13 @@
 // HBM to its KV-cache pool, so a later cudaMalloc for split-K scratch would
 // fail; and code on a latency-critical path (a decode loop, a callback) where
 // an allocation may stall behind a device-wide synchronisation.  For them the
-// scratch lives inside the library image: one fixed array per GPU, reserved
-// when the library is loaded on that GPU and held until the process exits.
+// scratch lives inside the library image: one fixed array per GPU.  CUDA loads
+// the module that holds it lazily, so a GPU sets its copy aside at the FIRST
+// call of this entry point on that GPU (the cudaGetSymbolAddress below) and
+// keeps it until the process exits.  Make that first call early -- one tiny
+// warm-up call per GPU is enough -- before the process hands the remaining HBM
+// to its pool, and outside any stream capture; if the memory is already gone
+// the call reports FP8LIN_ERR_WORKSPACE.
 //
 // The array is shared by every call on that GPU and keeps whatever the last
 // call left in it.  The only part that has to start at zero -- the split-K
@@ -70,12 +75,13 @@ extern "C" int fp8lin_linear_static_scratch(int scheme, const void* x, int64_t l
                          "with a caller-owned workspace", (long long)M);
     if (!x || !w_nk || !w_scale || !y || (scheme == FP8LIN_W8A8_STATIC && !input_scale))
         return set_error(FP8LIN_ERR_NULL, "x, w_nk, w_scale, y (and input_scale for W8A8) must not be NULL");
-    if (ldx < K || ldy < N || ldx % 8 != 0)
-        return set_error(FP8LIN_ERR_SHAPE, "ldx=%lld / ldy=%lld do not fit K / N (ldx must be a multiple of 8)",
-                         (long long)ldx, (long long)ldy);
+    if (ldx < K || ldy < N)
+        return set_error(FP8LIN_ERR_SHAPE, "ldx=%lld < K or ldy=%lld < N", (long long)ldx, (long long)ldy);
+    if (ldx % 8 != 0) return set_error(FP8LIN_ERR_ALIGN, "ldx=%lld must be a multiple of 8 elements", (long long)ldx);
     auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (!a16(x) || !a16(w_nk) || !a16(w_scale) || (bias && !a16(bias)))
         return set_error(FP8LIN_ERR_ALIGN, "x, w_nk, w_scale and bias must be 16-byte aligned");
+    if (!device_is_sm100()) return set_error(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
 
     const StreamPlan pl = plan_stream(scheme, M, K, N, -1);
     if (pl.partial_bytes > kStaticBodyBytes)
@@ -85,6 +91,12 @@ extern "C" int fp8lin_linear_static_scratch(int scheme, const void* x, int64_t l
 
     unsigned char* scratch = nullptr;
     cudaError_t e = static_scratch_for_current_device(&scratch);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return set_error(FP8LIN_ERR_WORKSPACE,
+                         "no device memory left for the built-in %zu-byte scratch array: make the first call on each "
+                         "GPU before the process gives the remaining HBM away", kStaticBytes);
+    }
     if (e != cudaSuccess) return set_error(FP8LIN_ERR_LAUNCH, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
     cudaStream_t st = (cudaStream_t)stream;
     WsView ws = ws_view(scratch, kStaticBytes);

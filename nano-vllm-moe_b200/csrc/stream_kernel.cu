@@ -294,7 +294,7 @@ static cudaError_t launch_one(const StreamArgs& a, dim3 grid, cudaStream_t strea
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = pdl_attribute(attr);
     cfg.attrs = attr;
-    return cudaLaunchKernelEx(&cfg, kern, a);
+    return counted(cudaLaunchKernelEx(&cfg, kern, a));
 }
 
 StreamPlan plan_stream(int scheme, int64_t M, int64_t K, int64_t N, int force_splits) {

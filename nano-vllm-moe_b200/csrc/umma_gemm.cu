@@ -693,7 +693,7 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s);
+    return counted(cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s));
 }
 
 static cudaError_t launch_umma(bool f16, const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why,

@@ -275,7 +275,7 @@ static cudaError_t launch_grouped(const GroupedArgs& a, const CUtensorMap& tw, c
     cudaLaunchAttribute attr[1];
     cfg.numAttrs = pdl_attribute(attr);
     cfg.attrs = attr;
-    return cudaLaunchKernelEx(&cfg, kern, tw, tx, a);
+    return counted(cudaLaunchKernelEx(&cfg, kern, tw, tx, a));
 }
 
 int grouped_chunk_rows(int64_t rows, int num_experts) {

@@ -374,7 +374,7 @@ cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensor
     ++na;
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s, h_scale);
+    return counted(cudaLaunchKernelEx(&cfg, kern, ta, tb, ty, a, s, h_scale));
 }
 
 }  // namespace

@@ -432,7 +432,7 @@ static cudaError_t launch_swap(const SwapPlan& pl, const UmmaArgs& a, const CUte
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s);
+    return counted(cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s));
 }
 
 cudaError_t launch_swap_w8a8(const SwapPlan& pl, const UmmaArgs& a, const void* x, int64_t ldx, cudaStream_t stream,

@@ -428,7 +428,7 @@ static cudaError_t launch_swap16(const SwapPlan& pl, const UmmaArgs& a, const CU
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s);
+    return counted(cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s));
 }
 
 cudaError_t launch_swap_w8a16(const SwapPlan& pl, const UmmaArgs& a, const void* x, int64_t ldx, cudaStream_t stream,

@@ -17,6 +17,7 @@ import torch
 from .. import _lib
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_retired: list[torch.Tensor] = []       # outgrown scratch buffers, kept alive (see workspace())
 
 
 def _require_cuda(*tensors: torch.Tensor) -> None:
@@ -32,26 +33,53 @@ def _stream_ptr(device: torch.device) -> int:
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """Zero-initialised scratch for the current stream of ``device``, grown on demand.
 
-    One buffer per (device, stream): calls on different streams never share
-    scratch.  Growing allocates, so warm a shape up once before capturing it
-    in a CUDA graph (or call ``reserve_workspace``)."""
+    One buffer per (device, stream): calls on different streams never share scratch.
+    A buffer that is outgrown is retired, not freed: a CUDA graph captured earlier has its
+    address (split-K counters, partial sums, quantised activations) baked in, and its replays
+    must keep writing into memory nobody else owns.  ``release_workspaces()`` frees everything
+    once no such graph is left.
+
+    Growing allocates and zero-fills, which must not happen inside a stream capture: warm every
+    shape up once (or call ``reserve_workspace`` with the largest size) ON THE STREAM THAT WILL
+    CAPTURE, before the capture starts.  ``torch.cuda.graph`` captures on a side stream, so the
+    warm-up belongs inside ``with torch.cuda.stream(side):`` too.  Graphs captured on the same
+    stream share one scratch buffer; replay them on one stream at a time."""
     key = (device.index if device.index is not None else torch.cuda.current_device(), _stream_ptr(device))
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                f"fp8lin scratch for this stream must grow to {nbytes} bytes during a CUDA graph capture; "
+                "run the shape once (or call reserve_workspace) on the capturing stream before the capture")
         size = max(nbytes, _lib.WS_HEADER_BYTES)
         if ws is not None:
             size = max(size, 2 * ws.numel())
+            _retired.append(ws)
         ws = torch.zeros(size, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
 
 def reserve_workspace(device: torch.device, nbytes: int) -> None:
+    """Make the current stream's scratch at least ``nbytes`` large (see ``workspace``)."""
     workspace(device, nbytes)
+
+
+def release_workspaces() -> None:
+    """Free every scratch buffer, retired ones included.  Only when no kernel of this library is
+    in flight and no CUDA graph that captured one of its calls will be replayed again."""
+    torch.cuda.synchronize()
+    _workspaces.clear()
+    _retired.clear()
 
 
 def workspace_bytes(scheme: int, m: int, k: int, n: int) -> int:
     return int(_lib.load().fp8lin_workspace_bytes(scheme, m, k, n))
+
+
+def launch_count() -> int:
+    """Kernel launches the library has made so far in this process (difference it around a call)."""
+    return int(_lib.load().fp8lin_launch_count())
 
 
 def variant_name(scheme: int, m: int, k: int, n: int) -> str:

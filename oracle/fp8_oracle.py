@@ -23,6 +23,8 @@ Reference locations restated here (paths inside the reference project):
                               scripts/quantization/fp8_linear_microbench.py:67,77,
                               scripts/debug/debug_ptx_mma.py:75-88
 * row-parallel reduction      nanovllm/layers/linear.py:258-262
+* SiluAndMul                  nanovllm/layers/activation.py:6-14
+* RMSNorm                     nanovllm/layers/layernorm.py:17-41
 * router                      nanovllm/executor/moe/router.py:24-34
 * expert FFN                  nanovllm/executor/moe/experts/eager_experts.py:26-35
 * top-k combine               nanovllm/executor/moe/prepare_finalize/no_ep.py:45
@@ -290,12 +292,47 @@ def softmax_topk(router_logits, top_k, renormalize=False):
 
 def silu_mul(gate_up: np.ndarray) -> np.ndarray:
     """bf16(silu(gate) * up) with gate/up the two halves of the last axis,
-    evaluated in fp32 from bf16-valued inputs."""
+    evaluated in fp32 from bf16-valued inputs, ONE rounding: what the reference's
+    ``SiluAndMul.forward`` computes as it is decorated (``@torch.compile`` fuses the two
+    ops into one fp32 expression; nanovllm/layers/activation.py:11-14).  Pinned by
+    ``activation.npz['compiled']``."""
     half = gate_up.shape[-1] // 2
     g = gate_up[..., :half].astype(np.float32)
     u = gate_up[..., half:].astype(np.float32)
     s = (g / (np.float32(1.0) + np.exp(-g).astype(np.float32))).astype(np.float32)
     return bf16_round((s * u).astype(np.float32))
+
+
+def rmsnorm(x, weight, eps, residual=None, compiled=True):
+    """RMSNorm.rms_forward / add_rms_forward (nanovllm/layers/layernorm.py:17-41) on bf16-valued
+    float32 inputs, bf16 weight.  fp32: v = x [+ residual]; var = mean(v^2); n = v * rsqrt(var + eps).
+
+    compiled=True (the form the reference runs: both methods are ``@torch.compile``d, and the
+    compiler keeps the fused expression in fp32, dropping the intermediate ``.to(bf16)``):
+    out = bf16(n * weight), one rounding.  compiled=False (the same Python run eagerly):
+    out = bf16(bf16(n) * weight).  With a residual the second result is bf16(x + residual),
+    the stream the next layer adds to; the normalisation uses the unrounded fp32 sum.
+    Both forms are pinned by ``rmsnorm.npz``."""
+    v = np.asarray(x, np.float32)
+    new_res = None
+    if residual is not None:
+        v = (v + np.asarray(residual, np.float32)).astype(np.float32)
+        new_res = bf16_round(v)
+    var = (v.astype(np.float32) ** 2).mean(axis=-1, keepdims=True, dtype=np.float32)
+    inv = (np.float32(1.0) / np.sqrt(var + np.float32(eps), dtype=np.float32)).astype(np.float32)
+    normed = (v * inv).astype(np.float32)
+    if not compiled:
+        normed = bf16_round(normed)
+    out = bf16_round((normed * np.asarray(weight, np.float32)[None, :]).astype(np.float32))
+    return out if residual is None else (out, new_res)
+
+
+def rmsnorm_quant(x, weight, eps, input_scale, residual=None):
+    """RMSNorm feeding a W8A8-static linear: the norm's bf16 output quantised with the linear's static
+    activation scale (layernorm.py:17-41 followed by kernels/fp8.py:250-252).  Returns (codes, new residual)."""
+    r = rmsnorm(x, weight, eps, residual)
+    out, new_res = (r, None) if residual is None else r
+    return quantize_activation(out, input_scale), new_res
 
 
 def mlp_w8a8(x, gu_q, gu_scale, gu_in_scale, gu_bias, down_q, down_scale, down_in_scale, down_bias):
@@ -319,7 +356,7 @@ def moe_experts_w8a8(x, topk_ids, topk_weights, w13_q, w13_scale, w13_in_scale,
 
     x [T,H]; topk_ids/topk_weights [T,k]; w13_q [E,2I,H] codes, w13_scale [E,2I];
     w2_q [E,H,I] codes, w2_scale [E,H]; in-scales scalars (one per layer).
-    Per routed row: gu = bf16(W8A8 linear); h = bf16(silu(g)*u);
+    Per routed row: gu = bf16(W8A8 linear); h = bf16(bf16(silu(g))*u) (eager, two roundings);
     o = (W8A8 linear)(h) * weight in fp32, rounded to bf16 once; the k routed
     rows of a token are then summed in fp32 in slot order and rounded to bf16.
     PARITY UNPINNED by the reference for the FP8 operands (its experts are
@@ -335,7 +372,7 @@ def moe_experts_w8a8(x, topk_ids, topk_weights, w13_q, w13_scale, w13_in_scale,
         if tok.size == 0:
             continue
         gu = linear_w8a8(x[tok], w13_q[e], w13_scale[e], w13_in_scale)
-        hmid = silu_mul(gu)
+        hmid = silu_mul_unfused(gu)
         o = linear_w8a8(hmid, w2_q[e], w2_scale[e], w2_in_scale, round_out=False)
         routed[tok, slot] = bf16_round(o * topk_weights[tok, slot][:, None].astype(np.float32))
     return bf16_round(routed.sum(axis=1, dtype=np.float32))
@@ -359,7 +396,9 @@ def moe_experts_dense(x, topk_ids, topk_weights, w13, w2):
 
 
 def silu_mul_unfused(gate_up):
-    """torch eager in bf16: bf16(silu(gate)) then bf16(. * up)."""
+    """torch eager in bf16: bf16(silu(gate)) then bf16(. * up) -- the expert FFN's form
+    (``F.silu(gate) * up`` outside any compiled region, experts/eager_experts.py:33).
+    Pinned by ``activation.npz['eager']`` and through ``moe.npz['moe_out']``."""
     half = gate_up.shape[-1] // 2
     g = gate_up[..., :half].astype(np.float32)
     u = gate_up[..., half:].astype(np.float32)

@@ -24,6 +24,17 @@ What is recorded, and which reference code produced it:
   moe.npz           executor/moe/router.py SoftmaxTopKRouter, experts/eager_experts.py
                     EagerExperts, prepare_finalize/no_ep.py NoEPPrepareFinalize,
                     utils/moe.py moe_align_block_size
+  activation.npz    nanovllm/layers/activation.py SiluAndMul.forward, run twice: as plain eager torch
+                    (two bf16 roundings: silu, then the product) and through torch.compile as the
+                    reference decorates it (one fused fp32 expression, one rounding)
+  rmsnorm.npz       nanovllm/layers/layernorm.py RMSNorm.rms_forward / add_rms_forward with bf16
+                    weights (the reference builds its models under a bf16 default dtype), eager
+                    and compiled
+
+Optional further arguments name the generators to run (codec act_quant weight_quant loaders
+linear moe checkpoint activation rmsnorm); without them all run.  The two compiled fixtures need
+a host C++ compiler that inductor can use with OpenMP (``CXX=/usr/bin/g++`` in the build
+container, whose default g++ wrapper lacks libgomp.spec).
 """
 from __future__ import annotations
 
@@ -36,6 +47,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
 REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NANOVLLM_REFERENCE", ""))
+ONLY = set(sys.argv[2:])
 if not (REF / "nanovllm").is_dir():
     raise SystemExit("usage: make_golden.py <reference checkout>")
 sys.path.insert(0, str(REF))
@@ -246,6 +258,55 @@ def gen_moe():
     np.savez_compressed(HERE / "moe.npz", **out)
 
 
+def _eager_and_compiled(fn):
+    """Run ``fn`` (a call into a torch.compile-decorated reference method) without and with compilation."""
+    import torch._inductor.config as inductor_config
+    cxx = os.environ.get("CXX")
+    if cxx:
+        inductor_config.cpp.cxx = (cxx,)
+    with torch.compiler.set_stance("force_eager"):
+        eager = fn()
+    return eager, fn()
+
+
+def gen_activation():
+    from nanovllm.layers.activation import SiluAndMul
+    rng = np.random.default_rng(21)
+    parts = [rng.standard_normal((96, 512)).astype(np.float32) * s for s in (0.1, 1.0, 4.0)]
+    edge = np.zeros((8, 512), np.float32)
+    edge[:, :256] = np.linspace(-30.0, 30.0, 8 * 256, dtype=np.float32).reshape(8, 256)     # gate sweep
+    edge[:, 256:] = rng.standard_normal((8, 256)).astype(np.float32) * 3.0
+    x = O.bf16_round(np.concatenate(parts + [edge]))
+    act = SiluAndMul()
+    eager, compiled = _eager_and_compiled(lambda: act(bf16_t(x)))
+    np.savez_compressed(HERE / "activation.npz", x=x, eager=f32(eager), compiled=f32(compiled))
+
+
+def gen_rmsnorm():
+    from nanovllm.layers.layernorm import RMSNorm
+    rng = np.random.default_rng(22)
+    out = {}
+    for tag, (rows, hidden, eps) in {"a": (24, 256, 1e-6), "b": (7, 3584, 1e-6), "c": (5, 64, 1e-5)}.items():
+        x = O.bf16_round(rng.standard_normal((rows, hidden)).astype(np.float32) * 2.0)
+        res = O.bf16_round(rng.standard_normal((rows, hidden)).astype(np.float32))
+        w = O.bf16_round(1.0 + 0.25 * rng.standard_normal(hidden).astype(np.float32))
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(torch.bfloat16)        # as the reference's model runner does before it builds the model
+        try:
+            norm = RMSNorm(hidden, eps)
+        finally:
+            torch.set_default_dtype(prev)
+        assert norm.weight.dtype == torch.bfloat16
+        norm.weight.data.copy_(bf16_t(w))
+        e1, c1 = _eager_and_compiled(lambda: norm(bf16_t(x)))
+        e2, c2 = _eager_and_compiled(lambda: norm(bf16_t(x), bf16_t(res)))
+        out.update({f"{tag}_x": x, f"{tag}_residual": res, f"{tag}_weight": w, f"{tag}_eps": np.float32(eps),
+                    f"{tag}_eager": f32(e1), f"{tag}_compiled": f32(c1),
+                    f"{tag}_add_eager": f32(e2[0]), f"{tag}_add_compiled": f32(c2[0]),
+                    f"{tag}_add_residual_eager": f32(e2[1]), f"{tag}_add_residual_compiled": f32(c2[1])})
+    np.savez_compressed(HERE / "rmsnorm.npz", **out)
+
+
 def _tiny_block(layers_mod, cfg, nn):
     """model.layers.0.{self_attn.{qkv_proj,o_proj}, mlp.{gate_up_proj,down_proj}} + model.norm, the
     fused-module naming of the reference's Qwen2 (models/qwen2.py:193-199)."""
@@ -355,6 +416,10 @@ def gen_checkpoint():
 if __name__ == "__main__":
     torch.manual_seed(0)
     torch.set_num_threads(1)
-    gen_codec(); gen_act_quant(); gen_weight_quant(); gen_loaders(); gen_linear(); gen_moe(); gen_checkpoint()
+    for name, gen in (("codec", gen_codec), ("act_quant", gen_act_quant), ("weight_quant", gen_weight_quant),
+                      ("loaders", gen_loaders), ("linear", gen_linear), ("moe", gen_moe), ("checkpoint", gen_checkpoint),
+                      ("activation", gen_activation), ("rmsnorm", gen_rmsnorm)):
+        if not ONLY or name in ONLY:
+            gen()
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)

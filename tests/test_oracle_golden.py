@@ -118,3 +118,52 @@ def test_row_parallel_sums_to_full():
         assert ok, (tp, worst)
     ycol = O.column_parallel(c["x"], c["wq"], c["w_scale"], c["input_scale"], c["bias"], 4, "fp8_w8a8_static")
     np.testing.assert_array_equal(ycol, full)
+
+
+def test_silu_and_mul_both_forms_match_reference(golden):
+    """The activation as the reference runs it (compiled: one rounding) and as the same Python runs
+    eagerly (two roundings) -- the dense MLP uses the first, the expert FFN the second."""
+    g = golden("activation")
+    fused, eager = O.silu_mul(g["x"]), O.silu_mul_unfused(g["x"])
+    # exp() differs in the last fp32 bit between libraries: at most a handful of bf16 results move by one ulp
+    for got, want in ((fused, g["compiled"]), (eager, g["eager"])):
+        diff = O.bf16_bits(got) != O.bf16_bits(want)
+        assert diff.mean() < 1e-3 and _bf16_ulps(got, want).max() <= 1
+    # the two forms are really different functions on these inputs, so the fixture tells them apart
+    assert (O.bf16_bits(fused) != O.bf16_bits(g["eager"])).mean() > 0.1
+    assert (O.bf16_bits(eager) != O.bf16_bits(g["compiled"])).mean() > 0.1
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_rmsnorm_matches_reference(golden, tag):
+    g = golden("rmsnorm")
+    x, res, w, eps = g[f"{tag}_x"], g[f"{tag}_residual"], g[f"{tag}_weight"], g[f"{tag}_eps"]
+    for compiled, key in ((True, "compiled"), (False, "eager")):
+        y = O.rmsnorm(x, w, eps, compiled=compiled)
+        y2, r2 = O.rmsnorm(x, w, eps, res, compiled=compiled)
+        # the fp32 mean of squares is summed in another order here: at most one bf16 ulp, almost never
+        for got, want in ((y, g[f"{tag}_{key}"]), (y2, g[f"{tag}_add_{key}"])):
+            assert (O.bf16_bits(got) != O.bf16_bits(want)).mean() < 1e-3 and _bf16_ulps(got, want).max() <= 1
+        np.testing.assert_array_equal(r2, g[f"{tag}_add_residual_{key}"])
+    assert (O.bf16_bits(O.rmsnorm(x, w, eps)) != O.bf16_bits(g[f"{tag}_eager"])).mean() > 0.05
+
+
+def test_moe_row_grouping_matches_reference_alignment(golden):
+    """moe_align_block_size (nanovllm/utils/moe.py) on the fixture's routing: every block holds rows of one
+    expert only, each expert's rows appear exactly once, padding uses the sentinel T*k."""
+    g = golden("moe")
+    ids = g["topk_ids_ren0"].reshape(-1)
+    st, eids, nb = g["align_sorted_weight_idx"], g["align_expert_ids"], int(g["align_total_blocks"])
+    tok = g["align_sorted_token_ids"]
+    np.testing.assert_array_equal(tok[st < ids.size], st[st < ids.size] // 4)      # token of a routed row (k = 4)
+    block = 8
+    assert st.size >= nb * block
+    for b in range(nb):
+        rows = st[b * block:(b + 1) * block]
+        real = rows[rows < ids.size]
+        assert (ids[real] == eids[b]).all()
+    real = st[: nb * block]
+    real = real[real < ids.size]
+    np.testing.assert_array_equal(np.sort(real), np.arange(ids.size))
+    perm, counts, _ = O.ep_dispatch_plan(g["topk_ids_ren0"], 12, 1)
+    assert counts.sum() == ids.size
