@@ -245,6 +245,13 @@ int fp8lin_set_tuning(const char* knob, int value);
  * `stream`) and clears it.  0 = no kernel gave up a bounded wait. */
 int fp8lin_read_status(void* workspace, void* stream, int* status_out);
 
+/* Exercises the give-up path of the kernels' bounded waits without a fault (no counterpart in the
+ * reference, whose kernels have no such waits): launches one CTA that waits, with the same routine the
+ * tcgen05 kernels use but a limit of about `limit_us` microseconds (1..100000), on a barrier nothing
+ * arrives on.  The wait runs out, the kernel writes its code to the status word at the start of
+ * `workspace` and returns normally; the next fp8lin_read_status reports FP8LIN_ERR_DEVICE and clears it. */
+int fp8lin_debug_wait_timeout(void* workspace, int64_t limit_us, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,7 @@ SIGNATURES = {
                                              c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "fp8lin_quantize_activation": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "fp8lin_moe_route": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fp8lin_debug_wait_timeout": (c_int, [c_void_p, c_int64, c_void_p]),
     "fp8lin_moe_align": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "fp8lin_moe_workspace_bytes": (c_size_t, [c_int64, c_int, c_int64, c_int64]),
     "fp8lin_moe_experts_w8a8": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,

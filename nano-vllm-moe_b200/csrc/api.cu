@@ -35,6 +35,8 @@ struct Tuning {
     int w8a16_umma_min_m = -1;  // smallest M for the dequantise-to-f16 + tcgen05 GEMM route (0 = never)
     int w8a16_chunk_mb = -1;    // size of the f16 weight chunk that route keeps in L2
     int umma_pair = -1;         // 1 = large-M GEMMs on CTA pairs (256 x 256 tiles), 0 = never
+    int fuse_quant = -1;        // large-M W8A8: 0 = quantise x in a separate pass, never inside the GEMM;
+                                // n > 0 = the pass takes the first n rows (rounded up to 128), the GEMM the rest
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -106,8 +108,8 @@ F16Chunks plan_f16_chunks(int64_t M, int64_t K, int64_t N) {
     const double t_tile = (double)fp8lin::pack_kblocks(K) * 2 * 0.115;     // us per 128x256 tile (64-element K blocks)
     auto rounds_of = [&](int64_t blocks) -> double {
         const int64_t tiles = m_tiles * blocks;
-        if (tiles > 74) return (double)((tiles + 147) / 148);
-        int64_t splits = 148 / tiles;                                       // few tiles: cluster split-K
+        if (tiles > (sm_count() / 2)) return (double)((tiles + (sm_count() - 1)) / sm_count());
+        int64_t splits = sm_count() / tiles;                                       // few tiles: cluster split-K
         if (splits > 8) splits = 8;
         return 1.0 / (double)splits + 0.15;
     };
@@ -136,9 +138,9 @@ bool pair_eligible(int64_t M, int64_t N) {
     const int64_t nt = (N + 255) / 256;
     const int64_t pt = ((M + 255) / 256) * nt;
     const int64_t tiles = ((M + 127) / 128) * nt;
-    if (pt < 4 * 74) return false;
-    const double pair_fill = (double)pt / (double)(((pt + 73) / 74) * 74);
-    const double one_fill = (double)tiles / (double)(((tiles + 147) / 148) * 148);
+    if (pt < 4 * (sm_count() / 2)) return false;
+    const double pair_fill = (double)pt / (double)(((pt + (sm_count() / 2 - 1)) / (sm_count() / 2)) * (sm_count() / 2));
+    const double one_fill = (double)tiles / (double)(((tiles + (sm_count() - 1)) / sm_count()) * sm_count());
     return pair_fill >= 0.95 && pair_fill >= one_fill - 1e-9;
 }
 
@@ -160,6 +162,34 @@ bool swap_prequant(int64_t M) {
     return M >= min_m;
 }
 
+// Large-M W8A8 with the activation quantiser inside the GEMM: a short pass quantises the rows that the first
+// round of tiles reads (tiles are walked in groups of eight tile rows), the kernel's quantiser warps do the
+// rest while the tensor cores run.  Returns the number of rows for the pass; M = everything (no fusion).
+int64_t prequant_rows(int64_t M, int64_t n_tiles, int tile_rows, int first_round_tiles) {
+    if (g_tune.fuse_quant == 0 || 2 + (M + 127) / 128 > kWsMaxCounters) return M;
+    if (g_tune.fuse_quant > 0) {                      // forced split (tests): this many rows, rounded up to a row block
+        const int64_t forced = ((int64_t)g_tune.fuse_quant + 127) / 128 * 128;
+        return forced >= M ? M : forced;
+    }
+    const int64_t m_tiles = (M + tile_rows - 1) / tile_rows;
+    const int64_t total = m_tiles * n_tiles;
+    const int64_t first = total < first_round_tiles ? total : first_round_tiles;
+    const int64_t groups = (first + 8 * n_tiles - 1) / (8 * n_tiles);
+    const int64_t rows = groups * 8 * tile_rows;
+    return rows >= M ? M : rows;
+}
+
+// Quantise rows [0, pre) in a pass of their own and hand the rest to the GEMM's quantiser warps.
+int start_quant(const void* x, int64_t ldx, const float* input_scale, unsigned char* xq, int64_t M, int64_t K, int64_t pre,
+                const WsView& ws, UmmaArgs& a, cudaStream_t st) {
+    cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, xq, pre, K, st);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
+    if (pre < M) {
+        a.x = (const __nv_bfloat16*)x; a.ldx = (int)ldx; a.q_row_start = (int)pre; a.q_ctrl = ws.counters;
+    }
+    return FP8LIN_OK;
+}
+
 bool umma_eligible(int64_t M, int64_t N, int64_t ldy, const void* y) {
     const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
     return M > max_m && N % 8 == 0 && ldy % 8 == 0 && aligned16(y);
@@ -171,6 +201,16 @@ namespace fp8lin {
 static std::atomic<unsigned long long> g_launches{0};
 void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 bool device_is_sm100() { return check_arch() != 0; }
+int sm_count() {
+    static int cached = 0;
+    if (cached > 0) return cached;
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+        return cached = n;
+    cudaGetLastError();
+    return 148;              // no device to ask (host-side planning only): not cached, a later call may have one
+}
 static int g_pdl = 1;
 void set_pdl_enabled(int on) { g_pdl = on; }
 int pdl_attribute(cudaLaunchAttribute* attr) {
@@ -343,15 +383,18 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
         return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes",
                     FP8LIN_WS_HEADER_BYTES + xq_bytes + pl.partial_bytes);
     unsigned char* xq = ws.body;
-    cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, xq, M, K, st);
-    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
     UmmaArgs a;
     a.xq = xq; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
     a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y;
     a.partial = (float*)(ws.body + xq_bytes); a.counters = ws.counters; a.status = ws.status;
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ldy;
+    const bool pair = pair_eligible(M, N);
+    const int64_t pre = pair ? prequant_rows(M, (N + 255) / 256, 256, sm_count() / 2)
+                             : (pl.splits > 1 ? M : prequant_rows(M, pl.n_tiles, 128, sm_count()));
+    rc = start_quant(x, ldx, input_scale, xq, M, K, pre, ws, a, st);
+    if (rc != FP8LIN_OK) return rc;
     const char* why = nullptr;
-    e = pair_eligible(M, N) ? launch_umma_pair(false, a, st, &why) : launch_umma_w8a8(pl, a, st, &why);
+    cudaError_t e = pair ? launch_umma_pair(false, a, st, &why) : launch_umma_w8a8(pl, a, st, &why);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     return FP8LIN_OK;
 }
@@ -373,14 +416,14 @@ int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const floa
     const size_t xq_bytes = align_up((size_t)M * K, 256);
     if (!workspace || ws.body_bytes < xq_bytes)
         return fail(FP8LIN_ERR_WORKSPACE, "workspace too small: need %zu bytes", FP8LIN_WS_HEADER_BYTES + xq_bytes);
-    cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, ws.body, M, K, st);
-    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
     UmmaArgs a;
     a.xq = ws.body; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
     a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)dst_ptrs[0]; a.partial = nullptr; a.counters = ws.counters;
     a.status = ws.status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ld_dst;
+    rc = start_quant(x, ldx, input_scale, ws.body, M, K, prequant_rows(M, pl.n_tiles, 128, sm_count()), ws, a, st);
+    if (rc != FP8LIN_OK) return rc;
     const char* why = nullptr;
-    e = launch_umma_w8a8(pl, a, st, &why, n_dst, dst_ptrs, ld_dst);
+    cudaError_t e = launch_umma_w8a8(pl, a, st, &why, n_dst, dst_ptrs, ld_dst);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     return FP8LIN_OK;
 }
@@ -464,14 +507,14 @@ int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const flo
         if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "silu-multiply pass launch: %s", cudaGetErrorString(e));
     } else {
         unsigned char* xq = ws.body;
-        cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, gate_up_input_scale, xq, M, H, st);
-        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
         UmmaArgs a;
         a.xq = xq; a.w = (const unsigned char*)w_gate_up; a.w_scale = gate_up_scale; a.input_scale = gate_up_input_scale;
         a.bias = (const __nv_bfloat16*)gate_up_bias; a.y = nullptr; a.partial = nullptr; a.counters = ws.counters;
         a.status = ws.status; a.M = (int)M; a.K = (int)H; a.N = (int)(2 * I); a.ldy = 0;
+        rc = start_quant(x, ldx, gate_up_input_scale, xq, M, H, prequant_rows(M, (2 * I + 255) / 256, 256, sm_count() / 2), ws, a, st);
+        if (rc != FP8LIN_OK) return rc;
         const char* why = nullptr;
-        e = launch_umma_pair_mlp(a, hq, down_input_scale, st, &why);
+        cudaError_t e = launch_umma_pair_mlp(a, hq, down_input_scale, st, &why);
         if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "fused gate_up launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     }
     return run_w8a8_prequantised(hq, w_down, down_scale, down_input_scale, down_bias, y, ldy, M, I, N, ws, st);
@@ -573,6 +616,7 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "w8a16_umma_min_m")) g_tune.w8a16_umma_min_m = value;
     else if (!strcmp(knob, "w8a16_chunk_mb")) g_tune.w8a16_chunk_mb = value;
     else if (!strcmp(knob, "umma_pair")) g_tune.umma_pair = value;
+    else if (!strcmp(knob, "fuse_quant")) g_tune.fuse_quant = value;
     else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;
@@ -696,6 +740,16 @@ int fp8lin_moe_combine(const void* routed, void* y, int64_t T, int top_k, int64_
     if (!aligned16(routed) || !aligned16(y)) return fail(FP8LIN_ERR_ALIGN, "routed and y must be 16-byte aligned");
     cudaError_t e = launch_moe_combine((const __nv_bfloat16*)routed, (__nv_bfloat16*)y, (int)T, top_k, (int)H, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "combine launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+int fp8lin_debug_wait_timeout(void* workspace, int64_t limit_us, void* stream) {
+    if (!workspace) return fail(FP8LIN_ERR_NULL, "workspace must not be NULL");
+    if (limit_us < 1 || limit_us > 100000) return fail(FP8LIN_ERR_ARG, "limit_us must be 1..100000");
+    if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
+    // clock64 ticks at the SM clock: at most ~2 GHz, so 2000 cycles per microsecond is an upper bound
+    cudaError_t e = launch_wait_timeout_probe((int*)workspace, (long long)limit_us * 2000, nullptr, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "probe launch: %s", cudaGetErrorString(e));
     return FP8LIN_OK;
 }
 

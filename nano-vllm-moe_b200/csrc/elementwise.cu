@@ -33,7 +33,7 @@ cudaError_t launch_act_quant(const __nv_bfloat16* x, int64_t ldx, const float* i
     const int64_t total = M * (K / 16);
     if (total == 0) return cudaSuccess;
     int64_t blocks = (total + 255) / 256;
-    const int64_t cap = 148 * 16;
+    const int64_t cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)blocks);
@@ -76,7 +76,7 @@ cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t sl
     const int64_t total = M * (N / 8);
     if (total == 0) return cudaSuccess;
     int64_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
     sum_slots_kernel<<<(unsigned)blocks, 256, 0, stream>>>(slots, n_slots, slot_stride, y, ldy, M, N, ld_slot);
     return counted(cudaGetLastError());
 }
@@ -101,7 +101,7 @@ cudaError_t launch_x_to_f16(const __nv_bfloat16* x, int64_t ldx, void* x16, int6
     const int64_t total = M * (K / 8);
     if (total == 0) return cudaSuccess;
     int64_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)blocks);
     cfg.blockDim = dim3(256);
@@ -143,7 +143,7 @@ cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_
     const int64_t total = src_bytes / 16;
     if (total == 0) return cudaSuccess;
     int64_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)blocks);
     cfg.blockDim = dim3(256);
@@ -189,7 +189,7 @@ cudaError_t launch_silu_mul_quant_interleaved(const __nv_bfloat16* gu, const flo
     const int64_t total = M * (I / 8);
     if (total == 0) return cudaSuccess;
     int64_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)blocks);
     cfg.blockDim = dim3(256);
@@ -278,7 +278,7 @@ cudaError_t launch_abs_max(const __nv_bfloat16* x, int64_t ldx, int64_t M, int64
     const int64_t total = M * (K / 8);
     if (total == 0) return cudaSuccess;
     int64_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     abs_max_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, M, K, amax);
     return counted(cudaGetLastError());
 }

@@ -14,6 +14,9 @@ int set_error(int code, const char* fmt, ...);
 
 // Fills the attribute that makes a launch a programmatic dependent of the previous kernel in
 // its stream; returns the number of attributes written (0 when disabled by the tuning knob).
+// Streaming multiprocessors of the current device (cached per process; 148, a B200's, when no device can be
+// asked).  Grid sizes and the tile-round arithmetic of the launch plans are derived from it.
+int sm_count();
 // Whether the current device is an sm_100 part (cached per process; defined in api.cu).
 bool device_is_sm100();
 int pdl_attribute(cudaLaunchAttribute* attr);
@@ -77,6 +80,13 @@ struct UmmaArgs {
     int* status;                 // device status word
     int M, K, N;
     int ldy;
+    // Activation quantisation inside the kernel (large-M W8A8, e4m3 operands only): when x is not NULL the
+    // kernel's quantiser warps write rows [q_row_start, M) of xq from x while the GEMM runs; rows below
+    // q_row_start (a multiple of 128) must already be in xq.  q_ctrl: 2 + ceil(M / 128) zeroed ints of scratch.
+    const __nv_bfloat16* x = nullptr;
+    int ldx = 0;
+    int q_row_start = 0;
+    int* q_ctrl = nullptr;
 };
 
 struct UmmaPlan {
@@ -114,6 +124,10 @@ cudaError_t launch_silu_mul_quant_interleaved(const __nv_bfloat16* gu, const flo
                                               int64_t I, cudaStream_t stream);
 cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t slot_stride, __nv_bfloat16* y, int64_t ldy,
                              int64_t M, int64_t N, int64_t ld_slot, cudaStream_t stream);
+
+// A one-CTA launch whose only mbarrier is never arrived on: the bounded wait gives up after
+// `limit_cycles`, writes kDevTimeoutFull to *status (and 1 to *gave_up if given) and returns.
+cudaError_t launch_wait_timeout_probe(int* status, long long limit_cycles, int* gave_up, cudaStream_t stream);
 
 // ---- swapped-operand tcgen05 kernel for M <= 64 (umma_swap.cu) -------------------
 struct SwapPlan {

@@ -164,7 +164,7 @@ moe_gather_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int x_
 cudaError_t launch_moe_gather_quant(const __nv_bfloat16* x, int64_t ldx, int x_div, const int* sorted_rows, const int* meta,
                                     const float* input_scale, unsigned char* xq, int max_rows, int H, cudaStream_t stream) {
     int64_t blocks = ((int64_t)max_rows * (H / 16) + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     if (blocks < 1) blocks = 1;
     moe_gather_quant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, x_div, sorted_rows, meta, input_scale, xq, H);
     return counted(cudaGetLastError());
@@ -204,7 +204,7 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restr
 cudaError_t launch_silu_mul_quant(const __nv_bfloat16* gu, const float* input_scale, unsigned char* hq, const int* meta,
                                   int max_rows, int I, cudaStream_t stream) {
     int64_t blocks = ((int64_t)max_rows * (I / 8) + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     if (blocks < 1) blocks = 1;
     silu_mul_quant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(gu, input_scale, hq, meta, I);
     return counted(cudaGetLastError());
@@ -238,7 +238,7 @@ cudaError_t launch_moe_combine(const __nv_bfloat16* routed, __nv_bfloat16* y, in
                                cudaStream_t stream) {
     if (T == 0) return cudaSuccess;
     int64_t blocks = ((int64_t)T * (H / 8) + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     moe_combine_kernel<<<(unsigned)blocks, 256, 0, stream>>>(routed, y, T, top_k, H);
     return counted(cudaGetLastError());
 }

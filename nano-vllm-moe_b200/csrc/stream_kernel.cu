@@ -307,7 +307,7 @@ StreamPlan plan_stream(int scheme, int64_t M, int64_t K, int64_t N, int force_sp
     pl.n_tiles = (int)((N + bn - 1) / bn);
     const int chunks = (int)((K + kChunk - 1) / kChunk);
     // aim for about four resident CTAs per SM (two for the wide-M variants)
-    const int target = 148 * (pl.mt >= 4 ? 2 : 4);
+    const int target = sm_count() * (pl.mt >= 4 ? 2 : 4);
     const int tiles = pl.n_tiles * pl.m_passes;
     int splits = force_splits > 0 ? force_splits : (target + tiles / 2) / tiles;
     if (splits < 1) splits = 1;

@@ -22,8 +22,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
-// Bounded wait; false = gave up (status word written).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+// Bounded wait; false = gave up after `limit` clock cycles (status word written).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code,
+                                          long long limit = kWaitCycles) {
     long long start = -1;
     for (uint32_t it = 0;; ++it) {
         uint32_t done;
@@ -34,7 +35,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
         if ((it & 0x3ff) == 0x3ff) {
             const long long now = clock64();
             if (start < 0) start = now;
-            else if (now - start > kWaitCycles) { atomicExch(status, code); return false; }
+            else if (now - start > limit) { atomicExch(status, code); return false; }
         }
     }
 }
@@ -200,6 +201,117 @@ bool encode_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
 // box's row length (128 or 64 bytes).
 bool encode_out_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
                    uint32_t box_cols);
+
+// ---- activation quantisation inside the large-M GEMM ------------------------------------------------
+// The GEMM kernels that take bf16 activations carry kQuantWarps extra warps.  Those warps turn rows
+// [row_start, M) of x into e4m3 rows of the scratch matrix xq that the kernel's own TMA producer loads as
+// the "A" operand, while the tensor cores work on rows quantised earlier (rows below row_start are
+// quantised by a short pass in front of the kernel, so the first round of tiles does not wait).
+//
+// The work is handed out in units of kQuantRows rows through a ticket counter in global scratch: a warp
+// takes the next ticket, converts its rows, and adds one to the "done" counter of the 128-row block the
+// rows belong to.  A TMA producer that needs a row block waits (bounded) until that block's counter has
+// reached its number of units.  Tickets are only ever taken by warps that are already running, and a warp
+// holding a ticket waits for nothing, so the scheme makes progress however many of the grid's CTAs are
+// resident at a time.  The last CTA to leave zeroes the counters again (scratch counters are zero between
+// calls).  Layout of ctrl: [0] next ticket, [1] CTAs that have left, [2 + b] units done in row block b.
+constexpr int kQuantWarps = 4;
+constexpr int kQuantRows = 8;           // rows per unit; divides 128, so a unit lies inside one row block
+
+struct QuantJob {
+    const __nv_bfloat16* x;      // bf16 activations [M][ldx]; nullptr = nothing to do (xq arrives complete)
+    unsigned char* xq;           // e4m3 [M][K]
+    int* ctrl;
+    int ldx;
+    int row_start;               // multiple of 128
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// orders earlier generic-proxy accesses to global memory against later async-proxy (TMA) ones
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Units of the 128-row block `block` that the in-kernel quantiser produces.
+__device__ __forceinline__ int quant_units_in_block(const QuantJob& j, int M, int block) {
+    const int r0 = max(block * 128, j.row_start);
+    const int r1 = min(block * 128 + 128, M);
+    return r1 > r0 ? (r1 - r0 + kQuantRows - 1) / kQuantRows : 0;
+}
+
+// Producer side: wait until row block `block` of xq is complete.  false = gave up (status written).
+__device__ __forceinline__ bool quant_wait_block(const QuantJob& j, int M, int block, int* status) {
+    const int need = quant_units_in_block(j, M, block);
+    if (need == 0) return true;
+    const int* flag = j.ctrl + 2 + block;
+    long long start = -1;
+    for (uint32_t it = 0;; ++it) {
+        if (ld_acquire_gpu(flag) >= need) break;
+        if ((it & 0xff) == 0xff) {
+            const long long now = clock64();
+            if (start < 0) start = now;
+            else if (now - start > kWaitCycles) { atomicExch(status, (int)kDevTimeoutQuant); return false; }
+        }
+        __nanosleep(64);
+    }
+    fence_proxy_async_all();       // the rows were written with ordinary stores; the TMA unit reads them next
+    return true;
+}
+
+// One quantiser warp: take units until none are left.
+__device__ __forceinline__ void quant_worker(const QuantJob& j, const float* input_scale, int M, int K, int lane) {
+    const ExactDiv div(fmaxf(__ldg(input_scale), 1e-12f));
+    const int total_units = M > j.row_start ? (M - j.row_start + kQuantRows - 1) / kQuantRows : 0;
+    const int vec_per_row = K >> 4;
+    for (;;) {
+        int u = 0;
+        if (lane == 0) u = atomicAdd(j.ctrl, 1);
+        u = __shfl_sync(0xffffffffu, u, 0);
+        if (u >= total_units) break;
+        const int row0 = j.row_start + u * kQuantRows;
+        const int rows = min(kQuantRows, M - row0);
+        // two rows per step: four 16-byte loads in flight per lane
+        for (int r = 0; r < rows; r += 2) {
+            const bool two = r + 1 < rows;
+            const __nv_bfloat16* s0 = j.x + (size_t)(row0 + r) * j.ldx;
+            const __nv_bfloat16* s1 = s0 + (two ? j.ldx : 0);
+            unsigned char* d0 = j.xq + (size_t)(row0 + r) * K;
+            unsigned char* d1 = d0 + (two ? K : 0);
+            for (int v = lane; v < vec_per_row; v += 32) {
+                const uint4 a0 = ld_stream16(s0 + v * 16), a1 = ld_stream16(s0 + v * 16 + 8);
+                const uint4 b0 = ld_stream16(s1 + v * 16), b1 = ld_stream16(s1 + v * 16 + 8);
+                const uint2 qa0 = quant8_e4m3(a0, div), qa1 = quant8_e4m3(a1, div);
+                *reinterpret_cast<uint4*>(d0 + v * 16) = make_uint4(qa0.x, qa0.y, qa1.x, qa1.y);
+                if (two) {
+                    const uint2 qb0 = quant8_e4m3(b0, div), qb1 = quant8_e4m3(b1, div);
+                    *reinterpret_cast<uint4*>(d1 + v * 16) = make_uint4(qb0.x, qb0.y, qb1.x, qb1.y);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) {
+            fence_proxy_async_all();
+            __threadfence();
+            atomicAdd(j.ctrl + 2 + (row0 >> 7), 1);
+        }
+    }
+}
+
+// Every CTA calls this once all its warps are done with the counters (after its last __syncthreads):
+// the last one to arrive zeroes them for the next call.
+__device__ __forceinline__ void quant_ctrl_release(const QuantJob& j, int M) {
+    __threadfence();
+    const int left = atomicAdd(j.ctrl + 1, 1);
+    if (left == (int)gridDim.x - 1) {
+        const int blocks = (M + 127) >> 7;
+        for (int b = 0; b < blocks; ++b) j.ctrl[2 + b] = 0;
+        j.ctrl[0] = 0;
+        __threadfence();
+        j.ctrl[1] = 0;
+    }
+}
 
 // Destinations of a GEMM epilogue's TMA stores (all describe a bf16 [M][N] matrix of the same shape).
 struct OutMaps {

@@ -127,8 +127,10 @@ __device__ __forceinline__ WorkItem decode_work(const UmmaSched& s, int w) {
 // kF16 = true:  f16 x f16 (large-M W8A16; A = activations converted to f16, B = weight tiles widened to
 // f16 by dequant_tiles_f16_kernel into scratch).  A K block is 128 bytes of a row in both cases.
 // kNarrow (256-wide persistent launches only): the launch ends with half-width work items.
-template <int BN, bool kSplit, bool kF16 = false, bool kNarrow = false>
-__global__ void __launch_bounds__(kThreads, 1)
+// kFuseQ (persistent e4m3 launches only): kQuantWarps more warps quantise the bf16 activations into xq while
+// the GEMM runs (umma_common.cuh); the producer waits for a row block of xq before it loads from it.
+template <int BN, bool kSplit, bool kF16 = false, bool kNarrow = false, bool kFuseQ = false>
+__global__ void __launch_bounds__(kThreads + (kFuseQ ? kQuantWarps * 32 : 0), 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ OutMaps outs, UmmaArgs p, UmmaSched sched) {
     using Cfg = UmmaCfg<BN>;
@@ -168,8 +170,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     pdl_launch_dependents();
+    static_assert(!kFuseQ || (!kSplit && !kF16), "in-kernel quantisation: persistent e4m3 launches only");
+    QuantJob qjob;
+    qjob.x = p.x; qjob.xq = const_cast<unsigned char*>(p.xq); qjob.ctrl = p.q_ctrl; qjob.ldx = p.ldx; qjob.row_start = p.q_row_start;
 
-    if (warp == 0) {
+    if (kFuseQ && warp >= 2 + kEpiWarps) {
+        // ================= activation quantiser (warps 10..13) =================
+        pdl_wait();                    // x comes from the kernel before; xq may still be read by it
+        quant_worker(qjob, p.input_scale, p.M, p.K, lane);
+    } else if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
@@ -198,11 +207,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         }
                     }
                     pdl_wait();       // the quantised activations are written by the kernel before this one
+                    if (kFuseQ && !quant_wait_block(qjob, p.M, tm, p.status)) { s_abort = 1; ok = false; break; }
                     for (int i = 0; i < first_kb; ++i)
                         tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_a, (kb0 + i) * kBK, tm * kBM, smem_u32(&bar_full[i]));
                     waited = true;
                     it = (uint32_t)first_kb;
                     if (kb0 + first_kb >= kb1) continue;
+                } else if (kFuseQ) {
+                    if (s_abort || !quant_wait_block(qjob, p.M, tm, p.status)) { s_abort = 1; ok = false; break; }
                 }
                 for (int kb = kb0 + (w == first_work ? min(kb1 - kb0, S) : 0); kb < kb1; ++kb, ++it) {
                     const int st = it % S;
@@ -492,6 +504,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
+    if (kFuseQ && threadIdx.x == 0) quant_ctrl_release(qjob, p.M);
+}
+
+// ---- the give-up path of a bounded wait, exercised on its own ----------------------------------
+// One CTA initialises an mbarrier that nothing ever arrives on and waits for it with the routine every
+// tcgen05 kernel here uses, but with a limit of `limit_cycles` instead of about a second.  The wait runs
+// out, records kDevTimeoutFull in the status word and the kernel returns normally: the context stays
+// usable and the host sees the code through fp8lin_read_status.  Nothing faults, traps or spins on.
+__global__ void __launch_bounds__(32)
+wait_timeout_probe_kernel(int* status, long long limit_cycles, int* gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool arrived = mbar_wait(smem_u32(&bar), 0, status, kDevTimeoutFull, limit_cycles);
+        if (gave_up) *gave_up = arrived ? 0 : 1;
+    }
+}
+
+cudaError_t launch_wait_timeout_probe(int* status, long long limit_cycles, int* gave_up, cudaStream_t stream) {
+    wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(status, limit_cycles, gave_up);
+    return counted(cudaGetLastError());
 }
 
 // ---- host side -------------------------------------------------------------------
@@ -591,8 +625,8 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
         const long tiles = (long)m_tiles * n_tiles;
         int splits = 1;
         if (force_splits > 0) splits = force_splits;
-        else if (tiles <= 74) {
-            splits = (int)(148 / tiles);
+        else if (tiles <= (sm_count() / 2)) {
+            splits = (int)(sm_count() / tiles);
             const int max_by_k = kblocks / 4 > 0 ? kblocks / 4 : 1;  // at least four K blocks per slice
             if (splits > max_by_k) splits = max_by_k;
         }
@@ -602,7 +636,7 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
         int kps = (kblocks + splits - 1) / splits;
         splits = (kblocks + kps - 1) / kps;                           // no empty K slice
         const long work = tiles * splits;
-        long waves = (work + 147) / 148;
+        long waves = (work + (sm_count() - 1)) / sm_count();
         if (splits > 1) {
             const void* kern = bn == 256 ? (const void*)umma_gemm_kernel<256, true>
                              : bn == 128 ? (const void*)umma_gemm_kernel<128, true> : (const void*)umma_gemm_kernel<64, true>;
@@ -612,17 +646,17 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
             waves = (tiles + slots - 1) / slots;
         }
         double rounds = (double)waves;
-        if (splits == 1 && force_splits <= 0 && kblocks >= 64 && tiles > 148 && tiles % 148 != 0 && tiles % 148 <= 74)
-            rounds = (double)(tiles / 148) + 0.4;      // the last partial round goes to the split-K tail launch
-        else if (bn == 256 && splits == 1 && force_splits <= 0 && tiles > 148 && tiles % 148 != 0 && tiles % 148 <= 74)
-            rounds = (double)(tiles / 148) + 0.62;     // ... or runs as half-width work items
+        if (splits == 1 && force_splits <= 0 && kblocks >= 64 && tiles > sm_count() && tiles % sm_count() != 0 && tiles % sm_count() <= (sm_count() / 2))
+            rounds = (double)(tiles / sm_count()) + 0.4;      // the last partial round goes to the split-K tail launch
+        else if (bn == 256 && splits == 1 && force_splits <= 0 && tiles > sm_count() && tiles % sm_count() != 0 && tiles % sm_count() <= (sm_count() / 2))
+            rounds = (double)(tiles / sm_count()) + 0.62;     // ... or runs as half-width work items
         // main loop + fixed per-tile prologue/epilogue; split-K pays one cluster reduction
         const double cost = rounds * (kps * unit[i] + 3.0 * unit[i]) + (splits > 1 ? 2.0 : 0.0);
         if (cost < best_cost) {
             best_cost = cost;
             best.bn = bn; best.splits = splits; best.kblocks_per_split = kps;
             best.m_tiles = m_tiles; best.n_tiles = n_tiles;
-            best.grid = splits > 1 ? (int)work : (int)(work < 148 ? work : 148);
+            best.grid = splits > 1 ? (int)work : (int)(work < sm_count() ? work : sm_count());
             best.partial_bytes = 0;
         }
     }
@@ -631,10 +665,10 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
     // finishes them in about 1/s of a round.
     best.tail_tiles = 0; best.tail_splits = 1; best.tail_kps = 0; best.narrow_tiles = 0;
     const long tiles = (long)best.m_tiles * best.n_tiles;
-    if (force_splits <= 0 && best.splits == 1 && tiles > 148 && kblocks >= 64) {   // a round must outlast a launch
-        const int r = (int)(tiles % 148);
-        if (r > 0 && r <= 74) {
-            int s = 148 / r;
+    if (force_splits <= 0 && best.splits == 1 && tiles > sm_count() && kblocks >= 64) {   // a round must outlast a launch
+        const int r = (int)(tiles % sm_count());
+        if (r > 0 && r <= (sm_count() / 2)) {
+            int s = sm_count() / r;
             if (s > 8) s = 8;
             while (s > 1 && kblocks / s < 2) --s;
             if (s > 1) {
@@ -651,20 +685,20 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
     }
     // Short K: a second launch costs more than it saves; the last r <= 74 tiles of a 256-wide plan are
     // instead cut into 2r half-width work items of the same persistent launch.
-    if (force_splits <= 0 && best.bn == 256 && best.splits == 1 && best.tail_tiles == 0 && tiles > 148) {
-        const int r = (int)(tiles % 148);
-        if (r > 0 && r <= 74) best.narrow_tiles = r;
+    if (force_splits <= 0 && best.bn == 256 && best.splits == 1 && best.tail_tiles == 0 && tiles > sm_count()) {
+        const int r = (int)(tiles % sm_count());
+        if (r > 0 && r <= (sm_count() / 2)) best.narrow_tiles = r;
     }
     return best;
 }
 
-template <int BN, bool kSplit, bool kF16, bool kNarrow = false>
+template <int BN, bool kSplit, bool kF16, bool kNarrow = false, bool kFuseQ = false>
 static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb,
                              const OutMaps& ty, cudaStream_t stream, int tile_base, int tile_end, int splits, int kps,
                              int grid, int narrow_tiles) {
     using Cfg = UmmaCfg<BN>;
     static_assert(!kNarrow || (BN == 256 && !kSplit), "half-width items exist in the 256-wide persistent kernel only");
-    auto kern = umma_gemm_kernel<BN, kSplit, kF16, kNarrow>;
+    auto kern = umma_gemm_kernel<BN, kSplit, kF16, kNarrow, kFuseQ>;
     static SmemOptIn opted;
     {
         cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kSmemBytes, opted);
@@ -679,7 +713,7 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
     s.narrow_from = tile_end - narrow_tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kThreads + (kFuseQ ? kQuantWarps * 32 : 0));
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -727,9 +761,18 @@ static cudaError_t launch_umma(bool f16, const UmmaPlan& pl, const UmmaArgs& a, 
 #define FP8LIN_GO(BN_, SPLIT_, F16_) launch_bn<BN_, SPLIT_, F16_>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow)
 #define FP8LIN_GO_BN(BN_) (f16 ? (split ? FP8LIN_GO(BN_, true, true) : FP8LIN_GO(BN_, false, true)) \
                                : (split ? FP8LIN_GO(BN_, true, false) : FP8LIN_GO(BN_, false, false)))
-        if (narrow > 0)       // (only set for 256-wide non-split plans)
+        if (narrow > 0) {     // (only set for 256-wide non-split plans)
+            if (!f16 && a.x) return launch_bn<256, false, false, true, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow);
             return f16 ? launch_bn<256, false, true, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow)
                        : launch_bn<256, false, false, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow);
+        }
+        if (!f16 && !split && a.x) {     // activations quantised inside the persistent launch
+            switch (pl.bn) {
+                case 256: return launch_bn<256, false, false, false, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow);
+                case 128: return launch_bn<128, false, false, false, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow);
+                case 64: return launch_bn<64, false, false, false, true>(pl, a, ta, tb, ty, stream, base, end, splits, kps, grid, narrow);
+            }
+        }
         switch (pl.bn) {
             case 256: return FP8LIN_GO_BN(256);
             case 128: return FP8LIN_GO_BN(128);
@@ -743,7 +786,7 @@ static cudaError_t launch_umma(bool f16, const UmmaPlan& pl, const UmmaArgs& a, 
     if (pl.splits > 1) return go(true, 0, tiles, pl.splits, pl.kblocks_per_split, pl.grid);
     const int narrow = pl.bn == 256 && pl.tail_tiles == 0 ? pl.narrow_tiles : 0;
     const int main_work = main_tiles + narrow;
-    cudaError_t e = go(false, 0, main_tiles, 1, pl.kblocks_per_split, main_work < 148 ? main_work : 148, narrow);
+    cudaError_t e = go(false, 0, main_tiles, 1, pl.kblocks_per_split, main_work < sm_count() ? main_work : sm_count(), narrow);
     if (e != cudaSuccess || pl.tail_tiles == 0) return e;
     return go(true, main_tiles, tiles, pl.tail_splits, pl.tail_kps, pl.tail_tiles * pl.tail_splits);
 }

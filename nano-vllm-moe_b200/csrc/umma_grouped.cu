@@ -268,7 +268,7 @@ static cudaError_t launch_grouped(const GroupedArgs& a, const CUtensorMap& tw, c
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(148);
+    cfg.gridDim = dim3(sm_count());
     cfg.blockDim = dim3(kGrpThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;

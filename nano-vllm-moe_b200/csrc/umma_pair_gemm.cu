@@ -67,8 +67,10 @@ __device__ __forceinline__ void decode_pair_tile(const PairSched& s, int tile, i
 // projection consumes instead of the bf16 tile: h = bf16(silu(g) * u) from g, u rounded to bf16 (the values
 // the unfused path materialises), quantised to e4m3 with the down projection's static scale `h_scale`;
 // 128 bytes per row and tile go to the e4m3 matrix [M][N/2] described by outs.m[0].
-template <bool kF16, bool kMlp>
-__global__ void __launch_bounds__(kThreads, 1)
+// kFuseQ (e4m3 operands only): kQuantWarps more warps per CTA quantise the bf16 activations into xq while the
+// GEMM runs (umma_common.cuh); each CTA's producer waits for its own 128-row block of xq before loading it.
+template <bool kF16, bool kMlp, bool kFuseQ = false>
+__global__ void __launch_bounds__(kThreads + (kFuseQ ? kQuantWarps * 32 : 0), 1)
 umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ OutMaps outs, UmmaArgs p, PairSched sched, const float* h_scale) {
     constexpr int S = kStages;
@@ -104,8 +106,15 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     pdl_launch_dependents();
+    static_assert(!kFuseQ || !kF16, "in-kernel quantisation: e4m3 operands only");
+    QuantJob qjob;
+    qjob.x = p.x; qjob.xq = const_cast<unsigned char*>(p.xq); qjob.ctrl = p.q_ctrl; qjob.ldx = p.ldx; qjob.row_start = p.q_row_start;
 
-    if (warp == 0) {
+    if (kFuseQ && warp >= 2 + kEpiWarps) {
+        // ================= activation quantiser (warps 10..13 of both CTAs) =================
+        pdl_wait();
+        quant_worker(qjob, p.input_scale, p.M, p.K, lane);
+    } else if (warp == 0) {
         // ================= TMA producer (both CTAs) =================
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
@@ -118,6 +127,9 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 decode_pair_tile(sched, t, tmp, tn);
                 const int row0 = (2 * tmp + (int)rank) * kBM;
                 const int n_sub = tn * kBN + (int)rank * 128;             // this CTA's 128 channels
+                if (kFuseQ && (s_abort || !quant_wait_block(qjob, p.M, 2 * tmp + (int)rank, p.status))) {
+                    s_abort = 1; ok = false; break;
+                }
                 for (int kb = 0; kb < sched.kblocks; ++kb, ++it) {
                     const int st = it % S;
                     const uint32_t ph = (it / S) & 1;
@@ -338,12 +350,14 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, kTmemCols);
     }
+    if (kFuseQ && threadIdx.x == 0) quant_ctrl_release(qjob, p.M);
 }
 
-template <bool kF16, bool kMlp>
+template <bool kF16, bool kMlp, bool kFuseQ = false>
 cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& ty,
                         cudaStream_t stream, const char** why, const float* h_scale = nullptr) {
-    auto kern = umma_pair_gemm_kernel<kF16, kMlp>;
+    auto kern = umma_pair_gemm_kernel<kF16, kMlp, kFuseQ>;
+    constexpr int kBlock = kThreads + (kFuseQ ? kQuantWarps * 32 : 0);
     static SmemOptIn opted;
     {
         cudaError_t e = ensure_dynamic_smem((const void*)kern, kSmemBytes, opted);
@@ -354,7 +368,7 @@ cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensor
     s.n_tiles = (a.N + kBN - 1) / kBN;
     s.kblocks = kF16 ? 2 * (int)pack_kblocks(a.K) : (a.K + kBK - 1) / kBK;
     s.total = s.mp_tiles * s.n_tiles;
-    int pairs = max_active_clusters((const void*)kern, kThreads, kSmemBytes, 2);
+    int pairs = max_active_clusters((const void*)kern, kBlock, kSmemBytes, 2);
     if (pairs < 1) {
         if (why) *why = "no CTA pair fits on this device";
         return cudaErrorInvalidConfiguration;
@@ -362,7 +376,7 @@ cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensor
     if (pairs > s.total) pairs = s.total;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kBlock);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -402,6 +416,7 @@ cudaError_t launch_umma_pair(bool f16, const UmmaArgs& a, cudaStream_t stream, c
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }
+    if (!f16 && a.x) return launch_pair<false, false, true>(a, ta, tb, ty, stream, why);
     return f16 ? launch_pair<true, false>(a, ta, tb, ty, stream, why) : launch_pair<false, false>(a, ta, tb, ty, stream, why);
 }
 
@@ -424,6 +439,7 @@ cudaError_t launch_umma_pair_mlp(const UmmaArgs& a, unsigned char* hq, const flo
         if (why) *why = "cuTensorMapEncodeTiled failed";
         return cudaErrorInvalidValue;
     }
+    if (a.x) return launch_pair<false, true, true>(a, ta, tb, ty, stream, why, h_scale);
     return launch_pair<false, true>(a, ta, tb, ty, stream, why, h_scale);
 }
 

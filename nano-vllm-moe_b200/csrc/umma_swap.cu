@@ -371,7 +371,7 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq)
         if (force_splits <= 0 && s > 1 && kblocks / s < 4) break;          // at least four K blocks per slice
         const int kps = (kblocks + s - 1) / s;
         if ((kblocks + kps - 1) / kps != s) continue;                        // would leave an empty slice
-        int slots = 148 * (pl.mp == 16 ? 2 : 1);
+        int slots = sm_count() * (pl.mp == 16 ? 2 : 1);
         if (s > 1) {
             if (preq) slots = pl.mp == 16 ? swap_max_clusters<16, true>(s) : (pl.mp == 32 ? swap_max_clusters<32, true>(s) : swap_max_clusters<64, true>(s));
             else slots = pl.mp == 16 ? swap_max_clusters<16, false>(s) : (pl.mp == 32 ? swap_max_clusters<32, false>(s) : swap_max_clusters<64, false>(s));
@@ -390,7 +390,7 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq)
     // 20.0 / 19.1 / 18.3 us with 6 / 7 / 8 slices although fewer 8-CTA clusters are resident at once --
     // shorter slices ramp and drain faster than the wave model above credits.  Take the most slices
     // that still leave 16 K blocks each.
-    if (force_splits <= 0 && pl.mp == 16 && kblocks >= 64 && pl.n_tiles * 8 <= 2 * 148) {
+    if (force_splits <= 0 && pl.mp == 16 && kblocks >= 64 && pl.n_tiles * 8 <= 2 * sm_count()) {
         for (int s = 8; s > best_s; --s) {
             const int kps = (kblocks + s - 1) / s;
             if (kps >= 16 && (kblocks + kps - 1) / kps == s) { best_s = s; break; }
@@ -398,7 +398,7 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq)
     }
     pl.splits = best_s;
     pl.kblocks_per_split = (kblocks + best_s - 1) / best_s;
-    const int resident = 148 * (pl.mp == 16 ? 2 : 1);
+    const int resident = sm_count() * (pl.mp == 16 ? 2 : 1);
     pl.grid = pl.splits > 1 ? pl.n_tiles * pl.splits : (pl.n_tiles < resident ? pl.n_tiles : resident);
     return pl;
 }

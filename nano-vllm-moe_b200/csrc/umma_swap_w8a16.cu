@@ -386,7 +386,7 @@ SwapPlan plan_swap_w8a16(int64_t M, int64_t K, int64_t N, int force_splits) {
         if (force_splits <= 0 && s > 1 && kblocks / s < 4) break;
         const int kps = (kblocks + s - 1) / s;
         if ((kblocks + kps - 1) / kps != s) continue;
-        int slots = 148;
+        int slots = sm_count();
         if (s > 1) slots = pl.mp == 16 ? swap16_max_clusters<16>(s) : (pl.mp == 32 ? swap16_max_clusters<32>(s) : swap16_max_clusters<64>(s));
         if (slots < 1) slots = 1;
         const int waves = (pl.n_tiles + slots - 1) / slots;
@@ -395,7 +395,7 @@ SwapPlan plan_swap_w8a16(int64_t M, int64_t K, int64_t N, int force_splits) {
     }
     pl.splits = best_s;
     pl.kblocks_per_split = (kblocks + best_s - 1) / best_s;
-    pl.grid = pl.splits > 1 ? pl.n_tiles * pl.splits : (pl.n_tiles < 148 ? pl.n_tiles : 148);
+    pl.grid = pl.splits > 1 ? pl.n_tiles * pl.splits : (pl.n_tiles < sm_count() ? pl.n_tiles : sm_count());
     return pl;
 }
 

@@ -23,6 +23,47 @@ def dequant_matmul(x_bf16: torch.Tensor, q_nk_u8: torch.Tensor, scale: torch.Ten
     return torch.mm(x_bf16, w.t())
 
 
+def time_linears(ops, steps: int, warmup: int, budget_s: float, rows_cap: int = 256):
+    """Time the reference's CPU formula on a bounded sample of a list of linears.
+
+    ops = [(x [M,K] bf16, q_nk [N,K] uint8, scale [N] f32, full_rows)]: every x holds at most
+    ``rows_cap`` of the ``full_rows`` rows the workload has; a linear's time is scaled by
+    full_rows / M (a matmul's time is linear in its rows) and the scaled times are summed to one pass.
+    Two figures per pass, as the reference's microbenchmarks report them: ``cached`` multiplies by a
+    bf16 weight dequantised once outside the timed region (fp8_linear_microbench.py:67,77 -- weights
+    as [K,N]), ``dequant`` dequantises inside every call (w8a16_linear_microbench.py:47-53).
+    Returns {"cached": [seconds per pass], "dequant": [...], "threads": n}."""
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    prepared = []
+    for x, q_nk, scale, full_rows in ops:
+        q_kn = q_nk.t().contiguous()                                   # the reference's runtime layout [K,N]
+        w_bf16 = q_kn.view(torch.float8_e4m3fn).to(torch.bfloat16) * scale.to(torch.bfloat16).unsqueeze(0)
+        prepared.append((x, q_kn, scale, w_bf16, full_rows / max(x.shape[0], 1)))
+
+    def one_pass(cached: bool) -> float:
+        total = 0.0
+        for x, q_kn, scale, w_bf16, factor in prepared:
+            t0 = time.perf_counter()
+            if cached:
+                torch.mm(x, w_bf16)
+            else:
+                torch.mm(x, q_kn.view(torch.float8_e4m3fn).to(torch.bfloat16) * scale.to(torch.bfloat16).unsqueeze(0))
+            total += (time.perf_counter() - t0) * factor
+        return total
+
+    out = {"cached": [], "dequant": [], "threads": torch.get_num_threads()}
+    for _ in range(warmup):
+        one_pass(True); one_pass(False)
+    t_start = time.perf_counter()
+    for _ in range(steps):
+        out["cached"].append(one_pass(True))
+        out["dequant"].append(one_pass(False))
+        if time.perf_counter() - t_start > budget_s:
+            break
+    return out
+
+
 def time_passes(tensors, steps: int, warmup: int, budget_s: float) -> tuple[list[float], int]:
     """Time ``steps`` passes over ``tensors`` = [(x, q_nk, scale), ...]; stops early when the
     wall-clock budget is spent.  Returns (seconds per pass, threads used)."""

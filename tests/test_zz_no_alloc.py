@@ -3,7 +3,9 @@ device memory (a server whose KV-cache pool already owns all free HBM, or a
 latency-critical loop that must not wait on an allocation).  It keeps its
 split-K scratch in a fixed array inside the library instead of a caller's
 workspace.  The test calls it through the C ABI, twice in a row on the same
-shared array, and compares with the workspace-taking entry points.
+shared array, and compares with the workspace-taking entry points and with the
+CPU oracle (the first alone would be a weak check where both entry points run
+the same kernel on different scratch).
 
 This file is named so that pytest collects it last."""
 import numpy as np
@@ -11,7 +13,7 @@ import pytest
 import torch
 
 from oracle import fp8_oracle as O
-from helpers import assert_parity, from_bf16, kernels, run_linear, upload_case
+from helpers import assert_parity, from_bf16, kernels, oracle_linear, run_linear, upload_case
 
 pytestmark = pytest.mark.gpu
 
@@ -44,6 +46,7 @@ def test_static_scratch_matches_workspace_entry_point(pkg, scheme):
         assert_parity(first, want, f"static scratch {scheme} {m}x{k}x{n} (1st call)")
         assert_parity(second, want, f"static scratch {scheme} {m}x{k}x{n} (2nd call)")
         np.testing.assert_array_equal(first, second)
+        assert_parity(first, oracle_linear(scheme, c), f"static scratch {scheme} {m}x{k}x{n} vs the oracle")
         del d
 
 
