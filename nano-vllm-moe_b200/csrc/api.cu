@@ -35,8 +35,10 @@ struct Tuning {
     int w8a16_umma_min_m = -1;  // smallest M for the dequantise-to-f16 + tcgen05 GEMM route (0 = never)
     int w8a16_chunk_mb = -1;    // size of the f16 weight chunk that route keeps in L2
     int umma_pair = -1;         // 1 = large-M GEMMs on CTA pairs (256 x 256 tiles), 0 = never
-    int fuse_quant = -1;        // large-M W8A8: 0 = quantise x in a separate pass, never inside the GEMM;
-                                // n > 0 = the pass takes the first n rows (rounded up to 128), the GEMM the rest
+    int fuse_quant = -1;        // large-M W8A8: <= 0 (default) = quantise x in a separate pass; 1 = the pass takes the rows
+                                // of the first round of tiles, the GEMM's own quantiser warps the rest; n > 1 = the pass
+                                // takes the first n rows (rounded up to 128)
+    int quant_lead = -1;        // row blocks the in-kernel quantiser may run ahead (default: from the tile schedule)
 } g_tune;
 
 constexpr int kDefaultStreamMaxM = 64;
@@ -166,8 +168,14 @@ bool swap_prequant(int64_t M) {
 // round of tiles reads (tiles are walked in groups of eight tile rows), the kernel's quantiser warps do the
 // rest while the tensor cores run.  Returns the number of rows for the pass; M = everything (no fusion).
 int64_t prequant_rows(int64_t M, int64_t n_tiles, int tile_rows, int first_round_tiles) {
-    if (g_tune.fuse_quant == 0 || 2 + (M + 127) / 128 > kWsMaxCounters) return M;
-    if (g_tune.fuse_quant > 0) {                      // forced split (tests): this many rows, rounded up to a row block
+    // Off unless asked for.  Measured on a B200 (same process, alternating windows, 7B layer shapes at 4096 / 8192 /
+    // 16384 rows): with the quantiser inside the GEMM qkv 77 / 141 / 274 us against 74 / 142 / 277 us with the
+    // separate pass, o_proj 68 / 124 / 235 against 65 / 122 / 232, gate_up 511 / 1017 / 2045 against 513 / 1021 /
+    // 2040, down 328 / 607 / 1180 against 296 / 579 / 1150.  These GEMMs run at the board's power limit (SM clock
+    // 1.25-1.5 GHz of 1.965): hiding the pass does not remove its energy, the clock drops by what the extra warps
+    // draw, and the pass alone runs at a power the GEMM never sees.
+    if (g_tune.fuse_quant <= 0 || 3 + (M + 127) / 128 > kWsMaxCounters) return M;
+    if (g_tune.fuse_quant > 1) {                      // forced split (tests): this many rows, rounded up to a row block
         const int64_t forced = ((int64_t)g_tune.fuse_quant + 127) / 128 * 128;
         return forced >= M ? M : forced;
     }
@@ -180,12 +188,18 @@ int64_t prequant_rows(int64_t M, int64_t n_tiles, int tile_rows, int first_round
 }
 
 // Quantise rows [0, pre) in a pass of their own and hand the rest to the GEMM's quantiser warps.
+// n_tiles, tile_rows, round_tiles: the GEMM's column tiles, rows per tile (128, or 256 on CTA pairs) and tiles in flight.
 int start_quant(const void* x, int64_t ldx, const float* input_scale, unsigned char* xq, int64_t M, int64_t K, int64_t pre,
-                const WsView& ws, UmmaArgs& a, cudaStream_t st) {
+                const WsView& ws, UmmaArgs& a, cudaStream_t st, int64_t n_tiles, int tile_rows, int round_tiles) {
     cudaError_t e = launch_act_quant((const __nv_bfloat16*)x, ldx, input_scale, xq, pre, K, st);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation quantiser launch: %s", cudaGetErrorString(e));
     if (pre < M) {
         a.x = (const __nv_bfloat16*)x; a.ldx = (int)ldx; a.q_row_start = (int)pre; a.q_ctrl = ws.counters;
+        // a CTA's next tile lies one round ahead: that many groups of eight tile rows, plus the group in progress
+        // and one more so that the next blocks are ready when the tiles get there
+        const int64_t groups_per_round = (round_tiles + 8 * n_tiles - 1) / (8 * n_tiles);
+        a.q_lead = (int)((groups_per_round + 2) * 8 * (tile_rows / 128));
+        if (g_tune.quant_lead >= 0) a.q_lead = g_tune.quant_lead;
     }
     return FP8LIN_OK;
 }
@@ -391,7 +405,8 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
     const bool pair = pair_eligible(M, N);
     const int64_t pre = pair ? prequant_rows(M, (N + 255) / 256, 256, sm_count() / 2)
                              : (pl.splits > 1 ? M : prequant_rows(M, pl.n_tiles, 128, sm_count()));
-    rc = start_quant(x, ldx, input_scale, xq, M, K, pre, ws, a, st);
+    rc = pair ? start_quant(x, ldx, input_scale, xq, M, K, pre, ws, a, st, (N + 255) / 256, 256, sm_count() / 2)
+              : start_quant(x, ldx, input_scale, xq, M, K, pre, ws, a, st, pl.n_tiles, 128, sm_count());
     if (rc != FP8LIN_OK) return rc;
     const char* why = nullptr;
     cudaError_t e = pair ? launch_umma_pair(false, a, st, &why) : launch_umma_w8a8(pl, a, st, &why);
@@ -420,7 +435,8 @@ int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const floa
     a.xq = ws.body; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
     a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)dst_ptrs[0]; a.partial = nullptr; a.counters = ws.counters;
     a.status = ws.status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ld_dst;
-    rc = start_quant(x, ldx, input_scale, ws.body, M, K, prequant_rows(M, pl.n_tiles, 128, sm_count()), ws, a, st);
+    rc = start_quant(x, ldx, input_scale, ws.body, M, K, prequant_rows(M, pl.n_tiles, 128, sm_count()), ws, a, st, pl.n_tiles, 128,
+                     sm_count());
     if (rc != FP8LIN_OK) return rc;
     const char* why = nullptr;
     cudaError_t e = launch_umma_w8a8(pl, a, st, &why, n_dst, dst_ptrs, ld_dst);
@@ -511,7 +527,8 @@ int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const flo
         a.xq = xq; a.w = (const unsigned char*)w_gate_up; a.w_scale = gate_up_scale; a.input_scale = gate_up_input_scale;
         a.bias = (const __nv_bfloat16*)gate_up_bias; a.y = nullptr; a.partial = nullptr; a.counters = ws.counters;
         a.status = ws.status; a.M = (int)M; a.K = (int)H; a.N = (int)(2 * I); a.ldy = 0;
-        rc = start_quant(x, ldx, gate_up_input_scale, xq, M, H, prequant_rows(M, (2 * I + 255) / 256, 256, sm_count() / 2), ws, a, st);
+        rc = start_quant(x, ldx, gate_up_input_scale, xq, M, H, prequant_rows(M, (2 * I + 255) / 256, 256, sm_count() / 2), ws, a, st,
+                         (2 * I + 255) / 256, 256, sm_count() / 2);
         if (rc != FP8LIN_OK) return rc;
         const char* why = nullptr;
         cudaError_t e = launch_umma_pair_mlp(a, hq, down_input_scale, st, &why);
@@ -617,6 +634,7 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "w8a16_chunk_mb")) g_tune.w8a16_chunk_mb = value;
     else if (!strcmp(knob, "umma_pair")) g_tune.umma_pair = value;
     else if (!strcmp(knob, "fuse_quant")) g_tune.fuse_quant = value;
+    else if (!strcmp(knob, "quant_lead")) g_tune.quant_lead = value;
     else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;

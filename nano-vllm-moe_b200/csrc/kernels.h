@@ -82,10 +82,13 @@ struct UmmaArgs {
     int ldy;
     // Activation quantisation inside the kernel (large-M W8A8, e4m3 operands only): when x is not NULL the
     // kernel's quantiser warps write rows [q_row_start, M) of xq from x while the GEMM runs; rows below
-    // q_row_start (a multiple of 128) must already be in xq.  q_ctrl: 2 + ceil(M / 128) zeroed ints of scratch.
+    // q_row_start (a multiple of 128) must already be in xq.  q_ctrl: 3 + ceil(M / 128) zeroed ints of scratch.
+    // q_lead: 128-row blocks the quantiser may run ahead of the tiles in progress (at least the blocks that two
+    // consecutive rounds of tiles span, so that no tile ever waits for a throttled quantiser).
     const __nv_bfloat16* x = nullptr;
     int ldx = 0;
     int q_row_start = 0;
+    int q_lead = 0;
     int* q_ctrl = nullptr;
 };
 

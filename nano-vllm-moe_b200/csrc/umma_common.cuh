@@ -214,7 +214,12 @@ bool encode_out_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
 // reached its number of units.  Tickets are only ever taken by warps that are already running, and a warp
 // holding a ticket waits for nothing, so the scheme makes progress however many of the grid's CTAs are
 // resident at a time.  The last CTA to leave zeroes the counters again (scratch counters are zero between
-// calls).  Layout of ctrl: [0] next ticket, [1] CTAs that have left, [2 + b] units done in row block b.
+// calls).  The quantiser warps stay at most `lead` row blocks ahead of the furthest row block any producer has
+// started on (the "frontier"): running far ahead would stream all of x and xq through L2 while the GEMM's own
+// tiles live there, which measurably slows the GEMM down.  The lead is large enough that a producer never needs
+// a block beyond frontier + lead, so the throttle cannot stall the kernel (and a throttle wait that runs out
+// simply proceeds).  Layout of ctrl: [0] next ticket, [1] CTAs that have left, [2] frontier, [3 + b] units done
+// in row block b.
 constexpr int kQuantWarps = 4;
 constexpr int kQuantRows = 8;           // rows per unit; divides 128, so a unit lies inside one row block
 
@@ -224,7 +229,9 @@ struct QuantJob {
     int* ctrl;
     int ldx;
     int row_start;               // multiple of 128
+    int lead;                    // row blocks the quantiser may run ahead of the frontier
 };
+constexpr int kQuantCtrlWords = 3;
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     int v;
@@ -244,8 +251,9 @@ __device__ __forceinline__ int quant_units_in_block(const QuantJob& j, int M, in
 // Producer side: wait until row block `block` of xq is complete.  false = gave up (status written).
 __device__ __forceinline__ bool quant_wait_block(const QuantJob& j, int M, int block, int* status) {
     const int need = quant_units_in_block(j, M, block);
-    if (need == 0) return true;
-    const int* flag = j.ctrl + 2 + block;
+    if (need == 0) { atomicMax(j.ctrl + 2, block); return true; }
+    atomicMax(j.ctrl + 2, block);          // the frontier moves before the wait: the quantiser may be throttled on it
+    const int* flag = j.ctrl + kQuantCtrlWords + block;
     long long start = -1;
     for (uint32_t it = 0;; ++it) {
         if (ld_acquire_gpu(flag) >= need) break;
@@ -260,6 +268,15 @@ __device__ __forceinline__ bool quant_wait_block(const QuantJob& j, int M, int b
     return true;
 }
 
+// Early, non-blocking look at a row block the producer will need one tile from now: true = already complete
+// (completeness is monotonic, so the answer stays valid).  Issued a whole tile ahead, the global round trip of the
+// flag load overlaps the tile's loads instead of stalling the producer at the tile boundary.  Also moves the frontier.
+__device__ __forceinline__ bool quant_probe_block(const QuantJob& j, int M, int block) {
+    atomicMax(j.ctrl + 2, block);
+    const int need = quant_units_in_block(j, M, block);
+    return need == 0 || ld_acquire_gpu(j.ctrl + kQuantCtrlWords + block) >= need;
+}
+
 // One quantiser warp: take units until none are left.
 __device__ __forceinline__ void quant_worker(const QuantJob& j, const float* input_scale, int M, int K, int lane) {
     const ExactDiv div(fmaxf(__ldg(input_scale), 1e-12f));
@@ -272,21 +289,34 @@ __device__ __forceinline__ void quant_worker(const QuantJob& j, const float* inp
         if (u >= total_units) break;
         const int row0 = j.row_start + u * kQuantRows;
         const int rows = min(kQuantRows, M - row0);
-        // two rows per step: four 16-byte loads in flight per lane
-        for (int r = 0; r < rows; r += 2) {
-            const bool two = r + 1 < rows;
-            const __nv_bfloat16* s0 = j.x + (size_t)(row0 + r) * j.ldx;
-            const __nv_bfloat16* s1 = s0 + (two ? j.ldx : 0);
-            unsigned char* d0 = j.xq + (size_t)(row0 + r) * K;
-            unsigned char* d1 = d0 + (two ? K : 0);
+        if ((row0 >> 7) > ld_acquire_gpu(j.ctrl + 2) + j.lead) {          // too far ahead of the GEMM: hold back
+            const long long t0 = clock64();
+            while ((row0 >> 7) > ld_acquire_gpu(j.ctrl + 2) + j.lead && clock64() - t0 < kWaitCycles) __nanosleep(256);
+        }
+        // four rows per step: eight 16-byte loads in flight per lane.  The quantiser is latency-bound (a few
+        // warps per SM), and it has to keep up with the rate at which the GEMM consumes rows.
+        for (int r = 0; r < rows; r += 4) {
+            const __nv_bfloat16* src[4];
+            unsigned char* dst[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int rr = min(r + q, rows - 1);                   // a short tail re-reads the last row (not stored)
+                src[q] = j.x + (size_t)(row0 + rr) * j.ldx;
+                dst[q] = j.xq + (size_t)(row0 + rr) * K;
+            }
             for (int v = lane; v < vec_per_row; v += 32) {
-                const uint4 a0 = ld_stream16(s0 + v * 16), a1 = ld_stream16(s0 + v * 16 + 8);
-                const uint4 b0 = ld_stream16(s1 + v * 16), b1 = ld_stream16(s1 + v * 16 + 8);
-                const uint2 qa0 = quant8_e4m3(a0, div), qa1 = quant8_e4m3(a1, div);
-                *reinterpret_cast<uint4*>(d0 + v * 16) = make_uint4(qa0.x, qa0.y, qa1.x, qa1.y);
-                if (two) {
-                    const uint2 qb0 = quant8_e4m3(b0, div), qb1 = quant8_e4m3(b1, div);
-                    *reinterpret_cast<uint4*>(d1 + v * 16) = make_uint4(qb0.x, qb0.y, qb1.x, qb1.y);
+                uint4 a[4][2];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    a[q][0] = ld_stream16(src[q] + v * 16);
+                    a[q][1] = ld_stream16(src[q] + v * 16 + 8);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if (r + q < rows) {
+                        const uint2 q0 = quant8_e4m3(a[q][0], div), q1 = quant8_e4m3(a[q][1], div);
+                        *reinterpret_cast<uint4*>(dst[q] + v * 16) = make_uint4(q0.x, q0.y, q1.x, q1.y);
+                    }
                 }
             }
         }
@@ -294,7 +324,7 @@ __device__ __forceinline__ void quant_worker(const QuantJob& j, const float* inp
         if (lane == 0) {
             fence_proxy_async_all();
             __threadfence();
-            atomicAdd(j.ctrl + 2 + (row0 >> 7), 1);
+            atomicAdd(j.ctrl + kQuantCtrlWords + (row0 >> 7), 1);
         }
     }
 }
@@ -306,8 +336,9 @@ __device__ __forceinline__ void quant_ctrl_release(const QuantJob& j, int M) {
     const int left = atomicAdd(j.ctrl + 1, 1);
     if (left == (int)gridDim.x - 1) {
         const int blocks = (M + 127) >> 7;
-        for (int b = 0; b < blocks; ++b) j.ctrl[2 + b] = 0;
+        for (int b = 0; b < blocks; ++b) j.ctrl[kQuantCtrlWords + b] = 0;
         j.ctrl[0] = 0;
+        j.ctrl[2] = 0;
         __threadfence();
         j.ctrl[1] = 0;
     }

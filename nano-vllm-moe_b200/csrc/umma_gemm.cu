@@ -172,7 +172,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     pdl_launch_dependents();
     static_assert(!kFuseQ || (!kSplit && !kF16), "in-kernel quantisation: persistent e4m3 launches only");
     QuantJob qjob;
-    qjob.x = p.x; qjob.xq = const_cast<unsigned char*>(p.xq); qjob.ctrl = p.q_ctrl; qjob.ldx = p.ldx; qjob.row_start = p.q_row_start;
+    qjob.x = p.x; qjob.xq = const_cast<unsigned char*>(p.xq); qjob.ctrl = p.q_ctrl; qjob.ldx = p.ldx; qjob.row_start = p.q_row_start; qjob.lead = p.q_lead;
 
     if (kFuseQ && warp >= 2 + kEpiWarps) {
         // ================= activation quantiser (warps 10..13) =================
@@ -186,6 +186,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t it = 0;
             bool ok = true;
             bool waited = false;      // weight tiles of the first ring pass go out before the predecessor is done
+            bool next_ready = false;  // (kFuseQ) the next tile's rows of xq were complete when last looked at
             if (kF16) pdl_wait();     // ... unless the predecessor is the pass that writes the f16 weight tiles
             for (int w = first_work; w < sched.total_work && ok; w += work_step) {
                 const WorkItem wk = decode_work<BN, kNarrow>(sched, w);
@@ -208,13 +209,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     pdl_wait();       // the quantised activations are written by the kernel before this one
                     if (kFuseQ && !quant_wait_block(qjob, p.M, tm, p.status)) { s_abort = 1; ok = false; break; }
+                    if (kFuseQ && w + work_step < sched.total_work)
+                        next_ready = quant_probe_block(qjob, p.M, decode_work<BN, kNarrow>(sched, w + work_step).tm);
                     for (int i = 0; i < first_kb; ++i)
                         tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_a, (kb0 + i) * kBK, tm * kBM, smem_u32(&bar_full[i]));
                     waited = true;
                     it = (uint32_t)first_kb;
                     if (kb0 + first_kb >= kb1) continue;
                 } else if (kFuseQ) {
-                    if (s_abort || !quant_wait_block(qjob, p.M, tm, p.status)) { s_abort = 1; ok = false; break; }
+                    if (next_ready) fence_proxy_async_all();
+                    else if (s_abort || !quant_wait_block(qjob, p.M, tm, p.status)) { s_abort = 1; ok = false; break; }
+                    next_ready = w + work_step < sched.total_work &&
+                                 quant_probe_block(qjob, p.M, decode_work<BN, kNarrow>(sched, w + work_step).tm);
                 }
                 for (int kb = kb0 + (w == first_work ? min(kb1 - kb0, S) : 0); kb < kb1; ++kb, ++it) {
                     const int st = it % S;

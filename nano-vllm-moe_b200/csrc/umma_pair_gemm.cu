@@ -108,7 +108,7 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     pdl_launch_dependents();
     static_assert(!kFuseQ || !kF16, "in-kernel quantisation: e4m3 operands only");
     QuantJob qjob;
-    qjob.x = p.x; qjob.xq = const_cast<unsigned char*>(p.xq); qjob.ctrl = p.q_ctrl; qjob.ldx = p.ldx; qjob.row_start = p.q_row_start;
+    qjob.x = p.x; qjob.xq = const_cast<unsigned char*>(p.xq); qjob.ctrl = p.q_ctrl; qjob.ldx = p.ldx; qjob.row_start = p.q_row_start; qjob.lead = p.q_lead;
 
     if (kFuseQ && warp >= 2 + kEpiWarps) {
         // ================= activation quantiser (warps 10..13 of both CTAs) =================
@@ -122,13 +122,21 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             pdl_wait();            // the activations (and, for f16, the weight tiles) come from the kernel before
             uint32_t it = 0;
             bool ok = true;
+            bool next_ready = false;     // (kFuseQ) the next tile's rows of xq were complete when last looked at
             for (int t = first_tile; t < sched.total && ok; t += tile_step) {
                 int tmp, tn;
                 decode_pair_tile(sched, t, tmp, tn);
                 const int row0 = (2 * tmp + (int)rank) * kBM;
                 const int n_sub = tn * kBN + (int)rank * 128;             // this CTA's 128 channels
-                if (kFuseQ && (s_abort || !quant_wait_block(qjob, p.M, 2 * tmp + (int)rank, p.status))) {
-                    s_abort = 1; ok = false; break;
+                if (kFuseQ) {
+                    if (next_ready) fence_proxy_async_all();
+                    else if (s_abort || !quant_wait_block(qjob, p.M, 2 * tmp + (int)rank, p.status)) { s_abort = 1; ok = false; break; }
+                    next_ready = false;
+                    if (t + tile_step < sched.total) {
+                        int ntmp, ntn;
+                        decode_pair_tile(sched, t + tile_step, ntmp, ntn);
+                        next_ready = quant_probe_block(qjob, p.M, 2 * ntmp + (int)rank);
+                    }
                 }
                 for (int kb = 0; kb < sched.kblocks; ++kb, ++it) {
                     const int st = it % S;

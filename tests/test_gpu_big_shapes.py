@@ -103,14 +103,14 @@ def test_prefill_shapes_sampled(m, k, n, pair, expect):
     name = Kn.variant_name(1, m, k, n)
     assert expect in name, name
     d = big_case(m + k + n, m, k, n)
-    y = run("fp8_w8a8_static", d)              # default: rows past the first round of tiles are quantised inside the GEMM
+    y = run("fp8_w8a8_static", d)              # default: a separate pass quantises the activations
     rng = np.random.default_rng(m + n)
     rows, cols = sample(m, 48, rng), sample(n, 160, rng)
     check_sampled("fp8_w8a8_static", d, y, rows, cols, f"{name} {m}x{k}x{n}")
     # every row block and column block is written: no element keeps the fill value
     assert torch.isfinite(y.float()).all()
     assert torch.equal(y, run("fp8_w8a8_static", d))
-    Kn.set_tuning("fuse_quant", 0)             # the same GEMM behind a separate activation-quantiser pass: same bits
+    Kn.set_tuning("fuse_quant", 1)             # rows past the first round of tiles quantised inside the GEMM: same bits
     assert torch.equal(y, run("fp8_w8a8_static", d))
 
 
