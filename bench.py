@@ -66,6 +66,9 @@ for _m in (16, 64, 1024, 4096):    # fused MLP block (gate_up -> silu * up -> qu
 MLP = {"hidden": 3584, "inter": 18944}
 for _t in (1, 64, 1024, 4096):
     WORKLOADS[f"c5_t{_t}"] = ("moe_w8a8", _t)
+for _m in (1, 16, 64):             # the linear path of 28 decoder layers, replayed from one CUDA graph
+    WORKLOADS[f"c7_decode_layer_m{_m}"] = ("decode_w8a8", _m)
+DECODE = {"layers": 28, "hidden": 3584, "inter": 18944, "qkv": 4608}
 MOE = {"hidden": 2048, "experts": 60, "inter": 1408, "top_k": 4}
 
 DEFAULT_WORKLOAD = "c4_m16384"
@@ -622,6 +625,160 @@ def bench_moe(args, T):
         os._exit(0)
 
 
+def bench_decode(args, M):
+    """One step = the linear path of 28 decoder layers of a 7B-shaped model on M rows, W8A8-static:
+    per layer RMSNorm(+residual) fused with the e4m3 quantiser -> qkv on the codes -> [attention stand-in: the
+    first `hidden` columns] -> o_proj -> RMSNorm(+residual)+quantiser -> fused MLP on the codes; the whole step is
+    one CUDA graph on static buffers, as the reference's runner replays its decode step
+    (nanovllm/engine/model_runner.py:488-541).  `unfused_ms` runs the same layers as the reference composes
+    them: a bf16 RMSNorm, then every linear quantising its own input, the MLP as three steps."""
+    H, I, QKV, LAYERS = DECODE["hidden"], DECODE["inter"], DECODE["qkv"], DECODE["layers"]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    per_layer = H * QKV + H * H + H * 2 * I + I * H
+    flops = 2.0 * M * per_layer * LAYERS
+    config = {"workload": args.workload, "rows": M, **DECODE}
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        from oracle import torch_ref
+        torch.set_num_threads(os.cpu_count() or 1)
+        g = torch.Generator().manual_seed(SEED)
+        shapes = [(H, QKV), (H, H), (H, 2 * I), (I, H)]
+        ws = [(torch.randint(0, 120, (n, k), generator=g, dtype=torch.uint8), torch.full((n,), 1e-4)) for k, n in shapes]
+        wb = [q.t().contiguous().view(torch.float8_e4m3fn).to(torch.bfloat16) * s.to(torch.bfloat16).unsqueeze(0) for q, s in ws]
+        norm_w = torch.ones(H, dtype=torch.bfloat16)
+
+        def rms(x, res):
+            v = x.float() + res.float()
+            return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16) * norm_w, v.to(torch.bfloat16)
+
+        def layer(x, res):           # one decoder layer with cached bf16 weights (the microbenchmarks' W8A8 figure)
+            y, res = rms(x, res)
+            q = torch.mm(y, wb[0])
+            a = torch.mm(q[:, :H].contiguous(), wb[1])
+            y, res = rms(a, res)
+            gu = torch.mm(y, wb[2])
+            g_, u_ = gu.chunk(2, -1)
+            return torch.mm(torch.nn.functional.silu(g_) * u_, wb[3]), res
+        x = torch.randn((M, H), generator=g).to(torch.bfloat16)
+        res = torch.zeros_like(x)
+        times = []
+        for i in range(args.warmup + max(args.steps, 3)):
+            t0 = time.perf_counter(); layer(x, res); dt = time.perf_counter() - t0
+            if i >= args.warmup:
+                times.append(dt)
+            if sum(times) > 60:
+                break
+        sec = statistics.median(times) * LAYERS
+        val = flops / sec / 1e12
+        print(json.dumps({"impl": "reference", "metric": "fp8_linear_throughput", "value": val, "unit": "TFLOP/s",
+                          "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": sec * 1e3,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "bf16 (cpu dequant-then-matmul)", "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                           "sample": f"one of the {LAYERS} layers per pass (cached bf16 weights), time scaled by {LAYERS}"},
+                          "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return
+    if world > 1:
+        if rank == 0:
+            print(json.dumps({"metric": "fp8_linear_throughput", "unavailable": "the decode-layer workload is a one-GPU measurement"}))
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    Kn = importlib.import_module("nano-vllm-moe_b200.quantization.kernels")
+    lib = importlib.import_module("nano-vllm-moe_b200")._lib
+    peaks = load_peaks()
+    W = []
+    for li in range(LAYERS):
+        L = {}
+        for name, (k, n) in {"qkv": (H, QKV), "o": (H, H), "gate_up": (H, 2 * I), "down": (I, H)}.items():
+            q, sc = make_weights(k, n, SEED + 100 * li + len(L), dev)
+            L[name] = (Kn.pack_weight_nk(q), sc)
+            del q
+        L["gate_up_il"] = Kn.interleave_gate_up(L["gate_up"][0], L["gate_up"][1], None, I)[:2]
+        L["norm1"] = torch.ones(H, dtype=torch.bfloat16, device=dev)
+        L["norm2"] = torch.ones(H, dtype=torch.bfloat16, device=dev)
+        W.append(L)
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=dev)          # noqa: E731
+    s_qkv, s_o, s_gu, s_down = f32(6.0 / 448), f32(3.0 / 448), f32(6.0 / 448), f32(2.0 / 448)
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    hidden = torch.randn((M, H), generator=g, device=dev).to(torch.bfloat16)
+    host_in, host_out = hidden.cpu().pin_memory(), torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
+    work, residual = torch.empty_like(hidden), torch.empty_like(hidden)
+    xq = torch.empty((M, H), dtype=torch.uint8, device=dev)
+    qkv = torch.empty((M, QKV), dtype=torch.bfloat16, device=dev)
+    attn, normed = torch.empty_like(hidden), torch.empty_like(hidden)
+    gu = torch.empty((M, 2 * I), dtype=torch.bfloat16, device=dev)
+
+    def fused_step():
+        work.copy_(hidden); residual.zero_()
+        for L in W:
+            Kn.rmsnorm_quant(work, L["norm1"], 1e-6, input_scale=s_qkv, residual=residual, xq_out=xq)
+            Kn.launch_w8a8_preq(xq, L["qkv"][0], s_qkv, L["qkv"][1], None, out=qkv)
+            Kn.launch_w8a8_gemm(qkv[:, :H], L["o"][0], s_o, L["o"][1], None, out=attn)
+            Kn.rmsnorm_quant(attn, L["norm2"], 1e-6, input_scale=s_gu, residual=residual, xq_out=xq)
+            Kn.launch_mlp_w8a8(xq, L["gate_up_il"][0], L["gate_up_il"][1], s_gu, None, L["down"][0], L["down"][1], s_down, None, out=work)
+
+    def unfused_step():
+        work.copy_(hidden); residual.zero_()
+        for L in W:
+            Kn.rmsnorm_quant(work, L["norm1"], 1e-6, residual=residual, y_out=normed)
+            Kn.launch_w8a8_gemm(normed, L["qkv"][0], s_qkv, L["qkv"][1], None, out=qkv)
+            Kn.launch_w8a8_gemm(qkv[:, :H], L["o"][0], s_o, L["o"][1], None, out=attn)
+            Kn.rmsnorm_quant(attn, L["norm2"], 1e-6, residual=residual, y_out=normed)
+            Kn.launch_w8a8_gemm(normed, L["gate_up"][0], s_gu, L["gate_up"][1], None, out=gu)
+            a_, b_ = gu.chunk(2, -1)
+            Kn.launch_w8a8_gemm(torch.nn.functional.silu(a_) * b_, L["down"][0], s_down, L["down"][1], None, out=work)
+
+    side = torch.cuda.Stream(dev)
+    sampler = ClockSampler(0); sampler.start()
+    with torch.cuda.stream(side):
+        Kn.reserve_workspace(dev, 256 << 20)
+    ms_unfused, _ = time_graph(unfused_step, dev, side, args.min_seconds, 1, None, sampler)
+    n0 = Kn.launch_count()
+    with torch.cuda.stream(side):
+        fused_step(); torch.cuda.synchronize()
+    per_step = Kn.launch_count() - n0
+    ms, marks = time_graph(fused_step, dev, side, max(args.min_seconds, 0.4), 1, None, sampler)
+    clocks = sampler.summary(*marks)
+    # end to end: the step's input from pinned host memory, its output back, every step
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            fused_step()
+    def e2e_step():
+        hidden.copy_(host_in, non_blocking=True); graph.replay(); host_out.copy_(work, non_blocking=True)
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(10, int(args.min_seconds * 1e3 / ms))
+    a.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    b.record(); torch.cuda.synchronize()
+    e2e_ms = a.elapsed_time(b) / n_e2e
+    status = Kn.read_status(dev)
+    sampler.stop()
+    by = float(LAYERS * per_layer)                     # the weights, once per step: everything else is negligible at these row counts
+    ach = by / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "fp8_linear_throughput", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 -> bf16", "data": "synthetic", "config": config,
+        "run": {"launch": "one CUDA graph per step, static buffers", "l2": f"{LAYERS} distinct layers, {by / 1e9:.1f} GB of weights per step",
+                "timing": f"graph replays for at least {max(args.min_seconds, 0.4)} s, CUDA events"},
+        "clocks": clocks, "unfused_ms": ms_unfused, "fused_over_unfused": ms_unfused / ms, "us_per_layer": ms * 1e3 / LAYERS,
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                     "traffic": None, "algorithmic_bytes": by, "kernel": "decode kernels (norm+quantise, swapped-operand tcgen05 linears, fused MLP)",
+                     "peak_source": f"{peaks['source']}: HBM copy {peaks['hbm_gbs']} GB/s"},
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2},
+        "gpu_launches": per_step * args.steps, "kernels_per_step": per_step, "device_status": status}), flush=True)
+
+
 # --------------------------------------------------------------------------- linears: our arm
 def dram_traffic_table():
     """DRAM bytes per launch measured under ncu, keyed by "<variant> MxKxN" (text file: key, read bytes, write bytes)."""
@@ -765,6 +922,8 @@ def main():
         return bench_moe(args, WORKLOADS[args.workload][1])
     if WORKLOADS[args.workload][0] == "mlp_w8a8":
         return bench_mlp(args, WORKLOADS[args.workload][1])
+    if WORKLOADS[args.workload][0] == "decode_w8a8":
+        return bench_decode(args, WORKLOADS[args.workload][1])
     scheme, ops = WORKLOADS[args.workload]
     flops = sum(2 * m * k * n for _, m, k, n, _ in ops)
     config = {"workload": args.workload, "scheme": scheme, "shapes": [[m, k, n] for _, m, k, n, _ in ops]}

@@ -110,6 +110,28 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
                 int64_t M, int64_t K, int64_t N,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same linear for activations that are ALREADY e4m3 (xq: u8 [M][K], rows K bytes apart, quantised with
+ * *input_scale by fp8lin_rmsnorm_quant, fp8lin_quantize_activation or a producer of the caller's): no quantiser pass,
+ * every M takes a tcgen05 kernel.  The reference has no such entry (its quantiser is always inside the linear call,
+ * kernels/fp8.py:263-268 / csrc/w8a8_cutlass_kernel.cu:406-430); it is the second half of the RMSNorm fusion below.
+ * workspace: at least FP8LIN_WS_HEADER_BYTES. */
+int fp8lin_w8a8_preq(const void* xq, const void* w_nk, const float* w_scale, const float* input_scale,
+                     const void* bias, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* RMSNorm fused with the static activation quantiser: the producer of a W8A8 linear's input.  Replaces
+ * RMSNorm.rms_forward / add_rms_forward (nanovllm/layers/layernorm.py:17-41) followed by the quantiser of the linear
+ * that consumes the result (kernels/fp8.py:250-252).
+ *   v = x [+ residual] in fp32;  residual <- bf16(v) (in place, when residual is not NULL);
+ *   y = bf16( v * (1 / sqrt(mean(v^2) + eps)) * weight )   -- one rounding: the arithmetic of the reference's compiled
+ *                                                              methods, which keep the whole expression in fp32;
+ *   xq = e4m3(clamp(y / max(*input_scale, 1e-12), +-448)).
+ * x: bf16 [M][ldx]; residual: bf16 [M][ld_res] or NULL; weight: bf16 [H]; xq: u8 [M][H] (rows H bytes apart) or NULL;
+ * y: bf16 [M][ldy] or NULL (for consumers that need the bf16 tensor, e.g. a W8A16 linear); at least one of xq / y.
+ * H a multiple of 8, at most 8192.  One CTA per row; x is read once. */
+int fp8lin_rmsnorm_quant(const void* x, int64_t ldx, void* residual, int64_t ld_res, const void* weight, float eps,
+                         const float* input_scale, void* xq, void* y, int64_t ldy, int64_t M, int64_t H, void* stream);
+
 /* Row-parallel W8A8 linear with the reduction folded into the GEMM's stores (no counterpart in
  * the reference, which calls dist.all_reduce after the GEMM, nanovllm/layers/linear.py:258-262).
  * fp8lin_w8a8_scatter computes this rank's bf16 partial output and its epilogue TMA-stores every
@@ -230,6 +252,13 @@ int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const flo
                     const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
                     const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
                     int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream);
+/* The same block for activations that are already e4m3 (xq: u8 [M][H], rows H bytes apart, quantised with
+ * *gate_up_input_scale -- e.g. by fp8lin_rmsnorm_quant, the post-attention norm of the reference's decoder layer,
+ * nanovllm/models/qwen2.py:155-160): no quantiser pass in front of the gate_up GEMM.  Same scratch. */
+int fp8lin_mlp_w8a8_preq(const void* xq, const void* w_gate_up, const float* gate_up_scale,
+                         const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
+                         const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
+                         int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Which kernel variant a shape is routed to ("stream_mma_w8a8_m16", "umma_w8a8_128x256", ...),
  * for labelling bench rows and ncu captures.  Host-only, returns a static string. */
@@ -237,7 +266,8 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);
 
 /* Bench/ncu studies only: force a tuning knob (value < 0 restores the default).  Not thread safe.
  * Knobs: "stream_splits", "stream_max_m", "umma_bn", "umma_splits", "umma_pair" (CTA-pair GEMM on/off),
- * "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable", "w8a16_swap_min_m",
+ * "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable", "w8a16_swap_min_m", "fuse_quant" (1 = large-M W8A8 quantises most rows with warps of the GEMM
+ * itself instead of a pass in front of it; n > 1 = the pass takes the first n rows), "quant_lead",
  * "w8a16_umma_min_m" (rows from which W8A16 takes the f16 GEMM route; 0 = never), "w8a16_chunk_mb", "pdl". */
 int fp8lin_set_tuning(const char* knob, int value);
 

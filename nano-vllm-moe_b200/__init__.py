@@ -26,9 +26,10 @@ from .layers.linear import (  # noqa: F401
 )
 
 from .layers.mlp import FusedFp8MLP  # noqa: F401,E402
+from .layers.layernorm import QuantizedActivation, RMSNorm  # noqa: F401,E402
 
 __all__ = [
-    "FusedFp8MLP",
+    "FusedFp8MLP", "RMSNorm", "QuantizedActivation",
     "Fp8Config", "Fp8LinearMethod", "QuantizationConfig", "QuantizeMethodBase", "get_quant_config",
     "is_fp8_config", "process_weights_after_loading", "LinearBase", "ReplicatedLinear", "ColumnParallelLinear",
     "MergedColumnParallelLinear", "QKVParallelLinear", "RowParallelLinear",

@@ -31,6 +31,10 @@ SIGNATURES = {
                              c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "fp8lin_w8a8": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                             c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+    "fp8lin_w8a8_preq": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                 c_void_p, c_size_t, c_void_p]),
+    "fp8lin_rmsnorm_quant": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, ctypes.c_float, c_void_p, c_void_p, c_void_p,
+                                     c_int64, c_int64, c_int64, c_void_p]),
     "fp8lin_w8a8_scatter": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p),
                                     c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "fp8lin_quantize_weight": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
@@ -38,6 +42,8 @@ SIGNATURES = {
     "fp8lin_mlp_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
     "fp8lin_mlp_w8a8": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+    "fp8lin_mlp_w8a8_preq": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "fp8lin_sum_slots": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "fp8lin_linear_static_scratch": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int64, c_int64, c_int64, c_int64, c_void_p]),

@@ -496,10 +496,10 @@ size_t fp8lin_mlp_workspace_bytes(int64_t M, int64_t H, int64_t I, int64_t N) {
     return FP8LIN_WS_HEADER_BYTES + mlp_layout(M, H, I).total;
 }
 
-int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const float* gate_up_scale,
-                    const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
-                    const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
-                    int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+static int mlp_w8a8_impl(const void* x, int64_t ldx, bool x_is_e4m3, const void* w_gate_up, const float* gate_up_scale,
+                         const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
+                         const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
+                         int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
     if (I <= 0 || I % 128 != 0) return fail(FP8LIN_ERR_SHAPE, "the intermediate size must be a positive multiple of 128 (got %lld)", (long long)I);
     int rc = validate_common(x, ldx, w_gate_up, gate_up_scale, gate_up_bias, y, 2 * I, M, H, 2 * I);   // (its output is internal)
     if (rc != FP8LIN_OK) return rc;
@@ -516,25 +516,83 @@ int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const flo
     if (M <= kDefaultStreamMaxM) {
         // small batches: gate_up through the decode kernels into a bf16 buffer, one pass for silu * up + quantise
         __nv_bfloat16* gu = (__nv_bfloat16*)(ws.body + l.gu_off);
-        rc = fp8lin_w8a8(x, ldx, w_gate_up, gate_up_scale, gate_up_input_scale, gate_up_bias, gu, 2 * I, M, H, 2 * I, workspace,
-                         FP8LIN_WS_HEADER_BYTES + l.inner, stream);
+        if (x_is_e4m3) {
+            WsView inner = ws_view(workspace, FP8LIN_WS_HEADER_BYTES + l.inner);
+            rc = run_w8a8_prequantised((const unsigned char*)x, w_gate_up, gate_up_scale, gate_up_input_scale, gate_up_bias, gu, 2 * I,
+                                       M, H, 2 * I, inner, st);
+        } else {
+            rc = fp8lin_w8a8(x, ldx, w_gate_up, gate_up_scale, gate_up_input_scale, gate_up_bias, gu, 2 * I, M, H, 2 * I, workspace,
+                             FP8LIN_WS_HEADER_BYTES + l.inner, stream);
+        }
         if (rc != FP8LIN_OK) return rc;
         cudaError_t e = launch_silu_mul_quant_interleaved(gu, down_input_scale, hq, M, I, st);
         if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "silu-multiply pass launch: %s", cudaGetErrorString(e));
     } else {
-        unsigned char* xq = ws.body;
+        unsigned char* xq = x_is_e4m3 ? (unsigned char*)const_cast<void*>(x) : ws.body;
         UmmaArgs a;
         a.xq = xq; a.w = (const unsigned char*)w_gate_up; a.w_scale = gate_up_scale; a.input_scale = gate_up_input_scale;
         a.bias = (const __nv_bfloat16*)gate_up_bias; a.y = nullptr; a.partial = nullptr; a.counters = ws.counters;
         a.status = ws.status; a.M = (int)M; a.K = (int)H; a.N = (int)(2 * I); a.ldy = 0;
-        rc = start_quant(x, ldx, gate_up_input_scale, xq, M, H, prequant_rows(M, (2 * I + 255) / 256, 256, sm_count() / 2), ws, a, st,
-                         (2 * I + 255) / 256, 256, sm_count() / 2);
-        if (rc != FP8LIN_OK) return rc;
+        if (!x_is_e4m3) {
+            rc = start_quant(x, ldx, gate_up_input_scale, xq, M, H, prequant_rows(M, (2 * I + 255) / 256, 256, sm_count() / 2), ws, a, st,
+                             (2 * I + 255) / 256, 256, sm_count() / 2);
+            if (rc != FP8LIN_OK) return rc;
+        }
         const char* why = nullptr;
         cudaError_t e = launch_umma_pair_mlp(a, hq, down_input_scale, st, &why);
         if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "fused gate_up launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     }
     return run_w8a8_prequantised(hq, w_down, down_scale, down_input_scale, down_bias, y, ldy, M, I, N, ws, st);
+}
+
+int fp8lin_w8a8_preq(const void* xq, const void* w_nk, const float* w_scale, const float* input_scale, const void* bias,
+                     void* y, int64_t ldy, int64_t M, int64_t K, int64_t N, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+    int rc = validate_common(xq, K, w_nk, w_scale, bias, y, ldy, M, K, N);      // (xq rows are K bytes apart)
+    if (rc != FP8LIN_OK || M == 0) return rc;
+    if (!input_scale) return fail(FP8LIN_ERR_NULL, "input_scale must not be NULL");
+    if (N % 8 != 0 || ldy % 8 != 0 || !aligned16(y)) return fail(FP8LIN_ERR_ALIGN, "N and ldy must be multiples of 8 and y 16-byte aligned");
+    if (!workspace || workspace_bytes < FP8LIN_WS_HEADER_BYTES)
+        return fail(FP8LIN_ERR_WORKSPACE, "workspace (at least the %d-byte header) is required", FP8LIN_WS_HEADER_BYTES);
+    return run_w8a8_prequantised((const unsigned char*)xq, w_nk, w_scale, input_scale, bias, y, ldy, M, K, N,
+                                 ws_view(workspace, workspace_bytes), (cudaStream_t)stream);
+}
+
+int fp8lin_rmsnorm_quant(const void* x, int64_t ldx, void* residual, int64_t ld_res, const void* weight, float eps,
+                         const float* input_scale, void* xq, void* y, int64_t ldy, int64_t M, int64_t H, void* stream) {
+    if (M < 0 || H <= 0 || H % 8 != 0 || H > 8192)
+        return fail(FP8LIN_ERR_SHAPE, "bad shape M=%lld H=%lld (H a multiple of 8, at most 8192)", (long long)M, (long long)H);
+    if (M == 0) return FP8LIN_OK;
+    if (!x || !weight || (!xq && !y)) return fail(FP8LIN_ERR_NULL, "x, weight and at least one of xq / y must not be NULL");
+    if (xq && !input_scale) return fail(FP8LIN_ERR_NULL, "input_scale is required when xq is asked for");
+    if (ldx < H || (residual && ld_res < H) || (y && ldy < H)) return fail(FP8LIN_ERR_SHAPE, "a row stride is smaller than H");
+    if (ldx % 8 != 0 || (residual && ld_res % 8 != 0) || (y && ldy % 8 != 0))
+        return fail(FP8LIN_ERR_ALIGN, "row strides must be multiples of 8 elements");
+    if (!aligned16(x) || !aligned16(weight) || (residual && !aligned16(residual)) || (y && !aligned16(y)) ||
+        (xq && (reinterpret_cast<uintptr_t>(xq) & 7) != 0))
+        return fail(FP8LIN_ERR_ALIGN, "x, residual, weight and y must be 16-byte aligned, xq 8-byte aligned");
+    if (!(eps >= 0.f)) return fail(FP8LIN_ERR_ARG, "eps must not be negative");
+    if (!check_arch()) return fail(FP8LIN_ERR_ARCH, "fp8lin kernels are built for sm_100a only");
+    cudaError_t e = launch_rmsnorm_quant((const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)residual, ld_res, (const __nv_bfloat16*)weight,
+                                         eps, input_scale, (unsigned char*)xq, (__nv_bfloat16*)y, ldy, M, H, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "RMSNorm launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+int fp8lin_mlp_w8a8(const void* x, int64_t ldx, const void* w_gate_up, const float* gate_up_scale,
+                    const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
+                    const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
+                    int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    return mlp_w8a8_impl(x, ldx, false, w_gate_up, gate_up_scale, gate_up_input_scale, gate_up_bias, w_down, down_scale,
+                         down_input_scale, down_bias, y, ldy, M, H, I, N, workspace, workspace_bytes, stream);
+}
+
+int fp8lin_mlp_w8a8_preq(const void* xq, const void* w_gate_up, const float* gate_up_scale,
+                         const float* gate_up_input_scale, const void* gate_up_bias, const void* w_down,
+                         const float* down_scale, const float* down_input_scale, const void* down_bias, void* y, int64_t ldy,
+                         int64_t M, int64_t H, int64_t I, int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    return mlp_w8a8_impl(xq, (H + 7) / 8 * 8, true, w_gate_up, gate_up_scale, gate_up_input_scale, gate_up_bias, w_down, down_scale,
+                         down_input_scale, down_bias, y, ldy, M, H, I, N, workspace, workspace_bytes, stream);
 }
 
 int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, void* y, int64_t ldy,

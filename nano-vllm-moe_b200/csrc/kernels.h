@@ -67,6 +67,12 @@ cudaError_t launch_abs_max(const __nv_bfloat16* x, int64_t ldx, int64_t M, int64
 cudaError_t launch_pack_tiles(const unsigned char* src, unsigned char* dst, int64_t K, int64_t N, bool src_is_kn,
                               cudaStream_t stream);
 
+// RMSNorm (+ residual add) fused with the static activation quantiser (rmsnorm_quant.cu).  residual (in/out), xq and y
+// may each be nullptr; H <= 8192, a multiple of 8.
+cudaError_t launch_rmsnorm_quant(const __nv_bfloat16* x, int64_t ldx, __nv_bfloat16* residual, int64_t ld_res,
+                                 const __nv_bfloat16* weight, float eps, const float* input_scale, unsigned char* xq,
+                                 __nv_bfloat16* y, int64_t ldy, int64_t M, int64_t H, cudaStream_t stream);
+
 // ---- tcgen05 GEMM (umma_gemm.cu) ---------------------------------------------
 struct UmmaArgs {
     const unsigned char* xq;     // [M][K] e4m3, contiguous (produced by launch_act_quant)

@@ -47,7 +47,11 @@ class FusedFp8MLP(nn.Module):
         if release_unfused:
             gate_up_proj.qweight_packed = torch.empty((0,), dtype=torch.uint8, device=w.device)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x) -> torch.Tensor:
+        """``x``: bfloat16 [.., H], or a ``QuantizedActivation`` made with gate_up_proj's input scale."""
+        codes = getattr(x, "codes", None)
+        if codes is not None:
+            x = codes
         if not x.is_cuda:
             raise RuntimeError("FP8 W8A8 static requires CUDA")
         down = self.down_proj

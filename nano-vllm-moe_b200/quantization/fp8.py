@@ -149,6 +149,21 @@ class Fp8LinearMethod(QuantizeMethodBase):
         """``out`` (optional, bf16 [M, N], row stride a multiple of 8) receives the result in place;
         the row-parallel layer uses it to compute M in chunks into one buffer."""
         backend = getattr(layer, "_fp8_backend", None)
+        codes = getattr(x, "codes", None)
+        if codes is not None:
+            # activations already quantised by the producer (layers/layernorm.py RMSNorm.forward_quant)
+            if not self.is_w8a8:
+                raise ValueError("pre-quantised activations need the fp8_w8a8_static scheme")
+            if backend is None:
+                raise RuntimeError("FP8 backend is not initialized: call process_weights_after_loading first")
+            if (x.scale.data_ptr() != layer.input_scale.data_ptr() and not torch.cuda.is_current_stream_capturing()
+                    and not torch.equal(x.scale.reshape(()), layer.input_scale.reshape(()))):
+                raise ValueError("the activations were quantised with a scale other than this layer's input_scale")
+            if bias is not None and bias.dtype != torch.bfloat16:
+                bias = bias.to(torch.bfloat16)
+            y = kernels.launch_w8a8_preq(codes.reshape(-1, codes.shape[-1]), layer.qweight_packed, layer.input_scale,
+                                         layer.weight_scale, bias, out=out)
+            return out if out is not None else y.view(*codes.shape[:-1], y.shape[-1])
         if not x.is_cuda:
             scheme = "FP8 W8A8 static" if self.is_w8a8 else "FP8 W8A16"
             raise RuntimeError(f"{scheme} requires CUDA")

@@ -185,6 +185,60 @@ def launch_w8a8_gemm(x: torch.Tensor, w_packed: torch.Tensor, input_scale: torch
     return y
 
 
+def launch_w8a8_preq(xq: torch.Tensor, w_packed: torch.Tensor, input_scale: torch.Tensor, weight_scale: torch.Tensor,
+                     bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """W8A8 linear on activations that are already e4m3 codes (uint8 [M, K], contiguous), e.g. from
+    ``rmsnorm_quant``: no quantiser pass."""
+    _require_cuda(xq, w_packed, weight_scale, input_scale, bias)
+    if xq.dtype != torch.uint8 or xq.dim() != 2 or not xq.is_contiguous():
+        raise ValueError("xq must be a contiguous 2-D uint8 tensor of e4m3 codes [M, K]")
+    m, k = xq.shape
+    n = weight_scale.numel()
+    if k % 16 != 0 or w_packed.numel() != packed_bytes(k, n):
+        raise ValueError(f"xq has K={k}, weight_scale has N={n}, but the packed weight holds {w_packed.numel()} bytes")
+    y = out if out is not None else torch.empty((m, n), dtype=torch.bfloat16, device=xq.device)
+    with torch.cuda.device(xq.device):
+        ws = workspace(xq.device, workspace_bytes(_lib.W8A8_STATIC, m, k, n))
+        rc = _lib.load().fp8lin_w8a8_preq(
+            xq.data_ptr(), w_packed.data_ptr(), weight_scale.data_ptr(), input_scale.data_ptr(),
+            bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0), m, k, n,
+            ws.data_ptr(), ws.numel(), _stream_ptr(xq.device))
+    _lib.raise_for(rc, "fp8lin_w8a8_preq")
+    return y
+
+
+def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, input_scale: torch.Tensor | None = None,
+                  residual: torch.Tensor | None = None, want_bf16: bool = False,
+                  xq_out: torch.Tensor | None = None, y_out: torch.Tensor | None = None):
+    """RMSNorm (with ``residual``: of x + residual, and ``residual`` is overwritten in place with bf16(x + residual),
+    the stream the next layer adds to) fused with the static activation quantiser.
+    Returns (xq or None, y or None): e4m3 codes [M, H] when ``input_scale`` is given, the bf16 result when
+    ``want_bf16`` (or when there is no ``input_scale``)."""
+    _require_cuda(x, weight, input_scale, residual)
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise ValueError("x must be a 2-D bfloat16 tensor and weight a bfloat16 vector")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    m, h = x.shape
+    if weight.numel() != h or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous vector of H elements")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != torch.bfloat16 or residual.stride(1) != 1):
+        raise ValueError("residual must be a bfloat16 tensor of x's shape with contiguous rows (it is updated in place)")
+    xq = y = None
+    if input_scale is not None:
+        xq = xq_out if xq_out is not None else torch.empty((m, h), dtype=torch.uint8, device=x.device)
+    if want_bf16 or input_scale is None:
+        y = y_out if y_out is not None else torch.empty((m, h), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().fp8lin_rmsnorm_quant(
+            x.data_ptr(), x.stride(0), residual.data_ptr() if residual is not None else None,
+            residual.stride(0) if residual is not None else 0, weight.data_ptr(), float(eps),
+            input_scale.data_ptr() if input_scale is not None else None, xq.data_ptr() if xq is not None else None,
+            y.data_ptr() if y is not None else None, y.stride(0) if y is not None else 0, m, h, _stream_ptr(x.device))
+    _lib.raise_for(rc, "fp8lin_rmsnorm_quant")
+    return xq, y
+
+
 def quantize_activation(x: torch.Tensor, input_scale: torch.Tensor) -> torch.Tensor:
     """bf16 [M, K] -> e4m3 codes (uint8) with one static scale."""
     _require_cuda(x, input_scale)
@@ -246,8 +300,17 @@ def launch_mlp_w8a8(x: torch.Tensor, w_gate_up_il: torch.Tensor, gate_up_scale_i
                     down_scale: torch.Tensor, down_input_scale: torch.Tensor, down_bias: torch.Tensor | None,
                     out: torch.Tensor | None = None) -> torch.Tensor:
     """bf16 ``down(silu(gate(x)) * up(x))`` with both projections W8A8-static; operands as produced by
-    ``interleave_gate_up`` (gate_up) and ``pack_weight_nk`` / ``prepack_weight`` (down)."""
-    x, n2, h = _check_linear_args(x, w_gate_up_il, gate_up_scale_il, gate_up_bias_il)
+    ``interleave_gate_up`` (gate_up) and ``pack_weight_nk`` / ``prepack_weight`` (down).  ``x`` is bfloat16
+    [M, H], or uint8 [M, H] e4m3 codes already quantised with ``gate_up_input_scale`` (``rmsnorm_quant``)."""
+    preq = x.dtype == torch.uint8
+    if preq:
+        if x.dim() != 2 or not x.is_contiguous() or not x.is_cuda:
+            raise ValueError("pre-quantised activations must be a contiguous 2-D uint8 CUDA tensor")
+        n2, h = gate_up_scale_il.numel(), x.shape[1]
+        if h % 16 or w_gate_up_il.numel() != packed_bytes(h, n2):
+            raise ValueError("the packed gate_up weight does not match the activations' width")
+    else:
+        x, n2, h = _check_linear_args(x, w_gate_up_il, gate_up_scale_il, gate_up_bias_il)
     inter = n2 // 2
     n = down_scale.numel()
     _require_cuda(w_down, down_scale, gate_up_input_scale, down_input_scale)
@@ -260,6 +323,14 @@ def launch_mlp_w8a8(x: torch.Tensor, w_gate_up_il: torch.Tensor, gate_up_scale_i
     with torch.cuda.device(x.device):
         lib = _lib.load()
         ws = workspace(x.device, lib.fp8lin_mlp_workspace_bytes(m, h, inter, n))
+        if preq:
+            rc = lib.fp8lin_mlp_w8a8_preq(
+                x.data_ptr(), w_gate_up_il.data_ptr(), gate_up_scale_il.data_ptr(), gate_up_input_scale.data_ptr(),
+                gate_up_bias_il.data_ptr() if gate_up_bias_il is not None else None, w_down.data_ptr(), down_scale.data_ptr(),
+                down_input_scale.data_ptr(), down_bias.data_ptr() if down_bias is not None else None, y.data_ptr(), y.stride(0),
+                m, h, inter, n, ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
+            _lib.raise_for(rc, "fp8lin_mlp_w8a8_preq")
+            return y
         rc = lib.fp8lin_mlp_w8a8(
             x.data_ptr(), x.stride(0), w_gate_up_il.data_ptr(), gate_up_scale_il.data_ptr(), gate_up_input_scale.data_ptr(),
             gate_up_bias_il.data_ptr() if gate_up_bias_il is not None else None, w_down.data_ptr(), down_scale.data_ptr(),

@@ -185,8 +185,14 @@ def linear_w8a8(x, wq_nk, w_scale, input_scale, bias=None, *, exact=True, round_
     them into one per-tensor scale at load, fp8.py:100-105; see
     ``requantize_per_tensor`` for that variant).
     """
+    return linear_w8a8_preq(quantize_activation(x, input_scale), wq_nk, w_scale, input_scale, bias, exact=exact,
+                            round_out=round_out)
+
+
+def linear_w8a8_preq(xq_codes, wq_nk, w_scale, input_scale, bias=None, *, exact=True, round_out=True):
+    """The W8A8 linear from activations that are already e4m3 codes (the same epilogue algebra)."""
     s = np.maximum(np.float32(input_scale), np.float32(1e-12)).astype(np.float32)
-    xq = e4m3_decode(quantize_activation(x, input_scale))
+    xq = e4m3_decode(xq_codes)
     acc = _matmul_nt(xq, e4m3_decode(wq_nk), exact)
     y = (acc * s).astype(np.float32) * np.asarray(w_scale, np.float32)[None, :]
     if bias is not None:
