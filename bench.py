@@ -912,9 +912,10 @@ def main():
     ap.add_argument("--ep-dispatch", choices=["fixed", "dynamic"], default="fixed",
                     help="MoE workloads on N > 1 ranks: fixed-capacity all-to-all (graph-capturable) or the "
                          "reference's variable-split exchange with host-side counts")
-    ap.add_argument("--peer-reduce", choices=["auto", "on", "off"], default="auto",
-                    help="row-parallel layers: reduce through peer-memory stores in the GEMM epilogue (on), "
-                         "NCCL all-reduce after the GEMM (off), or by shape (auto, the layer default)")
+    ap.add_argument("--peer-reduce", choices=["auto", "on", "off", "rs"], default="auto",
+                    help="row-parallel layers: every rank's epilogue stores its partial into every rank (on), reduce-scatter "
+                         "in the epilogue + sum + all-gather by peer stores (rs), NCCL all-reduce after the GEMM (off), or "
+                         "by shape and rank count (auto, the layer default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -974,7 +975,7 @@ def main():
             lay.bias.weight_loader(lay.bias, bias)
             pkg.process_weights_after_loading(lay)
             if kind == "row" and args.peer_reduce != "auto":
-                lay.peer_reduce = args.peer_reduce == "on"
+                lay.peer_reduce = {"on": True, "off": False, "rs": "rs"}[args.peer_reduce]
             row.append(lay)
             if c == 0:
                 xl = x if (kind == "col" or tp == 1) else x[:, rank * (k // tp):(rank + 1) * (k // tp)].contiguous()
@@ -1010,12 +1011,13 @@ def main():
             nl = n // tp if (kind == "col" and tp > 1) else n
             # every rank checks its own column shard; the reduced row-parallel output is the same on all ranks,
             # rank i % tp checks layer i
+            checked.append(f"{label}:{kind}:{len(ref['rows'])}rows:{tp if (kind == 'row' and tp > 1) else 1}ulp:"
+                           + (f"rank{i % tp}" if (kind == "row" and tp > 1) else ("every rank's shard" if tp > 1 else "rank0")))
             if kind == "row" and tp > 1 and (i % tp) != rank:
                 continue
             y_rows = outs0[i][ref["rows"].to(dev)]
             ratio, cos, ulps = sampled_parity(scheme, ref, y_rows, slice(None), tp, kind, rank, slice(rank * nl, (rank + 1) * nl))
             worst, min_cos = max(worst, ratio), min(min_cos, cos)
-            checked.append(f"{label}:{kind}:{len(ref['rows'])}rows:{ulps:g}ulp")
         if world > 1:
             t = torch.tensor([worst, -min_cos], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -146,6 +146,21 @@ int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const floa
                         void* workspace, size_t workspace_bytes, void* stream);
 int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, void* y,
                      int64_t ldy, int64_t M, int64_t N, void* stream);
+/* The same reduction in reduce-scatter / all-gather form, for more than two ranks (the store-to-everyone form above
+ * sends (ranks - 1) x the payload per rank; this one 2 x (ranks - 1) / ranks).  fp8lin_w8a8_reduce_scatter computes
+ * this rank's partial output and stores the rows of band d = [d * band_rows, (d + 1) * band_rows) ONLY to
+ * dst_ptrs[d] (bf16 [band_rows][ld_dst]: this rank's slot in rank d's buffer), from that matrix's row 0 on;
+ * band_rows a multiple of 32 with band_rows * n_dst >= M.  After a cross-rank barrier every rank owns all ranks'
+ * partials of its band; fp8lin_sum_slots_gather adds them (fp32, slot order, one rounding) and stores the reduced
+ * band at rows [dst_row, dst_row + M) of EVERY matrix in dst_ptrs (HOST array of n_dst device pointers to the ranks'
+ * bf16 [..][ld_dst] outputs; plain 16-byte stores, peers over NVLink).  A second barrier, and every rank holds the
+ * whole reduced result -- or skip the gather and keep the result sharded by rows. */
+int fp8lin_w8a8_reduce_scatter(const void* x, int64_t ldx, const void* w_nk, const float* w_scale,
+                               const float* input_scale, const void* bias, int n_dst, void* const* dst_ptrs,
+                               int64_t ld_dst, int64_t band_rows, int64_t M, int64_t K, int64_t N,
+                               void* workspace, size_t workspace_bytes, void* stream);
+int fp8lin_sum_slots_gather(const void* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, int n_dst,
+                            void* const* dst_ptrs, int64_t ld_dst, int64_t dst_row, int64_t M, int64_t N, void* stream);
 
 /* Decode-sized linear (M <= 64, either scheme) that needs no workspace from the
  * caller and allocates nothing.  It has no counterpart in the reference; it

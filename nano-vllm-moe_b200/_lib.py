@@ -37,6 +37,10 @@ SIGNATURES = {
                                      c_int64, c_int64, c_int64, c_void_p]),
     "fp8lin_w8a8_scatter": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p),
                                     c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+    "fp8lin_w8a8_reduce_scatter": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p),
+                                           c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+    "fp8lin_sum_slots_gather": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, POINTER(c_void_p), c_int64, c_int64, c_int64,
+                                        c_int64, c_void_p]),
     "fp8lin_quantize_weight": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "fp8lin_abs_max": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "fp8lin_mlp_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),

@@ -414,9 +414,9 @@ int fp8lin_w8a8(const void* x, int64_t ldx, const void* w_nk, const float* w_sca
     return FP8LIN_OK;
 }
 
-int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const float* w_scale, const float* input_scale,
-                        const void* bias, int n_dst, void* const* dst_ptrs, int64_t ld_dst, int64_t M, int64_t K, int64_t N,
-                        void* workspace, size_t workspace_bytes, void* stream) {
+static int w8a8_to_destinations(const void* x, int64_t ldx, const void* w_nk, const float* w_scale, const float* input_scale,
+                                const void* bias, int n_dst, void* const* dst_ptrs, int64_t ld_dst, int64_t band_rows, int64_t M,
+                                int64_t K, int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
     if (n_dst < 1 || n_dst > 8 || !dst_ptrs) return fail(FP8LIN_ERR_ARG, "n_dst must be 1..8 and dst_ptrs non-NULL");
     for (int d = 0; d < n_dst; ++d)
         if (!dst_ptrs[d] || !aligned16(dst_ptrs[d])) return fail(FP8LIN_ERR_ALIGN, "destination %d is NULL or not 16-byte aligned", d);
@@ -424,8 +424,10 @@ int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const floa
     if (rc != FP8LIN_OK || M == 0) return rc;
     if (!input_scale) return fail(FP8LIN_ERR_NULL, "input_scale must not be NULL");
     if (N % 8 != 0 || ld_dst % 8 != 0) return fail(FP8LIN_ERR_SHAPE, "N and ld_dst must be multiples of 8");
+    if (band_rows != 0 && (band_rows < 32 || band_rows % 32 != 0 || band_rows * n_dst < M))
+        return fail(FP8LIN_ERR_SHAPE, "band_rows=%lld must be a multiple of 32 with band_rows * n_dst >= M", (long long)band_rows);
     cudaStream_t st = (cudaStream_t)stream;
-    UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, 1);      // the scatter epilogue exists in the non-split kernel only
+    UmmaPlan pl = plan_umma(M, K, N, g_tune.umma_bn, 1);      // the multi-destination epilogue exists in the non-split kernels only
     pl.tail_tiles = 0;
     WsView ws = ws_view(workspace, workspace_bytes);
     const size_t xq_bytes = align_up((size_t)M * K, 256);
@@ -435,13 +437,32 @@ int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const floa
     a.xq = ws.body; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = input_scale;
     a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)dst_ptrs[0]; a.partial = nullptr; a.counters = ws.counters;
     a.status = ws.status; a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldy = (int)ld_dst;
-    rc = start_quant(x, ldx, input_scale, ws.body, M, K, prequant_rows(M, pl.n_tiles, 128, sm_count()), ws, a, st, pl.n_tiles, 128,
-                     sm_count());
+    const bool pair = pair_eligible(M, N);
+    rc = pair ? start_quant(x, ldx, input_scale, ws.body, M, K, prequant_rows(M, (N + 255) / 256, 256, sm_count() / 2), ws, a, st,
+                            (N + 255) / 256, 256, sm_count() / 2)
+              : start_quant(x, ldx, input_scale, ws.body, M, K, prequant_rows(M, pl.n_tiles, 128, sm_count()), ws, a, st, pl.n_tiles, 128,
+                            sm_count());
     if (rc != FP8LIN_OK) return rc;
     const char* why = nullptr;
-    cudaError_t e = launch_umma_w8a8(pl, a, st, &why, n_dst, dst_ptrs, ld_dst);
+    cudaError_t e = pair ? launch_umma_pair(false, a, st, &why, n_dst, dst_ptrs, ld_dst, band_rows)
+                         : launch_umma_w8a8(pl, a, st, &why, n_dst, dst_ptrs, ld_dst, band_rows);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "tcgen05 GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
     return FP8LIN_OK;
+}
+
+int fp8lin_w8a8_scatter(const void* x, int64_t ldx, const void* w_nk, const float* w_scale, const float* input_scale,
+                        const void* bias, int n_dst, void* const* dst_ptrs, int64_t ld_dst, int64_t M, int64_t K, int64_t N,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+    return w8a8_to_destinations(x, ldx, w_nk, w_scale, input_scale, bias, n_dst, dst_ptrs, ld_dst, 0, M, K, N, workspace,
+                                workspace_bytes, stream);
+}
+
+int fp8lin_w8a8_reduce_scatter(const void* x, int64_t ldx, const void* w_nk, const float* w_scale, const float* input_scale,
+                               const void* bias, int n_dst, void* const* dst_ptrs, int64_t ld_dst, int64_t band_rows, int64_t M,
+                               int64_t K, int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    if (band_rows <= 0) return fail(FP8LIN_ERR_SHAPE, "band_rows must be positive");
+    return w8a8_to_destinations(x, ldx, w_nk, w_scale, input_scale, bias, n_dst, dst_ptrs, ld_dst, band_rows, M, K, N, workspace,
+                                workspace_bytes, stream);
 }
 
 // ---- fused MLP: y = down( silu(gate(x)) * up(x) ), both projections W8A8-static -----------------------
@@ -604,6 +625,25 @@ int fp8lin_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int64_
     if (!aligned16(slots) || !aligned16(y)) return fail(FP8LIN_ERR_ALIGN, "slots and y must be 16-byte aligned");
     cudaError_t e = launch_sum_slots((const __nv_bfloat16*)slots, n_slots, slot_stride, (__nv_bfloat16*)y, ldy, M, N, ld_slot,
                                      (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "slot sum launch: %s", cudaGetErrorString(e));
+    return FP8LIN_OK;
+}
+
+int fp8lin_sum_slots_gather(const void* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, int n_dst, void* const* dst_ptrs,
+                            int64_t ld_dst, int64_t dst_row, int64_t M, int64_t N, void* stream) {
+    if (n_slots < 1 || M < 0 || N <= 0 || N % 8 != 0 || ld_slot % 8 != 0 || ld_dst % 8 != 0 || slot_stride % 8 != 0 || dst_row < 0)
+        return fail(FP8LIN_ERR_SHAPE, "bad shape: N, ld_slot, ld_dst and slot_stride must be multiples of 8");
+    if (n_dst < 1 || n_dst > 8 || !dst_ptrs) return fail(FP8LIN_ERR_ARG, "n_dst must be 1..8 and dst_ptrs non-NULL");
+    if (M == 0) return FP8LIN_OK;
+    if (!slots || !aligned16(slots)) return fail(FP8LIN_ERR_ALIGN, "slots must be non-NULL and 16-byte aligned");
+    SumDst dst;
+    dst.n = n_dst;
+    for (int d = 0; d < n_dst; ++d) {
+        if (!dst_ptrs[d] || !aligned16(dst_ptrs[d])) return fail(FP8LIN_ERR_ALIGN, "destination %d is NULL or not 16-byte aligned", d);
+        dst.y[d] = (__nv_bfloat16*)dst_ptrs[d] + dst_row * ld_dst;
+    }
+    cudaError_t e = launch_sum_slots_gather((const __nv_bfloat16*)slots, n_slots, slot_stride, ld_slot, dst, ld_dst, M, N,
+                                            (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "slot sum launch: %s", cudaGetErrorString(e));
     return FP8LIN_OK;
 }

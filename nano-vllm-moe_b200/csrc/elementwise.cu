@@ -81,6 +81,44 @@ cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t sl
     return counted(cudaGetLastError());
 }
 
+// The same sum, written to every destination: y_d[m][n] for d < dst.n.  The destinations are the output matrices of
+// all ranks of a row-parallel linear (this rank's own among them), so the reduced band reaches its peers by plain
+// 16-byte stores over NVLink while the slots are read from local memory.
+__global__ void __launch_bounds__(256)
+sum_slots_gather_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, int64_t slot_stride, int64_t ld_slot, SumDst dst,
+                        int64_t ld_dst, int64_t M, int64_t N) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t vec_per_row = N / 8;
+    const int64_t total = M * vec_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / vec_per_row;
+        const int64_t c = (i - m * vec_per_row) * 8;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < n_slots; ++r) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + r * slot_stride + m * ld_slot + c));
+            acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+            acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+#pragma unroll
+        for (int d = 0; d < 8; ++d)
+            if (d < dst.n) *reinterpret_cast<uint4*>(dst.y[d] + m * ld_dst + c) = o;
+    }
+}
+
+cudaError_t launch_sum_slots_gather(const __nv_bfloat16* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, SumDst dst,
+                                    int64_t ld_dst, int64_t M, int64_t N, cudaStream_t stream) {
+    const int64_t total = M * (N / 8);
+    if (total == 0) return cudaSuccess;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    sum_slots_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(slots, n_slots, slot_stride, ld_slot, dst, ld_dst, M, N);
+    return counted(cudaGetLastError());
+}
+
 // x (bf16, row pitch ldx) -> f16 [M][K] contiguous, round to nearest: the "A" operand of the
 // large-M W8A16 GEMM.  Eight elements per thread and iteration.
 __global__ void __launch_bounds__(256)

@@ -114,8 +114,10 @@ UmmaPlan plan_umma(int64_t M, int64_t K, int64_t N, int force_bn, int force_spli
 // Returns cudaSuccess or an error; `why` (optional) receives a static description.
 // n_dst == 0: the result goes to args.y.  n_dst >= 1 (non-split plans only): the epilogue stores every
 // output box to each of dst_ptrs[0..n_dst) (bf16 [M][ld_dst] matrices; may be peer-GPU memory).
+// band_rows > 0 (a multiple of 32): destination d receives only rows [d * band_rows, (d + 1) * band_rows) of the result,
+// stored from its row 0 on (dst_ptrs[d] is a bf16 [band_rows][ld_dst] matrix).
 cudaError_t launch_umma_w8a8(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why,
-                             int n_dst = 0, void* const* dst_ptrs = nullptr, int64_t ld_dst = 0);
+                             int n_dst = 0, void* const* dst_ptrs = nullptr, int64_t ld_dst = 0, int64_t band_rows = 0);
 // Large-M W8A16: the same GEMM on f16 operands.  args.xq = activations as f16 [M][K] (launch_x_to_f16),
 // args.w = f16 weight tiles of the channels [0, N) (launch_dequant_tiles_f16), args.input_scale = nullptr.
 cudaError_t launch_umma_f16(const UmmaPlan& plan, const UmmaArgs& args, cudaStream_t stream, const char** why);
@@ -124,7 +126,7 @@ cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_
 // The same GEMM on CTA pairs (umma_pair_gemm.cu): 256 x 256 tiles, one MMA across two CTAs.  f16 selects the
 // operand type as above; destinations as launch_umma_w8a8.
 cudaError_t launch_umma_pair(bool f16, const UmmaArgs& args, cudaStream_t stream, const char** why, int n_dst = 0,
-                             void* const* dst_ptrs = nullptr, int64_t ld_dst = 0);
+                             void* const* dst_ptrs = nullptr, int64_t ld_dst = 0, int64_t band_rows = 0);
 // Fused MLP pieces: gate_up GEMM whose epilogue writes e4m3 h = silu(g) * u for the down projection
 // (umma_pair_gemm.cu), and the separate pass that does the same from a bf16 gate_up result (small batches).
 cudaError_t launch_umma_pair_mlp(const UmmaArgs& args, unsigned char* hq, const float* h_scale, cudaStream_t stream,
@@ -137,6 +139,15 @@ cudaError_t launch_sum_slots(const __nv_bfloat16* slots, int n_slots, int64_t sl
 // A one-CTA launch whose only mbarrier is never arrived on: the bounded wait gives up after
 // `limit_cycles`, writes kDevTimeoutFull to *status (and 1 to *gave_up if given) and returns.
 cudaError_t launch_wait_timeout_probe(int* status, long long limit_cycles, int* gave_up, cudaStream_t stream);
+
+// The same sum written to several destinations (this rank's band of a row-parallel result stored into every rank's
+// output matrix by plain stores; peers over NVLink).
+struct SumDst {
+    __nv_bfloat16* y[8];
+    int n;
+};
+cudaError_t launch_sum_slots_gather(const __nv_bfloat16* slots, int n_slots, int64_t slot_stride, int64_t ld_slot, SumDst dst,
+                                    int64_t ld_dst, int64_t M, int64_t N, cudaStream_t stream);
 
 // ---- swapped-operand tcgen05 kernel for M <= 64 (umma_swap.cu) -------------------
 struct SwapPlan {

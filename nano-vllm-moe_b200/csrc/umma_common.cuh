@@ -348,6 +348,21 @@ __device__ __forceinline__ void quant_ctrl_release(const QuantJob& j, int M) {
 struct OutMaps {
     CUtensorMap m[8];
     int n;
+    // 0: every output box is stored to all n destinations.  > 0 (a multiple of 32): destination d receives only the
+    // rows [d * band_rows, (d + 1) * band_rows) of the result, at row (r - d * band_rows) of its matrix: the
+    // reduce-scatter form of a row-parallel linear, where rank d sums the bands it receives.
+    int band_rows;
 };
+
+// Store one staged 32-row box whose first row is `row0` of the result to its destination(s).
+__device__ __forceinline__ void store_box(const OutMaps& outs, uint32_t box, int col0, int row0) {
+    if (outs.band_rows > 0) {
+        const int d = row0 / outs.band_rows;
+        if (d < outs.n) tma_store_2d(&outs.m[d], box, col0, row0 - d * outs.band_rows);
+        else asm volatile("cp.async.bulk.commit_group;" ::: "memory");      // keep the group count per box uniform
+        return;
+    }
+    for (int d = 0; d < outs.n; ++d) tma_store_2d(&outs.m[d], box, col0, row0);
+}
 
 }  // namespace fp8lin

@@ -385,7 +385,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (h == 0 && lane == 0) {
                         // one store per destination: the local output, or (row-parallel scatter) this
                         // rank's slot in every rank's buffer, peers reached over NVLink
-                        for (int d = 0; d < outs.n; ++d) tma_store_2d(&outs.m[d], pbox, n0 + col, row0);
+                        store_box(outs, pbox, n0 + col, row0);
                     }
                 }
                 tc_fence_before();
@@ -453,7 +453,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (lane == 0) {
                         // one store per destination: the local output, or (row-parallel scatter) this
                         // rank's slot in every rank's buffer, peers reached over NVLink
-                        for (int d = 0; d < outs.n; ++d) tma_store_2d(&outs.m[d], box, n0 + col, row0);
+                        store_box(outs, box, n0 + col, row0);
                     }
                 }
             }
@@ -737,9 +737,10 @@ static cudaError_t launch_bn(const UmmaPlan& pl, const UmmaArgs& a, const CUtens
 }
 
 static cudaError_t launch_umma(bool f16, const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why,
-                               int n_dst, void* const* dst_ptrs, int64_t ld_dst) {
+                               int n_dst, void* const* dst_ptrs, int64_t ld_dst, int64_t band_rows = 0) {
     CUtensorMap ta, tb;
     OutMaps ty;
+    ty.band_rows = (int)band_rows;
     const uint32_t piece = pl.bn / 2 < 64 ? pl.bn / 2 : 64;      // UmmaCfg<BN>::kPiece
     const uint64_t esz = f16 ? 2 : 1;                            // the operand matrices are described in bytes
     bool ok = encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K * esz, kBM) &&
@@ -754,8 +755,14 @@ static cudaError_t launch_umma(bool f16, const UmmaPlan& pl, const UmmaArgs& a, 
             return cudaErrorInvalidValue;
         }
         ty.n = n_dst;
-        for (int d = 0; d < n_dst && ok; ++d)
-            ok = encode_out_2d(&ty.m[d], dst_ptrs[d], (uint64_t)a.M, (uint64_t)a.N, (uint64_t)ld_dst * 2, piece);
+        for (int d = 0; d < n_dst && ok; ++d) {
+            int64_t rows = a.M;
+            if (band_rows > 0) {          // destination d holds one band of rows (at least one row: a map cannot be empty)
+                rows = a.M - d * band_rows;
+                rows = rows > band_rows ? band_rows : (rows < 1 ? 1 : rows);
+            }
+            ok = encode_out_2d(&ty.m[d], dst_ptrs[d], (uint64_t)rows, (uint64_t)a.N, (uint64_t)ld_dst * 2, piece);
+        }
     }
     if (!ok) {
         if (why) *why = "cuTensorMapEncodeTiled failed";
@@ -798,8 +805,8 @@ static cudaError_t launch_umma(bool f16, const UmmaPlan& pl, const UmmaArgs& a, 
 }
 
 cudaError_t launch_umma_w8a8(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why,
-                             int n_dst, void* const* dst_ptrs, int64_t ld_dst) {
-    return launch_umma(false, pl, a, stream, why, n_dst, dst_ptrs, ld_dst);
+                             int n_dst, void* const* dst_ptrs, int64_t ld_dst, int64_t band_rows) {
+    return launch_umma(false, pl, a, stream, why, n_dst, dst_ptrs, ld_dst, band_rows);
 }
 
 cudaError_t launch_umma_f16(const UmmaPlan& pl, const UmmaArgs& a, cudaStream_t stream, const char** why) {

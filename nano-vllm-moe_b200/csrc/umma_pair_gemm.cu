@@ -334,7 +334,7 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 fence_async_smem();
                 asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
                 if (h == 0 && lane == 0) {
-                    for (int d = 0; d < outs.n; ++d) tma_store_2d(&outs.m[d], pbox, n0 + col, row0);
+                    store_box(outs, pbox, n0 + col, row0);
                 }
             }
             tc_fence_before();
@@ -402,9 +402,10 @@ cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensor
 }  // namespace
 
 cudaError_t launch_umma_pair(bool f16, const UmmaArgs& a, cudaStream_t stream, const char** why, int n_dst,
-                             void* const* dst_ptrs, int64_t ld_dst) {
+                             void* const* dst_ptrs, int64_t ld_dst, int64_t band_rows) {
     CUtensorMap ta, tb;
     OutMaps ty;
+    ty.band_rows = (int)band_rows;
     const uint64_t esz = f16 ? 2 : 1;                            // the operand matrices are described in bytes
     bool ok = encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K * esz, kBM) &&
               encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * esz * 128), 128, 128);
@@ -417,8 +418,14 @@ cudaError_t launch_umma_pair(bool f16, const UmmaArgs& a, cudaStream_t stream, c
             return cudaErrorInvalidValue;
         }
         ty.n = n_dst;
-        for (int d = 0; d < n_dst && ok; ++d)
-            ok = encode_out_2d(&ty.m[d], dst_ptrs[d], (uint64_t)a.M, (uint64_t)a.N, (uint64_t)ld_dst * 2, 64);
+        for (int d = 0; d < n_dst && ok; ++d) {
+            int64_t rows = a.M;
+            if (band_rows > 0) {
+                rows = a.M - d * band_rows;
+                rows = rows > band_rows ? band_rows : (rows < 1 ? 1 : rows);
+            }
+            ok = encode_out_2d(&ty.m[d], dst_ptrs[d], (uint64_t)rows, (uint64_t)a.N, (uint64_t)ld_dst * 2, 64);
+        }
     }
     if (!ok) {
         if (why) *why = "cuTensorMapEncodeTiled failed";
@@ -440,6 +447,7 @@ cudaError_t launch_umma_pair_mlp(const UmmaArgs& a, unsigned char* hq, const flo
     CUtensorMap ta, tb;
     OutMaps ty;
     ty.n = 1;
+    ty.band_rows = 0;
     const bool ok = encode_u8_2d(&ta, a.xq, (uint64_t)a.M, (uint64_t)a.K, kBM) &&
                     encode_u8_2d(&tb, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128, 128) &&
                     encode_u8_2d(&ty.m[0], hq, (uint64_t)a.M, (uint64_t)(a.N / 2), 32);

@@ -184,19 +184,83 @@ class RowParallelLinear(LinearBase):
     overlap_min_rows = None
     overlap_chunks = 4
 
-    # Fold the all-reduce into the GEMM: every rank's epilogue stores its bf16 partial tile straight
-    # into its slot of every rank's peer-mapped buffer (NVLink stores issued while the GEMM runs),
-    # a symmetric-memory barrier follows, and each rank adds the slots locally in rank order.
-    # Needs torch symmetric memory on the TP group.  "auto" takes this path when the local GEMM is
-    # long enough to hide the NVLink stores (measured on 2 B200s: K/tp = 9472 -> 216 vs 243 us at
-    # M = 4096 and 638 vs 792 us at M = 16384; K/tp = 1792 -> no gain), True forces it, False never.
+    # Fold the all-reduce into the GEMM through peer memory (torch symmetric memory on the TP group), two forms:
+    #  * reduce-scatter + all-gather ("rs", what "auto" takes from peer_reduce_min_rows rows and K/tp >= peer_rs_min_k):
+    #    the epilogue TMA-stores the rows of band r only into rank r's slot buffer while the GEMM runs; after a
+    #    symmetric-memory barrier rank r adds the tp partials of its band (fp32, rank order) and stores the reduced
+    #    band into every rank's output; a second barrier.  A rank sends 2 (tp - 1) / tp of the payload.
+    #    `reduce_results="scatter"` stops after the sum and returns this rank's band of rows only (for a caller that
+    #    continues row-sharded).  Measured on 2 B200s at M = 16384: o_proj (K/tp = 1792) 254 us against 363 us with the
+    #    NCCL all-reduce, down (K/tp = 9472) 679 us against 796 us.
+    #  * store-to-everyone (True): every rank's epilogue stores its whole partial into its slot of every rank's buffer,
+    #    one barrier, every rank sums locally.  (tp - 1) times the payload per rank: only sensible between two ranks
+    #    (down at M = 16384: 697 us).
+    # False = always the NCCL all-reduce, as the reference.
     peer_reduce = "auto"
     peer_reduce_min_rows = 512
     peer_reduce_min_k = 4096
+    peer_rs_min_k = 1024
 
-    def _use_peer_reduce(self, x: torch.Tensor, rows: int) -> bool:
+    def _use_peer_rs(self, x: torch.Tensor, rows: int) -> bool:
+        """Reduce-scatter + all-gather through peer memory (more than two ranks, or forced with peer_reduce = "rs")."""
         if self.peer_reduce is False or getattr(self, "_peer_failed", False):
             return False
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and getattr(self, "_fp8_backend", None) == "fp8lin_w8a8"):
+            return False
+        if self.output_size % 8:
+            return False
+        if self.peer_reduce == "rs" or self.reduce_results == "scatter":
+            wanted = True
+        elif self.peer_reduce == "auto":
+            wanted = rows >= self.peer_reduce_min_rows and self.input_size_per_partition >= self.peer_rs_min_k
+        else:
+            wanted = False                  # True = the store-to-everyone form at any number of ranks
+        return wanted and (getattr(self, "_rs_cap", 0) >= rows or not torch.cuda.is_current_stream_capturing())
+
+    def _rs_buffers(self, rows: int, device):
+        import torch.distributed._symmetric_memory as symm
+        cap = getattr(self, "_rs_cap", 0)
+        if cap < rows:
+            cap = max(rows, 2 * cap)
+            band = -(-(-(-cap // self.tp_size)) // 32) * 32             # rows per band, a multiple of 32
+            n = self.output_size
+            group = self.tp_group if self.tp_group is not None else dist.group.WORLD
+            # [tp slots of one band | the whole output]: peers store partial bands into the slots and reduced bands into the output
+            buf = symm.empty((self.tp_size * band + cap) * n, dtype=torch.bfloat16, device=device)
+            self._rs_handle = symm.rendezvous(buf, group)
+            self._rs_buf, self._rs_cap, self._rs_band_cap = buf, cap, band
+        return self._rs_buf, self._rs_handle
+
+    def _forward_peer_rs(self, x: torch.Tensor, bias, rows: int) -> torch.Tensor:
+        from ..quantization import kernels
+        x2 = x.reshape(rows, x.shape[-1])
+        buf, handle = self._rs_buffers(rows, x.device)
+        n, tp, rank = self.output_size, self.tp_size, self.tp_rank
+        band = -(-(-(-rows // tp)) // 32) * 32
+        band_cap = self._rs_band_cap
+        slot_elems = band_cap * n
+        y_off = tp * slot_elems                                  # element offset of the output inside the buffer
+        # the previous call's second barrier guarantees that every rank has summed its slots and read its output
+        dst = [int(handle.buffer_ptrs[r]) + rank * slot_elems * 2 for r in range(tp)]
+        kernels.launch_w8a8_reduce_scatter(x2, self.qweight_packed, self.input_scale, self.weight_scale, bias, dst, n, band)
+        handle.barrier(channel=0)                                # every rank's partial rows of my band have landed
+        mine = max(0, min(band, rows - rank * band))
+        if self.reduce_results == "scatter":
+            out = torch.empty((mine, n), dtype=torch.bfloat16, device=x.device)
+            kernels.sum_slots_gather(buf.data_ptr(), tp, slot_elems, n, [out.data_ptr()], n, 0, mine, n, x.device)
+            handle.barrier(channel=1)
+            return out
+        ys = [int(handle.buffer_ptrs[r]) + y_off * 2 for r in range(tp)]
+        kernels.sum_slots_gather(buf.data_ptr(), tp, slot_elems, n, ys, n, rank * band, mine, n, x.device)
+        handle.barrier(channel=1)                                # every band of the result is in place everywhere
+        y = buf[y_off:y_off + rows * n].view(rows, n)            # (valid until this layer's next call)
+        return y.view(*x.shape[:-1], n)
+
+    def _use_peer_reduce(self, x: torch.Tensor, rows: int) -> bool:
+        if self.peer_reduce is False or self.peer_reduce == "rs" or getattr(self, "_peer_failed", False):
+            return False
+        if self.peer_reduce == "auto" and self.tp_size > 2:
+            return False                    # store-to-everyone only pays between two ranks
         if not (x.is_cuda and x.dtype == torch.bfloat16 and getattr(self, "_fp8_backend", None) == "fp8lin_w8a8"):
             return False
         if rows < self.peer_reduce_min_rows or self.output_size % 8:
@@ -231,13 +295,15 @@ class RowParallelLinear(LinearBase):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         bias = self.bias if self.tp_rank == 0 else None
-        reduce = self.tp_size > 1 and self.reduce_results
+        reduce = self.tp_size > 1 and bool(self.reduce_results)
         rows = x.numel() // x.shape[-1] if x.dim() > 0 else 0
-        if reduce and self._use_peer_reduce(x, rows):
+        if reduce and (self._use_peer_rs(x, rows) or self._use_peer_reduce(x, rows)):
             try:
+                if self._use_peer_rs(x, rows):
+                    return self._forward_peer_rs(x, bias, rows)
                 return self._forward_peer_reduce(x, bias, rows)
             except (RuntimeError, ImportError, AttributeError) as exc:
-                if self.peer_reduce is True or getattr(self, "_peer_cap", 0) > 0:
+                if self.peer_reduce in (True, "rs") or getattr(self, "_peer_cap", 0) > 0 or getattr(self, "_rs_cap", 0) > 0:
                     raise
                 # symmetric memory is not available for this group (every rank fails alike in the
                 # collective rendezvous): remember it and use the all-reduce from now on

@@ -271,6 +271,33 @@ def launch_w8a8_scatter(x: torch.Tensor, w_packed: torch.Tensor, input_scale: to
     _lib.raise_for(rc, "fp8lin_w8a8_scatter")
 
 
+def launch_w8a8_reduce_scatter(x: torch.Tensor, w_packed: torch.Tensor, input_scale: torch.Tensor, weight_scale: torch.Tensor,
+                               bias: torch.Tensor | None, dst_ptrs: list[int], ld_dst: int, band_rows: int) -> None:
+    """This rank's partial output of a row-parallel linear, rows of band d stored only to ``dst_ptrs[d]``
+    (device pointers to bf16 [band_rows, ld_dst] matrices: this rank's slot in rank d's buffer)."""
+    x, n, k = _check_linear_args(x, w_packed, weight_scale, bias)
+    m = x.shape[0]
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    with torch.cuda.device(x.device):
+        ws = workspace(x.device, workspace_bytes(_lib.W8A8_STATIC, m, k, n))
+        rc = _lib.load().fp8lin_w8a8_reduce_scatter(
+            x.data_ptr(), x.stride(0), w_packed.data_ptr(), weight_scale.data_ptr(), input_scale.data_ptr(),
+            bias.data_ptr() if bias is not None else None, len(dst_ptrs), arr, ld_dst, band_rows, m, k, n,
+            ws.data_ptr(), ws.numel(), _stream_ptr(x.device))
+    _lib.raise_for(rc, "fp8lin_w8a8_reduce_scatter")
+
+
+def sum_slots_gather(slots_ptr: int, n_slots: int, slot_stride: int, ld_slot: int, dst_ptrs: list[int], ld_dst: int,
+                     dst_row: int, m: int, n: int, device: torch.device) -> None:
+    """Add ``n_slots`` bf16 [m, n] partials (``slot_stride`` elements apart) and store the sum at rows
+    [dst_row, dst_row + m) of every matrix in ``dst_ptrs`` (the ranks' outputs; peers by NVLink stores)."""
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    with torch.cuda.device(device):
+        rc = _lib.load().fp8lin_sum_slots_gather(slots_ptr, n_slots, slot_stride, ld_slot, len(dst_ptrs), arr, ld_dst,
+                                                 dst_row, m, n, _stream_ptr(device))
+    _lib.raise_for(rc, "fp8lin_sum_slots_gather")
+
+
 def sum_slots(slots: torch.Tensor, m: int, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """slots: bf16 [n_slots, rows >= m, n] -> bf16 [m, n], slots added in order in fp32."""
     n_slots = slots.shape[0]

@@ -33,7 +33,7 @@ def _worker(rank, world, port, out_dir):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(seconds=90))
     from oracle import fp8_oracle as O
     pkg = importlib.import_module("nano-vllm-moe_b200")
-    m, k, n = 640, 1024, 512
+    m, k, n = 650, 1024, 512            # ragged: the last rank's band of rows is shorter than the others'
     c = O.make_case(2468, m, k, n)
     with torch.device(dev):
         lay = pkg.RowParallelLinear(k, n, bias=True, quant_method=pkg.Fp8Config("fp8_w8a8_static").get_quant_method(None, "down"))
@@ -50,9 +50,17 @@ def _worker(rank, world, port, out_dir):
     lay.peer_reduce_min_rows = 1
     y_peer1 = lay(x).float().cpu().numpy()
     y_peer2 = lay(x).float().cpu().numpy()          # second call reuses the slots
+    lay.peer_reduce = "rs"                          # reduce-scatter in the epilogue + sum + all-gather by peer stores
+    y_rs1 = lay(x).float().cpu().numpy()
+    y_rs2 = lay(x).float().cpu().numpy()
+    lay.reduce_results = "scatter"                  # ... stopping after the sum: this rank's band of rows only
+    y_band = lay(x).float().cpu().numpy()
+    lay.reduce_results = True
+    band = -(-(-(-m // world)) // 32) * 32
     torch.cuda.synchronize()
     ref = O.row_parallel(c["x"], c["wq"], c["w_scale"], c["input_scale"], c["bias"], world, "fp8_w8a8_static")
-    np.savez(Path(out_dir) / f"r{rank}.npz", nccl=y_nccl, peer1=y_peer1, peer2=y_peer2, ref=ref)
+    np.savez(Path(out_dir) / f"r{rank}.npz", nccl=y_nccl, peer1=y_peer1, peer2=y_peer2, rs1=y_rs1, rs2=y_rs2, band=y_band,
+             band_ref=ref[rank * band:(rank + 1) * band], ref=ref)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -61,17 +69,20 @@ def _worker(rank, world, port, out_dir):
 def test_row_parallel_nccl_and_peer_reduce(tmp_path, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    if world > 2 and os.environ.get("FP8LIN_TEST_MANY_GPUS") != "1":
-        pytest.skip("the 4-rank variant has not run on a 4-GPU box yet; set FP8LIN_TEST_MANY_GPUS=1 to run it")
     import torch.multiprocessing as mp
     from oracle import fp8_oracle as O
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     outs = [np.load(tmp_path / f"r{rank}.npz") for rank in range(world)]
     for rank, d in enumerate(outs):
-        for key in ("nccl", "peer1", "peer2"):
+        for key in ("nccl", "peer1", "peer2", "rs1", "rs2"):
             ok, worst = O.check_close(d[key], d["ref"], ulps=float(world))     # one bf16 rounding per rank's partial
             assert ok, (rank, key, worst)
         np.testing.assert_array_equal(d["peer1"], d["peer2"])
+        np.testing.assert_array_equal(d["rs1"], d["rs2"])
+        np.testing.assert_array_equal(d["rs1"], d["peer1"])                    # same partials, same order of the sum
+        assert d["band"].shape == d["band_ref"].shape
+        ok, worst = O.check_close(d["band"], d["band_ref"], ulps=float(world))
+        assert ok, (rank, "band", worst)
         np.testing.assert_array_equal(outs[0]["peer1"], d["peer1"])            # every rank ends with the same bits
 
 

@@ -39,7 +39,8 @@ def test_weight_quantiser_properties(n, k16, seed):
     deq = O.e4m3_decode(q) * s[:, None]
     amax = np.abs(w).max(axis=1)
     np.testing.assert_array_equal(np.abs(O.e4m3_decode(q)).max(axis=1)[amax > 1e-8], 448.0)      # the extreme maps to +-448
-    assert np.all(np.abs(deq - w) <= amax[:, None] / 448.0 * 16.0 + 1e-12)                        # half a step of the top binade
+    # half a step of the top binade (and the fp32 roundings of w / scale and code * scale: a few ulps of slack)
+    assert np.all(np.abs(deq - w) <= amax[:, None] / 448.0 * 16.0 * (1.0 + 1e-5) + 1e-12)
     # scaling a row by a power of two scales its scale and leaves the codes alone
     q2, s2 = O.quantize_weight_per_channel(w * 4.0)
     np.testing.assert_array_equal(q2, q)
