@@ -490,25 +490,32 @@ def bench_moe(args, T):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         from datetime import timedelta
         dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=120))
-        if E % world:
-            if rank == 0:
-                print(json.dumps({"metric": "fp8_linear_throughput", "unavailable":
-                                  f"{E} experts do not divide over {world} ranks (the reference rejects it too)"}))
-            dist.destroy_process_group()
-            return
     moe = importlib.import_module("nano-vllm-moe_b200.executor.moe")
     Kn = importlib.import_module("nano-vllm-moe_b200.quantization.kernels")
     peaks = load_peaks()
-    cfg = moe.make_moe_parallel_config(tp_group=None, ep_group=dist.group.WORLD if world > 1 else None,
-                                       global_num_experts=E, intermediate_size=I)
+    # experts over the ranks; where they do not divide (60 experts on 8 ranks) the layout the reference accepts is
+    # EP (ranks / 2) x TP 2: experts over four ranks, every expert's intermediate dimension over two
+    tp_size = 1
+    if world > 1 and E % world:
+        tp_size = 2
+        if world % 2 or E % (world // 2) or I % 2:
+            if rank == 0:
+                print(json.dumps({"metric": "fp8_linear_throughput", "unavailable":
+                                  f"{E} experts do not divide over {world} ranks, nor over {world}/2 with the intermediate size halved"}))
+            dist.destroy_process_group()
+            return
+    tp_group, ep_group = (moe.make_ep_tp_groups(tp_size) if tp_size > 1 else (None, dist.group.WORLD if world > 1 else None))
+    cfg = moe.make_moe_parallel_config(tp_group=tp_group, ep_group=ep_group, global_num_experts=E, intermediate_size=I)
     el = cfg.local_num_experts
-    q13, s13, q2, s2 = make_expert_weights(el, H, I, SEED + 7919 * rank, dev)
-    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    # the ranks of a TP group hold the same experts (each its slice of the intermediate dimension) and the same tokens
+    q13, s13, q2, s2 = make_expert_weights(el, H, I, SEED + 7919 * cfg.ep_rank, dev)
+    g = torch.Generator(device=dev).manual_seed(SEED + cfg.ep_rank)
     calib = torch.randn((4096, H), generator=g, device=dev).to(torch.bfloat16)
     in13 = (calib.float().abs().amax() / 448.0).reshape(())
-    wts = moe.Fp8ExpertWeights.from_checkpoint_layout(q13, s13, in13, q2, s2, torch.tensor(4.0 / 448.0))
+    wts = moe.Fp8ExpertWeights.from_checkpoint_layout(q13, s13, in13, q2, s2, torch.tensor(4.0 / 448.0),
+                                                      tp_rank=cfg.tp_rank, tp_size=cfg.tp_size)
     del q13, q2
-    if world == 1:
+    if cfg.ep_size == 1:
         pf = moe.NoEPPrepareFinalize(cfg)
     elif args.ep_dispatch == "dynamic":      # the reference's exchange: variable splits, counts read back on the host
         pf = moe.TorchAllToAllPrepareFinalize(cfg)
@@ -589,8 +596,8 @@ def bench_moe(args, T):
         t = torch.tensor([ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
-    flops = flops_rank * world
-    by = min(E, T * K * world) * 3 * H * I + world * T * K * (H * 2 + 2 * I * 2 + I * 2 + H * 2)
+    flops = flops_rank * cfg.ep_size                # distinct tokens: one batch per EP rank (a TP group shares its batch)
+    by = min(E, T * K * cfg.ep_size) * 3 * H * I + cfg.ep_size * T * K * (H * 2 + 2 * I * 2 + I * 2 + H * 2)
     t_hbm = by / world / (peaks["hbm_gbs"] * 1e9)
     t_tc = flops_rank / (2 * peaks["bf16_tflops"] * 1e12)
     bound = "hbm" if t_hbm >= t_tc else "tensor"
@@ -603,7 +610,7 @@ def bench_moe(args, T):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 -> bf16", "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_rank": T, **MOE},
-            "run": {"parallelism": f"ep{world}" if world > 1 else "single",
+            "run": {"parallelism": (f"ep{cfg.ep_size}" + (f" x tp{cfg.tp_size}" if cfg.tp_size > 1 else "")) if world > 1 else "single",
                     "l2": f"expert weights {el * 3 * H * I / 1e6:.0f} MB per rank > 126 MB L2; inputs cycled over {sets} sets",
                     "launch": "cuda-graph replay" if use_graph else "eager",
                     "ep_dispatch": ("fixed-capacity all-to-all" if args.ep_dispatch == "fixed" else

@@ -35,3 +35,27 @@ def make_moe_parallel_config(*, tp_group, ep_group, global_num_experts: int, int
         raise ValueError(f"intermediate_size={intermediate_size} must be divisible by tp_size={tp_size}")
     return MoEParallelConfig(tp_group, ep_group, tp_size, tp_rank, ep_size, ep_rank, global_num_experts,
                              global_num_experts // ep_size, intermediate_size, intermediate_size // tp_size)
+
+
+def make_ep_tp_groups(tp_size: int):
+    """Process groups of an EP x TP layout over the default group: rank = ep_rank * tp_size + tp_rank, so the
+    ranks that split one expert's intermediate dimension are neighbours and each EP group holds the ranks with the
+    same tp_rank (the 8-GPU layout of 60 experts: EP 4 x TP 2, executor/moe/config.py:34-53 of the reference
+    accepts it because 60 % 4 == 0 and 1408 % 2 == 0).  Every rank must call this (new_group is collective).
+    Returns (tp_group, ep_group) of the calling rank; a group of size 1 is returned as None."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if tp_size < 1 or world % tp_size:
+        raise ValueError(f"world size {world} is not a multiple of tp_size={tp_size}")
+    ep_size = world // tp_size
+    my_tp = my_ep = None
+    for e in range(ep_size):
+        ranks = [e * tp_size + t for t in range(tp_size)]
+        g = dist.new_group(ranks) if tp_size > 1 else None
+        if rank in ranks:
+            my_tp = g
+    for t in range(tp_size):
+        ranks = [e * tp_size + t for e in range(ep_size)]
+        g = dist.new_group(ranks) if ep_size > 1 else None
+        if rank in ranks:
+            my_ep = g
+    return my_tp, my_ep

@@ -29,10 +29,24 @@ class Fp8ExpertWeights:
 
     @classmethod
     def from_checkpoint_layout(cls, w13_q: torch.Tensor, w13_scale: torch.Tensor, w13_input_scale: torch.Tensor,
-                               w2_q: torch.Tensor, w2_scale: torch.Tensor, w2_input_scale: torch.Tensor) -> "Fp8ExpertWeights":
-        """w13_q uint8 [E, 2I, H], w2_q uint8 [E, H, I] (the reference's stacked layout, blocks/base.py:58-63)."""
+                               w2_q: torch.Tensor, w2_scale: torch.Tensor, w2_input_scale: torch.Tensor,
+                               tp_rank: int = 0, tp_size: int = 1) -> "Fp8ExpertWeights":
+        """w13_q uint8 [E, 2I, H], w2_q uint8 [E, H, I] (the reference's stacked layout, blocks/base.py:58-63).
+        With ``tp_size`` > 1 this rank keeps slice ``tp_rank`` of the intermediate dimension: gate rows and up rows
+        [tp_rank * I/tp, (tp_rank + 1) * I/tp) of w13 with their scales, the matching columns of w2 (all of its
+        output-channel scales), as the reference shards its expert weights (blocks/base.py:66-93,
+        local_inter_size = I / tp); the ranks' outputs are summed by the TP all-reduce of ``finalize``."""
         e, two_i, h = w13_q.shape
         i = two_i // 2
+        if tp_size > 1:
+            if i % tp_size or (i // tp_size) % 16:
+                raise ValueError(f"the intermediate size {i} must split into {tp_size} slices that are multiples of 16")
+            il = i // tp_size
+            lo, hi = tp_rank * il, (tp_rank + 1) * il
+            w13_q = torch.cat([w13_q[:, lo:hi], w13_q[:, i + lo:i + hi]], dim=1).contiguous()
+            w13_scale = torch.cat([w13_scale[:, lo:hi], w13_scale[:, i + lo:i + hi]], dim=1).contiguous()
+            w2_q = w2_q[:, :, lo:hi].contiguous()
+            i = il
         if w2_q.shape != (e, h, i):
             raise ValueError(f"w2 must be [E, H, I] = {(e, h, i)}, got {tuple(w2_q.shape)}")
         w13_p = torch.cat([kernels.pack_weight_nk(w13_q[x]) for x in range(e)])

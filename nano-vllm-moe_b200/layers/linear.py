@@ -199,7 +199,7 @@ class RowParallelLinear(LinearBase):
     peer_reduce = "auto"
     peer_reduce_min_rows = 512
     peer_reduce_min_k = 4096
-    peer_rs_min_k = 1024
+    peer_rs_min_k = 0
 
     def _use_peer_rs(self, x: torch.Tensor, rows: int) -> bool:
         """Reduce-scatter + all-gather through peer memory (more than two ranks, or forced with peer_reduce = "rs")."""

@@ -100,6 +100,76 @@ def test_alltoall_dispatch_combine_closed_form(tmp_path, routing, flavour):
         assert dropped > 0
 
 
+def _ep_tp_worker(rank, world, port, result_dir):
+    """EP 2 x TP 2 on four CPU ranks: the two ranks of a TP group hold the same tokens and the same experts, each
+    contributes a share of every expert's output (standing in for its slice of the intermediate dimension), and
+    finalize adds the shares with the TP all-reduce (prepare_finalize/torch_alltoall.py:92 of the reference)."""
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    moe = importlib.import_module("nano-vllm-moe_b200.executor.moe")
+    tp_group, ep_group = moe.make_ep_tp_groups(2)
+    E, k, T, H = 6, 2, 10, 8
+    cfg = moe.make_moe_parallel_config(tp_group=tp_group, ep_group=ep_group, global_num_experts=E, intermediate_size=1408)
+    assert (cfg.tp_size, cfg.ep_size, cfg.local_num_experts, cfg.local_inter_size) == (2, 2, 3, 704)
+    assert (cfg.ep_rank, cfg.tp_rank) == (rank // 2, rank % 2)
+    errs = []
+    for pf in (moe.TorchAllToAllPrepareFinalize(cfg), moe.FixedCapacityAllToAllPrepareFinalize(cfg)):
+        g = torch.Generator().manual_seed(500 + cfg.ep_rank)           # the ranks of a TP group see the same tokens
+        x = torch.randn((T, H), generator=g)
+        ids = torch.randint(0, E, (T, k), generator=g)
+        w = torch.rand((T, k), generator=g)
+        prep = pf.prepare(x, w, ids)
+        valid = prep.topk_ids >= 0
+        share = 0.25 if cfg.tp_rank == 0 else 0.75                     # this TP rank's part of the expert output
+        local_out = prep.hidden_states * (prep.topk_ids[:, None].float() + 1.0) * prep.topk_weights[:, None] * share
+        local_out = torch.where(valid[:, None], local_out, torch.zeros_like(local_out))
+        y = pf.finalize(local_out, prep, output_shape=(T, H), model_dtype=torch.float32, reduce_tp=True)
+        local = ids % cfg.local_num_experts
+        want = (x[:, None, :] * (local[..., None].float() + 1.0) * w[..., None]).sum(dim=1)
+        errs.append(float((y - want).abs().max()))
+        y_half = pf.finalize(local_out, prep, output_shape=(T, H), model_dtype=torch.float32, reduce_tp=False)
+        errs.append(float((y_half - want * share).abs().max()))
+    np.save(Path(result_dir) / f"eptp_{rank}.npy", np.array(errs))
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_times_tensor_parallel_on_four_cpu_ranks(tmp_path):
+    mp.spawn(_ep_tp_worker, args=(4, _free_port(), str(tmp_path)), nprocs=4, join=True)
+    for rank in range(4):
+        assert np.load(tmp_path / f"eptp_{rank}.npy").max() < 1e-5, rank
+
+
+def test_expert_weights_are_sliced_along_the_intermediate_dimension():
+    """Fp8ExpertWeights.from_checkpoint_layout with a TP slice keeps gate and up rows of the slice and the matching
+    columns of the down weight (checked through the slicing arithmetic alone: packing needs a GPU)."""
+    exp = importlib.import_module("nano-vllm-moe_b200.executor.moe.experts")
+    E, I, H = 2, 64, 32
+    w13 = torch.arange(E * 2 * I * H, dtype=torch.int64).remainder(251).to(torch.uint8).view(E, 2 * I, H)
+    s13 = torch.arange(E * 2 * I, dtype=torch.float32).view(E, 2 * I)
+    w2 = torch.arange(E * H * I, dtype=torch.int64).remainder(241).to(torch.uint8).view(E, H, I)
+    seen = {}
+
+    def fake_pack(q):
+        seen.setdefault("shapes", []).append(tuple(q.shape))
+        seen.setdefault("first", []).append(q.clone())
+        return q.reshape(-1)
+    orig = exp.kernels.pack_weight_nk
+    exp.kernels.pack_weight_nk = fake_pack
+    try:
+        wt = exp.Fp8ExpertWeights.from_checkpoint_layout(w13, s13, torch.tensor(1.0), w2, torch.ones(E, H), torch.tensor(1.0),
+                                                         tp_rank=1, tp_size=2)
+    finally:
+        exp.kernels.pack_weight_nk = orig
+    assert wt.inter_size == 32 and seen["shapes"] == [(64, H), (64, H), (H, 32), (H, 32)]
+    assert torch.equal(seen["first"][0], torch.cat([w13[0, 32:64], w13[0, 96:128]]))
+    assert torch.equal(seen["first"][2], w2[0, :, 32:64])
+    assert torch.equal(wt.w13_scale[1], torch.cat([s13[1, 32:64], s13[1, 96:128]]))
+    with pytest.raises(ValueError):
+        exp.Fp8ExpertWeights.from_checkpoint_layout(w13, s13, torch.tensor(1.0), w2, torch.ones(E, H), torch.tensor(1.0), tp_rank=0, tp_size=8)
+
+
 def _row_parallel_worker(rank, world, port, result_dir):
     """Row-parallel layer wiring on CPU ranks: shard shapes, bias on rank 0 only, all-reduce."""
     sys.path.insert(0, str(ROOT))

@@ -72,7 +72,8 @@ def test_router_large_and_bf16(moe):
 
 
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 256, 128, 8, 2), (16, 512, 256, 12, 4), (64, 2048, 1408, 60, 4),
-                                       (300, 256, 128, 6, 2), (1024, 512, 384, 8, 4)])
+                                       (300, 256, 128, 6, 2), (1024, 512, 384, 8, 4),
+                                       (48, 2048, 704, 15, 4), (700, 512, 704, 5, 2)])     # 704 = a TP-2 slice of 1408
 def test_expert_ffn_matches_oracle(moe, T, H, I, E, k):
     c = make_moe_case(100 + T + E, T, H, I, E, k)
     wts = upload_weights(moe, c)

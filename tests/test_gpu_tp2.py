@@ -154,3 +154,66 @@ def test_expert_parallel_exchanges_agree_on_two_gpus(tmp_path):
         assert np.abs(d["full"]).max() > 0
         for key in ("dynamic", "fixed", "fixed_graph"):
             np.testing.assert_array_equal(d[key], d["full"], err_msg=f"rank {rank} {key}")
+
+
+def _ep_tp_worker(rank, world, port, out_dir):
+    """EP 2 x TP 2 on four GPUs: experts split over the EP group, every expert's intermediate dimension over the TP
+    group; a single rank holding everything is the comparison (different roundings: each TP rank rounds its own
+    partial down projection, so the bound is looser than bit equality)."""
+    import torch.distributed as dist
+    from datetime import timedelta
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(seconds=90))
+    moe = importlib.import_module("nano-vllm-moe_b200.executor.moe")
+    tp_group, ep_group = moe.make_ep_tp_groups(2)
+    E, K, T, H, I = 6, 2, 80, 256, 1408                                  # I / 2 = 704: not a multiple of 128
+    g = torch.Generator(device=dev).manual_seed(78)                      # the same full expert set on every rank
+    def codes(*shape):
+        w = torch.randn(shape, generator=g, device=dev) * 0.05
+        s = w.abs().amax(dim=-1).clamp(min=1e-8) / 448.0
+        return (w / s[..., None]).to(torch.float8_e4m3fn).view(torch.uint8), s
+    q13, s13 = codes(E, 2 * I, H)
+    q2, s2 = codes(E, H, I)
+    in13, in2 = torch.tensor(4.0 / 448.0), torch.tensor(2.0 / 448.0)
+    cfg = moe.make_moe_parallel_config(tp_group=tp_group, ep_group=ep_group, global_num_experts=E, intermediate_size=I)
+    gr = torch.Generator(device=dev).manual_seed(2000 + cfg.ep_rank)     # the ranks of a TP group share their tokens
+    x = torch.randn((T, H), generator=gr, device=dev).to(torch.bfloat16)
+    ids = torch.randint(0, E, (T, K), generator=gr, device=dev)
+    w = torch.rand((T, K), generator=gr, device=dev)
+    full_cfg = moe.make_moe_parallel_config(tp_group=None, ep_group=None, global_num_experts=E, intermediate_size=I)
+    full = moe.MoEKernel(prepare_finalize=moe.NoEPPrepareFinalize(full_cfg), experts=moe.Fp8Experts(), parallel_config=full_cfg)
+    y_full = full(x, w, ids, moe.Fp8ExpertWeights.from_checkpoint_layout(q13, s13, in13, q2, s2, in2), model_dtype=torch.bfloat16)
+    el = cfg.local_num_experts
+    mine = slice(cfg.ep_rank * el, (cfg.ep_rank + 1) * el)
+    wts = moe.Fp8ExpertWeights.from_checkpoint_layout(q13[mine], s13[mine], in13, q2[mine], s2[mine], in2,
+                                                      tp_rank=cfg.tp_rank, tp_size=cfg.tp_size)
+    assert wts.inter_size == I // 2
+    outs = {"full": y_full}
+    for name, pf in (("dynamic", moe.TorchAllToAllPrepareFinalize(cfg)), ("fixed", moe.FixedCapacityAllToAllPrepareFinalize(cfg))):
+        kern = moe.MoEKernel(prepare_finalize=pf, experts=moe.Fp8Experts(), parallel_config=cfg)
+        outs[name] = kern(x, w, ids, wts, model_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    np.savez(Path(out_dir) / f"eptp{rank}.npz", **{k: v.float().cpu().numpy() for k, v in outs.items()})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_times_tensor_parallel_on_four_gpus(tmp_path):
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    import torch.multiprocessing as mp
+    from oracle import fp8_oracle as O
+    mp.spawn(_ep_tp_worker, args=(4, _free_port(), str(tmp_path)), nprocs=4, join=True)
+    outs = [np.load(tmp_path / f"eptp{rank}.npz") for rank in range(4)]
+    for rank, d in enumerate(outs):
+        assert np.abs(d["full"]).max() > 0
+        np.testing.assert_array_equal(d["dynamic"], d["fixed"])
+        ok, worst = O.check_close(d["fixed"], d["full"], ulps=4.0)      # two partial down projections, each rounded, then summed
+        assert ok and O.cosine(d["fixed"], d["full"]) > 0.9999, (rank, worst)
+    np.testing.assert_array_equal(outs[0]["fixed"], outs[1]["fixed"])    # the two ranks of a TP group end with the same bits
+    np.testing.assert_array_equal(outs[2]["fixed"], outs[3]["fixed"])
