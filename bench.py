@@ -916,6 +916,10 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=0.25, help="device time to accumulate per measurement")
     ap.add_argument("--comparators", action="store_true",
                     help="also time torch._scaled_mm (cuBLASLt FP8) on the workload's shapes: a labelled library figure")
+    ap.add_argument("--no-overlap-reduce", action="store_true",
+                    help="N > 1: finish every row-parallel layer's reduction before the pass goes on (by default the sum and "
+                         "all-gather of a row-parallel output run on a side stream under the pass's next linears, and the pass "
+                         "ends when every output is complete)")
     ap.add_argument("--ep-dispatch", choices=["fixed", "dynamic"], default="fixed",
                     help="MoE workloads on N > 1 ranks: fixed-capacity all-to-all (graph-capturable) or the "
                          "reference's variable-split exchange with host-side counts")
@@ -983,6 +987,8 @@ def main():
             pkg.process_weights_after_loading(lay)
             if kind == "row" and args.peer_reduce != "auto":
                 lay.peer_reduce = {"on": True, "off": False, "rs": "rs"}[args.peer_reduce]
+            if kind == "row" and tp > 1 and not args.no_overlap_reduce:
+                lay.defer_gather = True
             row.append(lay)
             if c == 0:
                 xl = x if (kind == "col" or tp == 1) else x[:, rank * (k // tp):(rank + 1) * (k // tp)].contiguous()
@@ -997,7 +1003,11 @@ def main():
     torch.cuda.synchronize()
 
     def run_pass(c, xs):
-        return [lay(x) for lay, x in zip(layers[c % copies], xs)]
+        outs = [lay(x) for lay, x in zip(layers[c % copies], xs)]
+        for lay in layers[c % copies]:                  # the pass ends when every row-parallel output is complete
+            if hasattr(lay, "wait_reduce"):
+                lay.wait_reduce()
+        return outs
 
     xs_dev = [x for x, _ in inputs]
     # warm every (shape, scratch size) once eagerly so that graph capture sees no allocation
@@ -1132,6 +1142,8 @@ def main():
         def once(i=i, x=x):
             for c in range(copies):
                 layers[c][i](x)
+                if hasattr(layers[c][i], "wait_reduce"):
+                    layers[c][i].wait_reduce()
         if use_graph:
             ms, marks = time_graph(once, dev, side, args.min_seconds, world, dist, sampler if rank == 0 else None)
         else:
@@ -1236,6 +1248,8 @@ def main():
                 with torch.cuda.stream(s_comp):
                     s_comp.wait_event(ev_in[bset][j])
                     o = layers[i % copies][j](dev_in[bset][j])
+                    if hasattr(layers[i % copies][j], "wait_reduce"):
+                        layers[i % copies][j].wait_reduce()
                     ev_used[bset][j].record(s_comp)
                     ev_done[bset][j].record(s_comp)
                 with torch.cuda.stream(s_out):
@@ -1255,7 +1269,10 @@ def main():
             e2e_step(i)
         barrier()
         # the pipelined path returns what the plain call returns
-        torch.testing.assert_close(host_out[0][order[0]].to(dev), layers[2 % copies][order[0]](xs_dev[order[0]]), rtol=0, atol=0)
+        chk = layers[2 % copies][order[0]](xs_dev[order[0]])
+        if hasattr(layers[2 % copies][order[0]], "wait_reduce"):
+            layers[2 % copies][order[0]].wait_reduce()
+        torch.testing.assert_close(host_out[0][order[0]].to(dev), chk, rtol=0, atol=0)
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(s_out); s_in.wait_event(a); s_comp.wait_event(a)
@@ -1305,6 +1322,11 @@ def main():
             if scheme == "fp8_w8a8_static" else "fp8_e4m3 weights, f16 MMA -> fp32 -> bf16",
             "data": "synthetic", "config": config,
             "run": {"parallelism": f"tp{tp}" if tp > 1 else "single",
+                    "row_parallel_reduction": None if tp == 1 else (
+                        f"peer_reduce={args.peer_reduce}; " + ("each layer's reduction finished before the next linear starts"
+                                                               if args.no_overlap_reduce else
+                                                               "sum + all-gather of a row-parallel output on a side stream under the pass's "
+                                                               "next linears; every output complete before the pass (and the timed window) ends")),
                     "l2": f"weights cycled over {copies} distinct copies per shape "
                           f"({copies * weight_bytes / 1e6:.0f} MB > 126 MB L2)",
                     "launch": "cuda-graph replay" if use_graph else "eager",

@@ -196,6 +196,12 @@ class RowParallelLinear(LinearBase):
     #    one barrier, every rank sums locally.  (tp - 1) times the payload per rank: only sensible between two ranks
     #    (down at M = 16384: 697 us).
     # False = always the NCCL all-reduce, as the reference.
+    # defer_gather (reduce-scatter form only): forward returns once the GEMM (with its scatter) is enqueued; the
+    # barrier, the sum and the all-gather run on a side stream, so that the caller's next kernels -- work that does not
+    # read this output, e.g. the next micro-batch's or an independent linear's GEMM -- run while NVLink carries the
+    # reduced bands.  The output must not be read before `wait_reduce()` (which makes the current stream wait for
+    # the side stream); the layer's own next call waits by itself.
+    defer_gather = False
     peer_reduce = "auto"
     peer_reduce_min_rows = 512
     peer_reduce_min_k = 4096
@@ -241,20 +247,47 @@ class RowParallelLinear(LinearBase):
         slot_elems = band_cap * n
         y_off = tp * slot_elems                                  # element offset of the output inside the buffer
         # the previous call's second barrier guarantees that every rank has summed its slots and read its output
+        self.wait_reduce()                                       # a deferred gather of the previous call still owns the buffers
         dst = [int(handle.buffer_ptrs[r]) + rank * slot_elems * 2 for r in range(tp)]
         kernels.launch_w8a8_reduce_scatter(x2, self.qweight_packed, self.input_scale, self.weight_scale, bias, dst, n, band)
-        handle.barrier(channel=0)                                # every rank's partial rows of my band have landed
         mine = max(0, min(band, rows - rank * band))
         if self.reduce_results == "scatter":
+            handle.barrier(channel=0)                            # every rank's partial rows of my band have landed
             out = torch.empty((mine, n), dtype=torch.bfloat16, device=x.device)
             kernels.sum_slots_gather(buf.data_ptr(), tp, slot_elems, n, [out.data_ptr()], n, 0, mine, n, x.device)
             handle.barrier(channel=1)
             return out
         ys = [int(handle.buffer_ptrs[r]) + y_off * 2 for r in range(tp)]
-        kernels.sum_slots_gather(buf.data_ptr(), tp, slot_elems, n, ys, n, rank * band, mine, n, x.device)
-        handle.barrier(channel=1)                                # every band of the result is in place everywhere
         y = buf[y_off:y_off + rows * n].view(rows, n)            # (valid until this layer's next call)
+
+        def second_half():
+            handle.barrier(channel=0)                            # every rank's partial rows of my band have landed
+            kernels.sum_slots_gather(buf.data_ptr(), tp, slot_elems, n, ys, n, rank * band, mine, n, x.device)
+            handle.barrier(channel=1)                            # every band of the result is in place everywhere
+
+        if not self.defer_gather:
+            second_half()
+            return y.view(*x.shape[:-1], n)
+        main = torch.cuda.current_stream(x.device)
+        side = getattr(self, "_gather_stream", None)
+        if side is None:
+            side = self._gather_stream = torch.cuda.Stream(x.device)
+        scattered = torch.cuda.Event()
+        scattered.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(scattered)
+            second_half()
+            done = torch.cuda.Event()
+            done.record(side)
+        self._pending_gather = done
         return y.view(*x.shape[:-1], n)
+
+    def wait_reduce(self) -> None:
+        """Make the current stream wait for a deferred gather of this layer's last call (no-op otherwise)."""
+        done = getattr(self, "_pending_gather", None)
+        if done is not None:
+            torch.cuda.current_stream().wait_event(done)
+            self._pending_gather = None
 
     def _use_peer_reduce(self, x: torch.Tensor, rows: int) -> bool:
         if self.peer_reduce is False or self.peer_reduce == "rs" or getattr(self, "_peer_failed", False):
