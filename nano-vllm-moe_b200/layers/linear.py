@@ -201,7 +201,13 @@ class RowParallelLinear(LinearBase):
     # read this output, e.g. the next micro-batch's or an independent linear's GEMM -- run while NVLink carries the
     # reduced bands.  The output must not be read before `wait_reduce()` (which makes the current stream wait for
     # the side stream); the layer's own next call waits by itself.
+    # peer_scatter: how the partial bands reach their owners.  "epilogue" = the GEMM's TMA stores (the transfer
+    # overlaps the GEMM's own tiles: right when the local GEMM outlasts the transfer); "copy" = the GEMM writes a local
+    # partial result and the copy engines push its bands to the peers afterwards (large NVLink packets, no SM work;
+    # with defer_gather the whole exchange runs beside the caller's next kernels: right when K/tp is short and the
+    # transfer would outlast the GEMM); "auto" picks by that comparison.
     defer_gather = False
+    peer_scatter = "auto"
     peer_reduce = "auto"
     peer_reduce_min_rows = 512
     peer_reduce_min_k = 4096
@@ -248,9 +254,15 @@ class RowParallelLinear(LinearBase):
         y_off = tp * slot_elems                                  # element offset of the output inside the buffer
         # the previous call's second barrier guarantees that every rank has summed its slots and read its output
         self.wait_reduce()                                       # a deferred gather of the previous call still owns the buffers
+        mine = max(0, min(band, rows - rank * band))
+        by_copy = self.peer_scatter == "copy" or (
+            self.peer_scatter == "auto" and self.reduce_results != "scatter"
+            # GEMM time ~ 2 M K' N / 2.2e15 against (tp - 1) / tp * 2 M N bytes at ~0.6 TB/s of NVLink writes
+            and self.input_size_per_partition < 3667 * (tp - 1) // tp)
+        if by_copy:
+            return self._finish_rs_by_copy(x, x2, bias, rows, band, mine, buf, handle, slot_elems, y_off)
         dst = [int(handle.buffer_ptrs[r]) + rank * slot_elems * 2 for r in range(tp)]
         kernels.launch_w8a8_reduce_scatter(x2, self.qweight_packed, self.input_scale, self.weight_scale, bias, dst, n, band)
-        mine = max(0, min(band, rows - rank * band))
         if self.reduce_results == "scatter":
             handle.barrier(channel=0)                            # every rank's partial rows of my band have landed
             out = torch.empty((mine, n), dtype=torch.bfloat16, device=x.device)
@@ -277,6 +289,49 @@ class RowParallelLinear(LinearBase):
         with torch.cuda.stream(side):
             side.wait_event(scattered)
             second_half()
+            done = torch.cuda.Event()
+            done.record(side)
+        self._pending_gather = done
+        return y.view(*x.shape[:-1], n)
+
+    def _finish_rs_by_copy(self, x, x2, bias, rows, band, mine, buf, handle, slot_elems, y_off):
+        """Reduce-scatter with the copy engines: the plain GEMM writes this rank's partial result locally, then band r
+        goes to rank r's slot by one peer-to-peer copy each, the owner sums, and the reduced band is stored to every
+        rank.  With defer_gather everything after the GEMM runs on the side stream."""
+        from ..quantization import kernels
+        n, tp, rank = self.output_size, self.tp_size, self.tp_rank
+        part = getattr(self, "_partial", None)
+        if part is None or part.shape[0] < rows:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the row-parallel partial buffer must exist before a CUDA graph capture: run the shape once first")
+            part = self._partial = torch.empty((max(rows, getattr(self, "_rs_cap", rows)), n), dtype=torch.bfloat16, device=x.device)
+        self.quant_method.apply(self, x2, bias, out=part[:rows])
+        ys = [int(handle.buffer_ptrs[r]) + y_off * 2 for r in range(tp)]
+        y = buf[y_off:y_off + rows * n].view(rows, n)
+
+        def exchange():
+            for step in range(tp):
+                r = (rank + step) % tp                           # every rank starts with a different peer
+                lo, hi = r * band, min(rows, (r + 1) * band)
+                if hi > lo:
+                    slot = handle.get_buffer(r, (hi - lo, n), torch.bfloat16, storage_offset=rank * slot_elems)
+                    slot.copy_(part[lo:hi], non_blocking=True)
+            handle.barrier(channel=0)
+            kernels.sum_slots_gather(buf.data_ptr(), tp, slot_elems, n, ys, n, rank * band, mine, n, x.device)
+            handle.barrier(channel=1)
+
+        if not self.defer_gather:
+            exchange()
+            return y.view(*x.shape[:-1], n)
+        main = torch.cuda.current_stream(x.device)
+        side = getattr(self, "_gather_stream", None)
+        if side is None:
+            side = self._gather_stream = torch.cuda.Stream(x.device)
+        computed = torch.cuda.Event()
+        computed.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(computed)
+            exchange()
             done = torch.cuda.Event()
             done.record(side)
         self._pending_gather = done

@@ -51,6 +51,7 @@ def _worker(rank, world, port, out_dir):
     y_peer1 = lay(x).float().cpu().numpy()
     y_peer2 = lay(x).float().cpu().numpy()          # second call reuses the slots
     lay.peer_reduce = "rs"                          # reduce-scatter in the epilogue + sum + all-gather by peer stores
+    lay.peer_scatter = "epilogue"
     y_rs1 = lay(x).float().cpu().numpy()
     y_rs2 = lay(x).float().cpu().numpy()
     lay.defer_gather = True                         # sum + all-gather on a side stream; the caller joins before reading
@@ -60,14 +61,20 @@ def _worker(rank, world, port, out_dir):
     y_def = lay(x)                                  # (the next call waits for the previous gather by itself)
     lay.wait_reduce()
     y_def2 = y_def.float().cpu().numpy()
+    lay.peer_scatter = "copy"                       # the bands travel by copy engine instead of the GEMM's stores
+    y_cp = lay(x)
+    lay.wait_reduce()
+    y_cp1 = y_cp.float().cpu().numpy()
     lay.defer_gather = False
+    y_cp2 = lay(x).float().cpu().numpy()
+    lay.peer_scatter = "epilogue"
     lay.reduce_results = "scatter"                  # ... stopping after the sum: this rank's band of rows only
     y_band = lay(x).float().cpu().numpy()
     lay.reduce_results = True
     band = -(-(-(-m // world)) // 32) * 32
     torch.cuda.synchronize()
     ref = O.row_parallel(c["x"], c["wq"], c["w_scale"], c["input_scale"], c["bias"], world, "fp8_w8a8_static")
-    np.savez(Path(out_dir) / f"r{rank}.npz", nccl=y_nccl, peer1=y_peer1, peer2=y_peer2, rs1=y_rs1, rs2=y_rs2, def1=y_def1, def2=y_def2, band=y_band,
+    np.savez(Path(out_dir) / f"r{rank}.npz", nccl=y_nccl, peer1=y_peer1, peer2=y_peer2, rs1=y_rs1, rs2=y_rs2, def1=y_def1, def2=y_def2, cp1=y_cp1, cp2=y_cp2, band=y_band,
              band_ref=ref[rank * band:(rank + 1) * band], ref=ref)
     dist.barrier()
     dist.destroy_process_group()
@@ -90,6 +97,9 @@ def test_row_parallel_nccl_and_peer_reduce(tmp_path, world):
         np.testing.assert_array_equal(d["rs1"], d["peer1"])                    # same partials, same order of the sum
         np.testing.assert_array_equal(d["def1"], d["rs1"])
         np.testing.assert_array_equal(d["def2"], d["rs1"])
+        np.testing.assert_array_equal(d["cp1"], d["cp2"])
+        ok, worst = O.check_close(d["cp1"], d["ref"], ulps=float(world))       # (another GEMM route: same values to the accumulation order)
+        assert ok, (rank, "copy", worst)
         assert d["band"].shape == d["band_ref"].shape
         ok, worst = O.check_close(d["band"], d["band_ref"], ulps=float(world))
         assert ok, (rank, "band", worst)
