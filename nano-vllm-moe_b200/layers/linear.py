@@ -281,9 +281,7 @@ class RowParallelLinear(LinearBase):
             second_half()
             return y.view(*x.shape[:-1], n)
         main = torch.cuda.current_stream(x.device)
-        side = getattr(self, "_gather_stream", None)
-        if side is None:
-            side = self._gather_stream = torch.cuda.Stream(x.device)
+        side = self._exchange_stream(x.device)
         scattered = torch.cuda.Event()
         scattered.record(main)
         with torch.cuda.stream(side):
@@ -324,9 +322,7 @@ class RowParallelLinear(LinearBase):
             exchange()
             return y.view(*x.shape[:-1], n)
         main = torch.cuda.current_stream(x.device)
-        side = getattr(self, "_gather_stream", None)
-        if side is None:
-            side = self._gather_stream = torch.cuda.Stream(x.device)
+        side = self._exchange_stream(x.device)
         computed = torch.cuda.Event()
         computed.record(main)
         with torch.cuda.stream(side):
@@ -336,6 +332,19 @@ class RowParallelLinear(LinearBase):
             done.record(side)
         self._pending_gather = done
         return y.view(*x.shape[:-1], n)
+
+    _exchange_streams: dict = {}
+
+    @classmethod
+    def _exchange_stream(cls, device) -> torch.cuda.Stream:
+        """One side stream per device for ALL row-parallel layers: their deferred exchanges (each a sequence of
+        cross-rank barriers) then run in the same order on every rank, whatever the hardware does with parallel
+        branches -- two layers' barrier kernels can never wait for each other crosswise."""
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        st = cls._exchange_streams.get(key)
+        if st is None:
+            st = cls._exchange_streams[key] = torch.cuda.Stream(device)
+        return st
 
     def wait_reduce(self) -> None:
         """Make the current stream wait for a deferred gather of this layer's last call (no-op otherwise)."""

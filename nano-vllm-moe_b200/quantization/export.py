@@ -70,7 +70,15 @@ class AmaxObserver:
             raise ValueError("AmaxObserver.update needs a CUDA tensor")
         x2 = x.detach().reshape(-1, x.shape[-1])
         if x2.dtype != torch.bfloat16:
-            x2 = x2.to(torch.bfloat16)
+            # The reference's hook takes abs().float().max() of the activation in its own dtype (quantize.py make_hook).
+            # Rounding an fp32 / fp16 activation to bf16 first could round the maximum DOWN and shrink the scale, so
+            # other dtypes are folded in at full precision on the device (calibration only: not a hot path).
+            slot = self._amax.get(name)
+            if slot is None:
+                slot = self._amax[name] = torch.zeros((), dtype=torch.float32, device=x.device)
+            if x2.numel():
+                torch.maximum(slot, x2.abs().amax().to(torch.float32), out=slot)
+            return
         if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.shape[1] % 8:
             x2 = torch.nn.functional.pad(x2, (0, (-x2.shape[1]) % 8)).contiguous()
         slot = self._amax.get(name)

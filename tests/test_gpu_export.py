@@ -63,6 +63,13 @@ def test_abs_max_observer():
     obs.update("y", c)
     obs.update("y", torch.zeros((0, 100), dtype=torch.bfloat16, device="cuda"))
     assert obs.amax("y") == float(c.float().abs().max())
+    # fp32 / fp16 activations keep their own precision (a bf16 cast could round the maximum down)
+    f = torch.tensor([[1.00390625, -0.5], [0.25, 1.0]], device="cuda")          # 1 + 2^-8: not a bf16 value
+    obs.update("z", f)
+    assert obs.amax("z") == 1.00390625
+    obs.update("z", f.half() * 0.5)
+    assert obs.amax("z") == 1.00390625
+    obs.update("z", torch.zeros((0, 2), device="cuda"))
     scales = obs.input_scales()
     assert scales["x"].dtype == torch.float32 and scales["x"].shape == ()
     np.testing.assert_array_equal(scales["x"].numpy(), O.input_scale_from_amax(obs.amax("x")))
