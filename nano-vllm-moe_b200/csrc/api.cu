@@ -38,6 +38,7 @@ struct Tuning {
     int fuse_quant = -1;        // large-M W8A8: <= 0 (default) = quantise x in a separate pass; 1 = the pass takes the rows
                                 // of the first round of tiles, the GEMM's own quantiser warps the rest; n > 1 = the pass
                                 // takes the first n rows (rounded up to 128)
+    int moe_fused = -1;         // 0 = the expert FFN keeps its separate silu-multiply-quantise pass for every batch size
     int quant_lead = -1;        // row blocks the in-kernel quantiser may run ahead (default: from the tile schedule)
 } g_tune;
 
@@ -733,6 +734,8 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "umma_pair")) g_tune.umma_pair = value;
     else if (!strcmp(knob, "fuse_quant")) g_tune.fuse_quant = value;
     else if (!strcmp(knob, "quant_lead")) g_tune.quant_lead = value;
+    else if (!strcmp(knob, "moe_fused")) g_tune.moe_fused = value;
+    else if (!strcmp(knob, "pair_stages")) set_pair_stages(value);
     else if (!strcmp(knob, "pdl")) set_pdl_enabled(value != 0);
     else return fail(FP8LIN_ERR_ARG, "unknown tuning knob '%s'", knob);
     return FP8LIN_OK;
@@ -831,17 +834,28 @@ int fp8lin_moe_experts_w8a8(const void* x, int64_t ldx, int x_div, const int32_t
     a.input_scale = w13_input_scale; a.topk_w = topk_w; a.out = gu; a.status = (int*)workspace;
     a.ldx = (int)ldx; a.x_div = x_div; a.ld_out = (int)(2 * I); a.N = (int)(2 * I); a.K = (int)H; a.n_tiles = 0; a.kblocks = 0;
     a.scatter = 0;
+    // prefill-sized batches with whole 128-channel tiles: the gate_up GEMM's epilogue applies the activation and writes hq
+    // (from 32-row chunks on: the epilogue reads the two accumulators 32 rows at a time)
+    const bool fused_act = rows >= kMoePrequantRows && I % 128 == 0 && mp >= 32 && g_tune.moe_fused != 0;
     if (rows >= kMoePrequantRows) {
         unsigned char* xq = ws + L.off_xq;
         e = launch_moe_gather_quant((const __nv_bfloat16*)x, ldx, x_div, sorted, meta, w13_input_scale, xq, (int)rows, (int)H, st);
         if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "row gather launch: %s", cudaGetErrorString(e));
-        e = launch_grouped_w8a8(false, mp, a, w13_packed, E, xq, rows, st, &why);
+        if (fused_act) {
+            GroupedArgs f = a;
+            f.N = (int)I; f.hq = hq; f.h_scale = w2_input_scale; f.out = nullptr;
+            e = launch_grouped_w8a8(false, mp, f, w13_packed, E, xq, rows, st, &why);
+        } else {
+            e = launch_grouped_w8a8(false, mp, a, w13_packed, E, xq, rows, st, &why);
+        }
     } else {
         e = launch_grouped_w8a8(true, mp, a, w13_packed, E, nullptr, 0, st, &why);
     }
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "gate_up grouped GEMM launch: %s (%s)", cudaGetErrorString(e), why ? why : "");
-    e = launch_silu_mul_quant(gu, w2_input_scale, hq, meta, (int)rows, (int)I, st);
-    if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation launch: %s", cudaGetErrorString(e));
+    if (!fused_act) {
+        e = launch_silu_mul_quant(gu, w2_input_scale, hq, meta, (int)rows, (int)I, st);
+        if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "activation launch: %s", cudaGetErrorString(e));
+    }
     a.w_scale = w2_scale; a.input_scale = w2_input_scale; a.out = (__nv_bfloat16*)out_routed; a.ld_out = (int)ld_out;
     a.N = (int)H; a.K = (int)I; a.scatter = 1;
     e = launch_grouped_w8a8(false, mp, a, w2_packed, E, hq, rows, st, &why);

@@ -125,6 +125,7 @@ cudaError_t launch_x_to_f16(const __nv_bfloat16* x, int64_t ldx, void* x16, int6
 cudaError_t launch_dequant_tiles_f16(const unsigned char* src, void* dst, int64_t src_bytes, cudaStream_t stream);
 // The same GEMM on CTA pairs (umma_pair_gemm.cu): 256 x 256 tiles, one MMA across two CTAs.  f16 selects the
 // operand type as above; destinations as launch_umma_w8a8.
+void set_pair_stages(int n);        // 4 or 5 ring slots instead of 6 in the e4m3 pair kernel (pipeline-depth studies)
 cudaError_t launch_umma_pair(bool f16, const UmmaArgs& args, cudaStream_t stream, const char** why, int n_dst = 0,
                              void* const* dst_ptrs = nullptr, int64_t ld_dst = 0, int64_t band_rows = 0);
 // Fused MLP pieces: gate_up GEMM whose epilogue writes e4m3 h = silu(g) * u for the down projection
@@ -189,6 +190,12 @@ struct GroupedArgs {
     int* status;
     int ldx, x_div, ld_out;
     int N, K, n_tiles, kblocks;
+    // fused gate_up + activation (launch_grouped_w8a8 with hq set): N = I gate channels, w_scale = [E][2 I], the epilogue
+    // writes hq[sorted position][I] = e4m3(bf16(bf16(silu(g)) * u) / *h_scale) instead of `out`
+    unsigned char* hq = nullptr;
+    const float* h_scale = nullptr;
+    int w_tiles = 0;             // 128-channel tile rows per expert in the packed weight (set by the launcher)
+    int up_tile_offset = 0;      // tile rows from a gate tile to the up tile of the same channels (set by the launcher)
 };
 int grouped_chunk_rows(int64_t rows, int num_experts);
 cudaError_t launch_grouped_w8a8(bool gather, int mp, GroupedArgs a, const void* w_packed, int num_experts,

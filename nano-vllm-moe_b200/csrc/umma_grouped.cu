@@ -18,6 +18,13 @@
 //   0      gu[sorted position][channel] = bf16(acc * in_scale * w_scale[e][channel])
 //   1      out[routed row][channel] = bf16(acc * in_scale * w_scale[e][channel] * topk_w[routed row])
 //
+// kFused (prefill-sized gate_up only, rows already e4m3): a work item covers the gate tile t AND the up tile t of the
+// expert (two weight boxes per K block against one box of rows, two accumulators), and the epilogue writes what the down
+// projection reads instead of the bf16 gate_up rows: hq[sorted position][channel] = e4m3(h / h_scale) with
+// h = bf16(bf16(silu(g)) * u) from g, u rounded to bf16 -- the values and roundings of the unfused path (the eager
+// two-rounding SiluAndMul of the reference's experts).  Half the row bytes per MAC through L2 -> SM, and the bf16 gate_up
+// tensor (rows x 2I x 2 bytes each way) and the separate activation pass disappear.
+//
 // Weight-bandwidth-bound for small batches (each expert's weights are read once per chunk),
 // tensor-bound for prefill-sized batches.  All mbarrier waits are bounded.
 #include "umma_common.cuh"
@@ -29,24 +36,27 @@ constexpr int kGrpThreads = (2 + kGrpConvWarps + 4) * 32;
 constexpr int kGrpTile = 128;
 constexpr int kGrpKB = 128;
 
-template <int MP>
+template <int MP, bool kFused = false>
 struct GroupedCfg {
     static constexpr int kWBytes = kGrpTile * kGrpKB;
+    static constexpr int kWTiles = kFused ? 2 : 1;                 // weight boxes per K block (gate and up)
     static constexpr int kXqBytes = MP * kGrpKB;
-    static constexpr int kStageBytes = kWBytes + kXqBytes;
+    static constexpr int kStageBytes = kWTiles * kWBytes + kXqBytes;
     static constexpr int kStagesRaw = (225 * 1024) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
-    static constexpr int kTmemCols = 2 * MP < 32 ? 32 : 2 * MP;
+    static constexpr int kAccCols = kWTiles * MP;                  // TMEM columns of one accumulator stage
+    static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
     static constexpr int kTeam = MP <= 16 ? 1 : (MP <= 32 ? 2 : 4);
     static constexpr int kPiece = MP < 32 ? MP : 32;            // accumulator columns per TMEM read
     static_assert(kStageBytes % 1024 == 0, "stage alignment");
 };
 
-template <int MP, bool kGather>
+template <int MP, bool kGather, bool kFused = false>
 __global__ void __launch_bounds__(kGrpThreads, 1)
 grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_xq, GroupedArgs p) {
-    using Cfg = GroupedCfg<MP>;
+    static_assert(!kFused || !kGather, "the fused activation epilogue takes pre-quantised rows");
+    using Cfg = GroupedCfg<MP, kFused>;
     constexpr int S = Cfg::kStages;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[S];
@@ -94,7 +104,7 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 const int4 ch = p.chunks[w / p.n_tiles];
                 const int t = w % p.n_tiles;
-                const int wrow0 = (ch.x * p.n_tiles + t) * KB;        // packed tile index of (expert, tile, kb = 0)
+                const int wrow0 = (ch.x * p.w_tiles + t) * KB;        // packed tile index of (expert, tile, kb = 0)
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int st = it % S;
                     const uint32_t ph = (it / S) & 1;
@@ -103,9 +113,11 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     }
                     const uint32_t full = smem_u32(&bar_full[st]);
                     const uint32_t sa = smem_base + st * Cfg::kStageBytes;
-                    mbar_expect_tx(full, kGather ? Cfg::kWBytes : Cfg::kWBytes + Cfg::kXqBytes);
+                    mbar_expect_tx(full, kGather ? Cfg::kWBytes : Cfg::kWTiles * Cfg::kWBytes + Cfg::kXqBytes);
                     tma_load_2d(sa, &tmap_w, 0, (wrow0 + kb) * kGrpTile, full);
-                    if (!kGather) tma_load_2d(sa + Cfg::kWBytes, &tmap_xq, kb * kGrpKB, ch.y, full);
+                    // fused: the up tile of the same channels sits up_tile_offset tile rows further on in the expert's weight
+                    if (kFused) tma_load_2d(sa + Cfg::kWBytes, &tmap_w, 0, (wrow0 + p.up_tile_offset * KB + kb) * kGrpTile, full);
+                    if (!kGather) tma_load_2d(sa + Cfg::kWTiles * Cfg::kWBytes, &tmap_xq, kb * kGrpKB, ch.y, full);
                 }
             }
             if (!ok) {
@@ -127,7 +139,7 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     s_abort = 1; ok = false; break;
                 }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + as * MP;
+                const uint32_t d_tmem = tmem_base + as * Cfg::kAccCols;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int st = it % S;
                     const uint32_t ph = (it / S) & 1;
@@ -138,10 +150,13 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     tc_fence_after();
                     const uint32_t sa = smem_base + st * Cfg::kStageBytes;
                     const uint64_t da = make_smem_desc(sa);
-                    const uint64_t db = make_smem_desc(sa + Cfg::kWBytes);
+                    const uint64_t db = make_smem_desc(sa + Cfg::kWTiles * Cfg::kWBytes);
 #pragma unroll
-                    for (int k = 0; k < kGrpKB / 32; ++k)
+                    for (int k = 0; k < kGrpKB / 32; ++k) {
                         umma_f8(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        if (kFused)        // the up tile against the same rows, into the second half of the accumulator stage
+                            umma_f8(d_tmem + MP, make_smem_desc(sa + Cfg::kWBytes) + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit(smem_u32(&bar_empty[st]));
                 }
                 if (ok) umma_commit(smem_u32(&bar_tfull[as]));
@@ -199,7 +214,7 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             const int as = tl & 1;
             const uint32_t aph = (tl >> 1) & 1;
             const int n = t * kGrpTile + q * 32 + lane;                         // output channel of this lane
-            const float ws = n < p.N ? in_scale * __ldg(p.w_scale + (size_t)ch.x * p.N + n) : 0.f;
+            const float ws = (!kFused && n < p.N) ? in_scale * __ldg(p.w_scale + (size_t)ch.x * p.N + n) : 0.f;
             // routed-row index and routing weight of the chunk's rows, one row per lane and piece;
             // the inner loop gets them by shuffle instead of two dependent global loads per row
             int my_routed[(MP + 31) / 32];
@@ -215,7 +230,38 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             }
             if (!mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
             tc_fence_after();
-            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * MP;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + as * Cfg::kAccCols;
+            if (kFused) {
+                // lane = gate channel n of the expert; its up channel is n + N.  One e4m3 byte per row and lane.
+                const float wu = n < p.N ? in_scale * __ldg(p.w_scale + (size_t)ch.x * 2 * p.N + p.N + n) : 0.f;
+                const float wg = n < p.N ? in_scale * __ldg(p.w_scale + (size_t)ch.x * 2 * p.N + n) : 0.f;
+                const ExactDiv div_h(fmaxf(__ldg(p.h_scale), 1e-12f));
+#pragma unroll 1
+                for (int c0 = 0; c0 < MP; c0 += 32) {
+                    if (c0 >= ch.z) break;
+                    uint32_t g[32], u[32];
+                    __syncwarp();
+                    tmem_ld32_nowait(t_addr + c0, g);
+                    tmem_ld32_nowait(t_addr + MP + c0, u);
+                    tmem_ld_wait();
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (c0 + j < ch.z) {
+                                const uint32_t gu = pack_bf16x2(__uint_as_float(g[j]) * wg, __uint_as_float(u[j]) * wu);   // as the bf16 gate_up row
+                                const float gv = bf16_lo(gu);
+                                const uint32_t sv = pack_bf16x2(gv / (1.f + expf(-gv)), 0.f);                              // bf16(silu(g))
+                                const uint32_t hv = pack_bf16x2(bf16_lo(sv) * bf16_hi(gu), 0.f);                           // bf16(. * u)
+                                p.hq[(size_t)(ch.y + c0 + j) * p.N + n] = (unsigned char)(cvt_e4m3x2(div_h(bf16_lo(hv)), 0.f) & 0xffu);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < MP; c0 += Cfg::kPiece) {
                 if (c0 >= ch.z) break;                                           // uniform: no rows left in this chunk
@@ -258,10 +304,10 @@ grouped_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 }
 
 // ---- host side -------------------------------------------------------------------
-template <int MP, bool kGather>
+template <int MP, bool kGather, bool kFused = false>
 static cudaError_t launch_grouped(const GroupedArgs& a, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
-    using Cfg = GroupedCfg<MP>;
-    auto kern = grouped_w8a8_kernel<MP, kGather>;
+    using Cfg = GroupedCfg<MP, kFused>;
+    auto kern = grouped_w8a8_kernel<MP, kGather, kFused>;
     static SmemOptIn opted;
     {
         cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kSmemBytes, opted);
@@ -286,9 +332,16 @@ int grouped_chunk_rows(int64_t rows, int num_experts) {
 cudaError_t launch_grouped_w8a8(bool gather, int mp, GroupedArgs a, const void* w_packed, int num_experts,
                                 const void* xq_sorted, int64_t xq_rows, cudaStream_t stream, const char** why) {
     CUtensorMap tw, tx;
+    const bool fused = a.hq != nullptr;           // a.N = I gate channels; the expert's weight holds 2 I channels
     a.n_tiles = (int)pack_ntiles(a.N);
+    a.w_tiles = fused ? 2 * a.n_tiles : a.n_tiles;
+    a.up_tile_offset = fused ? a.n_tiles : 0;
     a.kblocks = (int)pack_kblocks(a.K);
-    if (!encode_u8_2d(&tw, w_packed, (uint64_t)num_experts * a.n_tiles * a.kblocks * 128, 128, kGrpTile)) {
+    if (fused && (gather || a.N % kGrpTile != 0 || mp < 32 || mp > 128)) {
+        if (why) *why = "the fused activation epilogue needs pre-quantised rows and an intermediate size that is a multiple of 128";
+        return cudaErrorInvalidValue;
+    }
+    if (!encode_u8_2d(&tw, w_packed, (uint64_t)num_experts * a.w_tiles * a.kblocks * 128, 128, kGrpTile)) {
         if (why) *why = "cuTensorMapEncodeTiled failed for the expert weights";
         return cudaErrorInvalidValue;
     }
@@ -298,7 +351,8 @@ cudaError_t launch_grouped_w8a8(bool gather, int mp, GroupedArgs a, const void* 
         return cudaErrorInvalidValue;
     }
 #define FP8LIN_GROUPED_CASE(MP_) \
-    if (mp == MP_) return gather ? launch_grouped<MP_, true>(a, tw, tx, stream) : launch_grouped<MP_, false>(a, tw, tx, stream);
+    if (mp == MP_) return fused ? launch_grouped<MP_, false, true>(a, tw, tx, stream) \
+                                : (gather ? launch_grouped<MP_, true>(a, tw, tx, stream) : launch_grouped<MP_, false>(a, tw, tx, stream));
     FP8LIN_GROUPED_CASE(16)
     FP8LIN_GROUPED_CASE(32)
     FP8LIN_GROUPED_CASE(64)

@@ -69,11 +69,12 @@ __device__ __forceinline__ void decode_pair_tile(const PairSched& s, int tile, i
 // 128 bytes per row and tile go to the e4m3 matrix [M][N/2] described by outs.m[0].
 // kFuseQ (e4m3 operands only): kQuantWarps more warps per CTA quantise the bf16 activations into xq while the
 // GEMM runs (umma_common.cuh); each CTA's producer waits for its own 128-row block of xq before loading it.
-template <bool kF16, bool kMlp, bool kFuseQ = false>
+// kS: ring slots in use (kStages; fewer only for pipeline-depth studies).
+template <bool kF16, bool kMlp, bool kFuseQ = false, int kS = kStages>
 __global__ void __launch_bounds__(kThreads + (kFuseQ ? kQuantWarps * 32 : 0), 1)
 umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ OutMaps outs, UmmaArgs p, PairSched sched, const float* h_scale) {
-    constexpr int S = kStages;
+    constexpr int S = kS;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[S];
     __shared__ __align__(8) uint64_t bar_empty[S];
@@ -361,10 +362,12 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (kFuseQ && threadIdx.x == 0) quant_ctrl_release(qjob, p.M);
 }
 
-template <bool kF16, bool kMlp, bool kFuseQ = false>
+int g_pair_stages = kStages;       // tuning knob "pair_stages" (studies only)
+
+template <bool kF16, bool kMlp, bool kFuseQ = false, int kS = kStages>
 cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& ty,
                         cudaStream_t stream, const char** why, const float* h_scale = nullptr) {
-    auto kern = umma_pair_gemm_kernel<kF16, kMlp, kFuseQ>;
+    auto kern = umma_pair_gemm_kernel<kF16, kMlp, kFuseQ, kS>;
     constexpr int kBlock = kThreads + (kFuseQ ? kQuantWarps * 32 : 0);
     static SmemOptIn opted;
     {
@@ -401,6 +404,8 @@ cudaError_t launch_pair(const UmmaArgs& a, const CUtensorMap& ta, const CUtensor
 
 }  // namespace
 
+void set_pair_stages(int n) { g_pair_stages = (n == 4 || n == 5) ? n : kStages; }
+
 cudaError_t launch_umma_pair(bool f16, const UmmaArgs& a, cudaStream_t stream, const char** why, int n_dst,
                              void* const* dst_ptrs, int64_t ld_dst, int64_t band_rows) {
     CUtensorMap ta, tb;
@@ -432,6 +437,8 @@ cudaError_t launch_umma_pair(bool f16, const UmmaArgs& a, cudaStream_t stream, c
         return cudaErrorInvalidValue;
     }
     if (!f16 && a.x) return launch_pair<false, false, true>(a, ta, tb, ty, stream, why);
+    if (!f16 && g_pair_stages == 5) return launch_pair<false, false, false, 5>(a, ta, tb, ty, stream, why);
+    if (!f16 && g_pair_stages == 4) return launch_pair<false, false, false, 4>(a, ta, tb, ty, stream, why);
     return f16 ? launch_pair<true, false>(a, ta, tb, ty, stream, why) : launch_pair<false, false>(a, ta, tb, ty, stream, why);
 }
 

@@ -89,6 +89,29 @@ def test_expert_ffn_matches_oracle(moe, T, H, I, E, k):
     assert kernels().read_status(torch.device("cuda", 0)) == 0
 
 
+@pytest.mark.parametrize("T,H,I,E,k", [(1024, 512, 384, 8, 4), (600, 2048, 1408, 60, 4), (4096, 256, 128, 6, 2), (900, 512, 256, 60, 1)])
+def test_fused_activation_epilogue_equals_the_separate_pass(moe, T, H, I, E, k):
+    """Prefill-sized batches: the gate_up grouped GEMM's epilogue applies silu * up and quantises for the down
+    projection.  Same values, same roundings as the separate pass: bit-identical outputs (chunks of 32, 64 and 128 rows,
+    experts with no rows, ragged last chunks)."""
+    Kn = kernels()
+    c = make_moe_case(300 + T + E, T, H, I, E, k)
+    wts = upload_weights(moe, c)
+    cfg = moe.make_moe_parallel_config(tp_group=None, ep_group=None, global_num_experts=E, intermediate_size=I)
+    kern = moe.MoEKernel(prepare_finalize=moe.NoEPPrepareFinalize(cfg), experts=moe.Fp8Experts(), parallel_config=cfg)
+    w, ids = moe.SoftmaxTopKRouter(k, False).select_experts(None, torch.from_numpy(c["logits"]).cuda())
+    x = to_bf16_cuda(c["x"])
+    try:
+        y_fused = kern(x, w, ids, wts, model_dtype=torch.bfloat16)
+        Kn.set_tuning("moe_fused", 0)
+        y_plain = kern(x, w, ids, wts, model_dtype=torch.bfloat16)
+    finally:
+        Kn.set_tuning("moe_fused", -1)
+    assert torch.equal(y_fused, y_plain)
+    assert y_fused.float().abs().max() > 0
+    assert Kn.read_status(torch.device("cuda", 0)) == 0
+
+
 def test_expert_rows_outside_local_range_are_skipped(moe):
     """Expert-parallel ranks see ids of other ranks' experts as out of range: those rows stay zero."""
     c = make_moe_case(7, 32, 256, 128, 4, 2)
