@@ -19,7 +19,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "libfp8lin.so"
-SOURCES = ["api.cu", "rmsnorm_quant.cu", "stream_kernel.cu", "elementwise.cu", "umma_gemm.cu", "umma_pair_gemm.cu", "umma_swap.cu", "umma_swap_w8a16.cu", "umma_grouped.cu", "moe_kernels.cu", "static_scratch.cu"]
+SOURCES = ["api.cu", "rmsnorm_quant.cu", "stream_kernel.cu", "elementwise.cu", "umma_gemm.cu", "umma_pair_gemm.cu", "umma_swap.cu", "umma_swap_w8a16.cu", "umma_grouped.cu", "umma_grouped_rows.cu", "moe_kernels.cu", "static_scratch.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",

@@ -198,6 +198,11 @@ struct GroupedArgs {
     int up_tile_offset = 0;      // tile rows from a gate tile to the up tile of the same channels (set by the launcher)
 };
 int grouped_chunk_rows(int64_t rows, int num_experts);
+// Prefill-sized batches (umma_grouped_rows.cu): the routed rows are the MMA M dimension, 128 rows x 256 channels per work
+// item, one epilogue thread per row.  args.hq set = gate_up with the activation fused (args.N = I); else the down projection
+// (scatter to routed rows, times the routing weight).  Needs the chunk list made with 128-row chunks and rows already e4m3.
+cudaError_t launch_grouped_rows_w8a8(GroupedArgs args, const void* w_packed, int num_experts, const void* xq_sorted,
+                                     int64_t xq_rows, cudaStream_t stream, const char** why);
 cudaError_t launch_grouped_w8a8(bool gather, int mp, GroupedArgs a, const void* w_packed, int num_experts,
                                 const void* xq_sorted, int64_t xq_rows, cudaStream_t stream, const char** why);
 

@@ -8,7 +8,8 @@ namespace fp8lin {
 // One warp per token: fp32 softmax over the E router logits, then top-k by k rounds of a
 // warp arg-max (ties go to the lower expert index), optional renormalisation of the k
 // weights.  Same algebra as softmax(dtype=float32) -> topk -> (w / sum w).
-template <typename LogitT>
+// kMaxPerLane: experts per lane (E <= 32 * kMaxPerLane); small expert counts get a short unrolled loop.
+template <typename LogitT, int kMaxPerLane>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const LogitT* __restrict__ logits, int64_t ld, int T, int E, int top_k, int renormalize,
                  float* __restrict__ out_w, int* __restrict__ out_ids) {
@@ -17,7 +18,6 @@ moe_route_kernel(const LogitT* __restrict__ logits, int64_t ld, int T, int E, in
     const int lane = threadIdx.x & 31;
     const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (token >= T) return;
-    constexpr int kMaxPerLane = 32;                  // E <= 1024
     float v[kMaxPerLane];
     const LogitT* row = logits + (size_t)token * ld;
     float mx = -INFINITY;
@@ -70,12 +70,19 @@ cudaError_t launch_moe_route(const void* logits, int logits_bf16, int64_t ld, in
     if (T == 0) return cudaSuccess;
     const int warps = 8;
     dim3 grid((unsigned)((T + warps - 1) / warps));
-    if (logits_bf16)
-        moe_route_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>((const __nv_bfloat16*)logits, ld, T, E, top_k,
-                                                                           renormalize, out_w, out_ids);
-    else
-        moe_route_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)logits, ld, T, E, top_k, renormalize,
-                                                                 out_w, out_ids);
+#define FP8LIN_ROUTE(PER_)                                                                                                \
+    do {                                                                                                                  \
+        if (logits_bf16)                                                                                                  \
+            moe_route_kernel<__nv_bfloat16, PER_><<<grid, warps * 32, 0, stream>>>((const __nv_bfloat16*)logits, ld, T, E, \
+                                                                                   top_k, renormalize, out_w, out_ids);   \
+        else                                                                                                              \
+            moe_route_kernel<float, PER_><<<grid, warps * 32, 0, stream>>>((const float*)logits, ld, T, E, top_k,         \
+                                                                           renormalize, out_w, out_ids);                  \
+    } while (0)
+    if (E <= 64) FP8LIN_ROUTE(2);
+    else if (E <= 256) FP8LIN_ROUTE(8);
+    else FP8LIN_ROUTE(32);
+#undef FP8LIN_ROUTE
     return counted(cudaGetLastError());
 }
 

@@ -58,7 +58,7 @@ def test_router_matches_reference_fixture(moe, golden):
 
 def test_router_large_and_bf16(moe):
     rng = np.random.default_rng(3)
-    for T, E, k in [(1, 60, 4), (257, 60, 4), (64, 128, 8), (5, 7, 2)]:
+    for T, E, k in [(1, 60, 4), (257, 60, 4), (64, 128, 8), (5, 7, 2), (33, 64, 6), (40, 300, 5), (9, 1000, 3)]:
         logits = rng.standard_normal((T, E), dtype=np.float32)
         w_ref, ids_ref = O.softmax_topk(logits, k, False)
         w, ids = moe.SoftmaxTopKRouter(k, False).select_experts(None, torch.from_numpy(logits).cuda())
@@ -89,7 +89,8 @@ def test_expert_ffn_matches_oracle(moe, T, H, I, E, k):
     assert kernels().read_status(torch.device("cuda", 0)) == 0
 
 
-@pytest.mark.parametrize("T,H,I,E,k", [(1024, 512, 384, 8, 4), (600, 2048, 1408, 60, 4), (4096, 256, 128, 6, 2), (900, 512, 256, 60, 1)])
+@pytest.mark.parametrize("T,H,I,E,k", [(1024, 512, 384, 8, 4), (600, 2048, 1408, 60, 4), (4096, 256, 128, 6, 2), (900, 512, 256, 60, 1),
+                                       (2100, 272, 128, 5, 3), (3000, 2048, 1408, 60, 4)])     # H = 272: a lone last weight tile
 def test_fused_activation_epilogue_equals_the_separate_pass(moe, T, H, I, E, k):
     """Prefill-sized batches: the gate_up grouped GEMM's epilogue applies silu * up and quantises for the down
     projection.  Same values, same roundings as the separate pass: bit-identical outputs (chunks of 32, 64 and 128 rows,
@@ -102,13 +103,22 @@ def test_fused_activation_epilogue_equals_the_separate_pass(moe, T, H, I, E, k):
     w, ids = moe.SoftmaxTopKRouter(k, False).select_experts(None, torch.from_numpy(c["logits"]).cuda())
     x = to_bf16_cuda(c["x"])
     try:
+        y_rows = kern(x, w, ids, wts, model_dtype=torch.bfloat16)          # default: rows as the MMA M dimension where chunks are 128 rows
+        Kn.set_tuning("moe_rows_major", 0)                                 # the channel-major grouped kernel, activation fused ...
         y_fused = kern(x, w, ids, wts, model_dtype=torch.bfloat16)
-        Kn.set_tuning("moe_fused", 0)
+        Kn.set_tuning("moe_fused", 0)                                      # ... and with the separate activation pass
         y_plain = kern(x, w, ids, wts, model_dtype=torch.bfloat16)
     finally:
         Kn.set_tuning("moe_fused", -1)
+        Kn.set_tuning("moe_rows_major", -1)
     assert torch.equal(y_fused, y_plain)
     assert y_fused.float().abs().max() > 0
+    # the other orientation multiplies the same codes; only the accumulation order inside the MMA may differ
+    assert_parity(from_bf16(y_rows), from_bf16(y_plain), "rows-major vs channel-major grouped GEMM", ulps=2.0, min_cos=0.99999)
+    w_ref, ids_ref = O.softmax_topk(c["logits"], k, False)
+    if T * k * H * I <= 2e9:
+        ref = O.moe_experts_w8a8(c["x"], ids_ref, w_ref, c["w13_q"], c["w13_s"], c["in13"], c["w2_q"], c["w2_s"], c["in2"])
+        assert_parity(from_bf16(y_rows), ref, f"rows-major moe T={T} E={E}", ulps=3.0, min_cos=0.9999)
     assert Kn.read_status(torch.device("cuda", 0)) == 0
 
 
