@@ -196,6 +196,9 @@ int fp8lin_quantize_activation(const void* x, int64_t ldx, const float* input_sc
  * w2_packed = E x packed(K=I, N=H).  Scales: w13_scale f32 [E][2I], w2_scale f32 [E][H],
  * one static activation scale per projection.
  *
+ * From 512 routed rows on the rows are gathered and quantised once, the gate_up grouped GEMM applies silu(g) * u and
+ * the down projection's quantiser in its epilogue (I a multiple of 128), and with more than 64 rows per expert on
+ * average both grouped GEMMs run with the routed rows as the MMA M dimension (128 x 256 work items).
  * fp8lin_moe_route replaces SoftmaxTopKRouter.select_experts (executor/moe/router.py:24-34):
  * fp32 softmax over E logits (logits_dtype 0 = f32, 1 = bf16), top-k, optional
  * renormalisation; topk_w f32 [T][k], topk_ids i32 [T][k]. */
@@ -283,7 +286,9 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);
  * Knobs: "stream_splits", "stream_max_m", "umma_bn", "umma_splits", "umma_pair" (CTA-pair GEMM on/off),
  * "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable", "w8a16_swap_min_m", "fuse_quant" (1 = large-M W8A8 quantises most rows with warps of the GEMM
  * itself instead of a pass in front of it; n > 1 = the pass takes the first n rows), "quant_lead",
- * "w8a16_umma_min_m" (rows from which W8A16 takes the f16 GEMM route; 0 = never), "w8a16_chunk_mb", "pdl". */
+ * "w8a16_umma_min_m" (rows from which W8A16 takes the f16 GEMM route; 0 = never), "w8a16_chunk_mb", "pdl",
+ * "moe_fused" (0 = the expert FFN keeps a separate activation pass), "moe_rows_major" (0 = prefill-sized expert
+ * batches stay on the channel-major grouped kernel), "pair_stages" (4 or 5 ring slots in the CTA-pair GEMM). */
 int fp8lin_set_tuning(const char* knob, int value);
 
 /* Blocking: copies the device status word out of `workspace` (after syncing

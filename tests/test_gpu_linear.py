@@ -417,3 +417,40 @@ def test_layer_end_to_end(pkg, scheme):
     ref = (O.linear_w8a16(x2, wq, ws, bias) if scheme == "fp8_w8a16"
            else O.linear_w8a8(x2, wq, ws, in_scale, bias))
     assert_parity(y.reshape(-1, n_gate + n_up), ref, f"layer {scheme}")
+
+
+CANARY_SHAPES = [
+    # (scheme, M, K, N): one shape per kernel route, with ragged M and N where the route allows them
+    ("fp8_w8a16", 3, 448, 576), ("fp8_w8a16", 40, 704, 72), ("fp8_w8a16", 150, 512, 264), ("fp8_w8a16", 300, 2368, 1000),
+    ("fp8_w8a8_static", 1, 2048, 2048), ("fp8_w8a8_static", 7, 16, 24), ("fp8_w8a8_static", 12, 1408, 1000),
+    ("fp8_w8a8_static", 33, 2368, 1000), ("fp8_w8a8_static", 64, 3584, 3584), ("fp8_w8a8_static", 130, 448, 576),
+    ("fp8_w8a8_static", 300, 2368, 1000), ("fp8_w8a8_static", 1280, 256, 4000), ("fp8_w8a8_static", 2048, 8192, 2560),
+    ("fp8_w8a8_static/pair", 300, 2368, 1000), ("fp8_w8a8_static/pair", 1025, 448, 520),
+]
+
+
+@pytest.mark.parametrize("scheme,m,k,n", CANARY_SHAPES)
+def test_no_kernel_writes_outside_its_output_matrix(scheme, m, k, n):
+    """The output is a window of a larger buffer filled with a sentinel: rows above and below it and the columns to
+    its right (row pitch > N) must come back untouched, whatever tails the tiles have (TMA stores clip at the tensor
+    map's extent, the other epilogues predicate).  Stands in for a memory checker on the store side."""
+    Kn = kernels()
+    if scheme.endswith("/pair"):
+        Kn.set_tuning("umma_pair", 1)
+        scheme = scheme.split("/")[0]
+    c = O.make_case(777 + m + n, m, k, n, calib_rows=64)
+    d = upload_case(c)
+    pitch = (n + 8 + 7) // 8 * 8 + 8                       # a multiple of 8, at least 8 spare columns
+    guard = 5
+    sentinel = -24576.0                                    # exactly representable in bf16, far from any output
+    buf = torch.full((m + 2 * guard, pitch), sentinel, dtype=torch.bfloat16, device="cuda")
+    window = buf[guard:guard + m, :n]
+    if scheme == "fp8_w8a16":
+        Kn.launch_w8a16_gemm(d["x"], d["w_nk"], d["w_scale"], d["bias"], out=window)
+    else:
+        Kn.launch_w8a8_gemm(d["x"], d["w_nk"], d["input_scale"], d["w_scale"], d["bias"], out=window)
+    torch.cuda.synchronize()
+    got = buf.float().cpu().numpy()
+    assert (got[:guard] == sentinel).all() and (got[guard + m:] == sentinel).all(), "rows outside the window were written"
+    assert (got[guard:guard + m, n:] == sentinel).all(), "columns past N were written"
+    assert_parity(got[guard:guard + m, :n], oracle_linear(scheme, c), f"windowed output {scheme} {m}x{k}x{n}")
