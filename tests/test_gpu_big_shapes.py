@@ -229,6 +229,36 @@ def test_row_grouping_matches_reference_alignment(golden):
     assert ((mixed.cpu().numpy()[kept] >= 0) & (mixed.cpu().numpy()[kept] < E)).all()
 
 
+@pytest.mark.parametrize("rows,E", [(5000, 60), (16384, 60), (2048, 128), (3000, 7), (4097, 129)])
+def test_row_grouping_many_rows(rows, E):
+    """Prefill-sized batches: every kept row exactly once, rows of an expert adjacent, chunks inside one expert, and
+    the per-expert counts of a numpy bincount."""
+    pkg = importlib.import_module("nano-vllm-moe_b200")
+    lib = pkg._lib.load()
+    rng = np.random.default_rng(rows + E)
+    ids_np = rng.integers(-1, E + 1, size=rows).astype(np.int32)            # a few ids outside [0, E): dropped
+    valid = (ids_np >= 0) & (ids_np < E)
+    ids = torch.from_numpy(ids_np).cuda()
+    offs = torch.full((E + 1,), -1, dtype=torch.int32, device="cuda")
+    srt = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    chunks = torch.full((E + rows // 16 + 2, 4), -1, dtype=torch.int32, device="cuda")
+    meta = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    pkg._lib.raise_for(lib.fp8lin_moe_align(ids.data_ptr(), rows, E, 128, offs.data_ptr(), srt.data_ptr(), chunks.data_ptr(),
+                                            meta.data_ptr(), torch.cuda.current_stream().cuda_stream), "fp8lin_moe_align")
+    offs, srt, chunks, meta = offs.cpu().numpy(), srt.cpu().numpy(), chunks.cpu().numpy(), meta.cpu().numpy()
+    counts = np.bincount(ids_np[valid], minlength=E)
+    np.testing.assert_array_equal(np.diff(offs), counts)
+    kept = srt[:meta[1]]
+    assert meta[1] == valid.sum()
+    np.testing.assert_array_equal(np.sort(kept), np.flatnonzero(valid))
+    np.testing.assert_array_equal(ids_np[kept], np.repeat(np.arange(E), counts))
+    covered = np.zeros(meta[1], bool)
+    for e, first, cnt, _ in chunks[:meta[0]]:
+        assert 0 < cnt <= 128 and offs[e] <= first and first + cnt <= offs[e + 1]
+        covered[first:first + cnt] = True
+    assert covered.all() and meta[0] == np.ceil(counts / 128).sum()
+
+
 def test_bounded_wait_runs_out_and_the_context_stays_usable():
     """A wait that nothing satisfies gives up after its limit, the host reads the code, and the next call is clean."""
     pkg = importlib.import_module("nano-vllm-moe_b200")
