@@ -368,7 +368,10 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq)
     for (int s = 1; s <= 8; ++s) {
         if (force_splits > 0 && s != (force_splits > 8 ? 8 : force_splits)) continue;
         if (s > kblocks) break;
-        if (force_splits <= 0 && s > 1 && kblocks / s < 4) break;          // at least four K blocks per slice
+        // at least four K blocks per slice -- two when every cluster is resident at one CTA per SM (a 4 MB layer such as
+        // 2048 -> 2048 at one row: 4.4 us with 8 slices of 2 blocks against 5.8 us with 4 slices of 4)
+        const int min_blocks = (pl.n_tiles * s <= sm_count()) ? 2 : 4;
+        if (force_splits <= 0 && s > 1 && kblocks / s < min_blocks) break;
         const int kps = (kblocks + s - 1) / s;
         if ((kblocks + kps - 1) / kps != s) continue;                        // would leave an empty slice
         int slots = sm_count() * (pl.mp == 16 ? 2 : 1);
