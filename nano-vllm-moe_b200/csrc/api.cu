@@ -149,15 +149,15 @@ bool pair_eligible(int64_t M, int64_t N) {
 }
 
 bool swap_eligible(int64_t M, int64_t K, int64_t N) {
+    (void)K; (void)N;
     const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
-    // up to 8 rows the mma.sync streaming kernel (several small CTAs per SM) starts and drains
-    // faster than the one-CTA-per-SM tcgen05 pipeline; measured cross-over is between 8 and 16 rows.
-    // Exception: a long K over few channel tiles (18944 -> 3584, 68 MB), where the 8-slice cluster
-    // split-K of the tcgen05 kernel streams faster from the first row on (M = 4: 16.9 vs 19.1 us).
-    int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 9;
-    if (g_tune.swap_min_m < 0 && K >= 8192 && N <= 4736 && K * N >= (32ll << 20)) min_m = 1;
-    // ... and a layer of a few MB whose 8-slice clusters are all resident at once (2048 -> 2048: 4.4 vs 5.9 us at one row)
-    if (g_tune.swap_min_m < 0 && K * N <= (4ll << 20) && K >= 2048 && ((N + 127) / 128) * 8 <= sm_count()) min_m = 1;
+    // The tcgen05 kernel from the first row on.  Since its split-K slices push their partial sums to the CTA that
+    // finishes a band (no cluster barrier, no remote loads) it beats the mma.sync streaming kernel at every size
+    // measured, e.g. at one row / eight rows: 3584 -> 4608 6.8 / 7.1 us against 7.8 / 8.2, 3584 -> 3584 6.0 / 6.3
+    // against 7.5 / 8.0, 2048 -> 11008 7.3 / 7.5 against 8.3 / 9.0, 11008 -> 2048 8.6 / 8.8 against 10.1 / 10.6,
+    // 1408 -> 2048 3.7 / 4.1 against 5.6 / 6.2, 3584 -> 37888 21.9 / 22.8 against 23.8 / 27.1 (3584 -> 9472: equal).
+    // The streaming kernel stays for W8A16 up to 32 rows and for the no-allocation entry point.
+    const int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 1;
     return g_tune.swap_enable != 0 && M >= min_m && M <= 64 && M <= max_m;
 }
 

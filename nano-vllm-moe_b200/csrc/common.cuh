@@ -35,7 +35,7 @@ __host__ __device__ inline WsView ws_view(void* ws, size_t bytes) {
 
 // device status codes written by kernels that gave up a bounded wait
 enum : int { kDevOk = 0, kDevTimeoutFull = 0x101, kDevTimeoutEmpty = 0x102, kDevTimeoutTmemFull = 0x103,
-             kDevTimeoutTmemEmpty = 0x104, kDevTimeoutQuant = 0x105 };
+             kDevTimeoutTmemEmpty = 0x104, kDevTimeoutQuant = 0x105, kDevTimeoutPeer = 0x106 };
 
 // ---- packed weight layout ----------------------------------------------------------
 // Weights are stored as 128-channel x 128-byte tiles, each tile contiguous (16 KiB),

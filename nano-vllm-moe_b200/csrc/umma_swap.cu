@@ -10,7 +10,9 @@
 //                tile (128-byte swizzle) and the raw bf16 activation block
 //                [MP x 128] into a ring of 5..9 stages (144..80 KB of weights in
 //                flight per SM).
-//   warps 2..9   activation converters in teams of 1, 2 or 4 warps, one ring slot per
+//   warps 2..9   activation converters in teams of 1, 2, 4 or 8 warps (one lane per 16 elements
+//                of the real rows, so a block is converted in one step: the first block's
+//                conversion is on the critical path of every call), one ring slot per
 //                team (several K blocks are converted concurrently): quantise the M real rows of
 //                the raw block to e4m3 with the static scale (exact division)
 //                and write them into the K-major, 128-byte-swizzled MMA "B"
@@ -23,9 +25,12 @@
 //
 // Launch shapes: persistent over the N/128 channel tiles, or, when there are too
 // few tiles to occupy 148 SMs, cluster split-K: the CTAs of a cluster (2..8)
-// take K slices of one tile, park fp32 partials in their own shared memory and
-// each reduces a band of channels over the cluster with ld.shared::cluster
-// (fixed order, deterministic).  All mbarrier waits are bounded.
+// take K slices of one tile and each finishes a band of channels.  A CTA whose
+// MMAs are done tells every peer that its ring is free (remote mbarrier arrive);
+// the epilogue lanes then push their fp32 partials of band r straight into CTA r's
+// ring with st.async, which counts the bytes on CTA r's barrier; CTA r adds the
+// slices in rank order (deterministic), writes y and leaves -- no cluster-wide
+// barrier after set-up, no remote loads.  All mbarrier waits are bounded.
 #include "umma_common.cuh"
 
 namespace fp8lin {
@@ -48,8 +53,6 @@ struct SwapCfg {
     // CTAs of the next kernel can start on an SM while this kernel's other CTA is still draining
     static constexpr int kCtasPerSm = MP <= 16 ? 2 : 1;
     static constexpr int kStages = kPreQ ? (MP <= 16 ? 6 : 9) : (MP <= 16 ? 5 : (MP <= 32 ? 7 : 5));
-    // converter warps that share one K block (more rows -> more warps per block)
-    static constexpr int kTeam = MP <= 16 ? 1 : (MP <= 32 ? 2 : 4);
     static constexpr int kRingBytes = kStages * kStageBytes;
     static constexpr int kSmemBytes = kRingBytes + 1024;
     static constexpr int kTmemCols = 2 * MP < 32 ? 32 : 2 * MP;
@@ -80,6 +83,9 @@ __device__ __forceinline__ void tmem_ld_cols<64>(uint32_t taddr, uint32_t* v) {
     tmem_ld32_nowait(taddr + 32, v + 32);
 }
 
+// converter warps that share one K block: one lane per (row, 16-element chunk) of the M real rows
+__host__ __device__ inline int conv_team(int m) { return m <= 4 ? 1 : (m <= 8 ? 2 : (m <= 16 ? 4 : 8)); }
+
 template <int MP, bool kSplit, bool kPreQ = false>
 __global__ void __launch_bounds__(kSwapThreads, SwapCfg<MP, kPreQ>::kCtasPerSm)
 swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -95,6 +101,8 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __shared__ __align__(8) uint64_t bar_empty[S];    // MMAs that read the stage are done
     __shared__ __align__(8) uint64_t bar_tfull[2];
     __shared__ __align__(8) uint64_t bar_tempty[2];
+    __shared__ __align__(8) uint64_t bar_ready;       // split-K: every CTA of the cluster is past its MMAs (its ring may be written)
+    __shared__ __align__(8) uint64_t bar_recv;        // split-K: the partials of this CTA's band have landed
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile int s_abort;
 
@@ -107,15 +115,25 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const int tile_step = kSplit ? sched.n_tiles : (int)gridDim.x;
     const int kb0 = split_rank * sched.kblocks_per_split;
     const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
+    // split-K: CTA r of the cluster finishes channels [r * band, r * band + band_rows) of the tile; a slice's partials
+    // of one channel are MP floats kPartPitch bytes apart, the slices of a band follow each other in the owner's ring
+    const int band = kSplit ? (kTileN + sched.splits - 1) / sched.splits : kTileN;
+    const int band_rows = kSplit ? min(kTileN, (split_rank + 1) * band) - split_rank * band : 0;
+    const int m_groups = (p.M + 3) >> 2;                          // rows travel in groups of four
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; ++i) {
             mbar_init(smem_u32(&bar_full[i]), 1);
-            mbar_init(smem_u32(&bar_xq[i]), Cfg::kTeam);
+            mbar_init(smem_u32(&bar_xq[i]), conv_team(p.M));
             mbar_init(smem_u32(&bar_empty[i]), 1);
         }
         for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bar_tfull[i]), 1); mbar_init(smem_u32(&bar_tempty[i]), 4); }
         s_abort = 0;
+        if (kSplit) {
+            mbar_init(smem_u32(&bar_ready), (uint32_t)sched.splits);
+            mbar_init(smem_u32(&bar_recv), 1);
+            mbar_expect_tx(smem_u32(&bar_recv), (uint32_t)(sched.splits * band_rows * m_groups * 16));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -131,6 +149,19 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     pdl_launch_dependents();
+    if (kSplit) cluster_arrive();                            // (waited for before the first remote access: the peers' barriers exist)
+    // scale and bias of the first channel this thread finishes, fetched long before they are needed
+    float ws0 = 0.f, bs0 = 0.f, in_scale0 = 0.f;
+    if constexpr (kSplit) {
+        in_scale0 = fmaxf(__ldg(p.input_scale), 1e-12f);
+        if (band_rows > 0 && (int)threadIdx.x < band_rows * m_groups) {
+            const int n0 = first_tile * kTileN + split_rank * band + (int)threadIdx.x % band_rows;
+            if (n0 < p.N) {
+                ws0 = __ldg(p.w_scale + n0);
+                if (p.bias) bs0 = __bfloat162float(p.bias[n0]);
+            }
+        }
+    }
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -211,9 +242,10 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     } else if (warp < 2 + kConvWarps) {
         // ================= activation converters (warps 2..9); idle when the rows come pre-quantised ====
         if (!kPreQ) {
-        constexpr int kTeams = kConvWarps / Cfg::kTeam;
-        const int team = (warp - 2) / Cfg::kTeam;            // a ring slot always belongs to the same team
-        const int member = (warp - 2) % Cfg::kTeam;
+        const int team_sz = conv_team(p.M);
+        const int kTeams = kConvWarps / team_sz;
+        const int team = (warp - 2) / team_sz;               // a ring slot always belongs to the same team
+        const int member = (warp - 2) % team_sz;
         const ExactDiv div_scale(fmaxf(__ldg(p.input_scale), 1e-12f));
         const int items = p.M * 8;                          // (row, 16-element chunk) pairs of the real rows
         uint32_t it = 0;
@@ -229,7 +261,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const uint32_t sa = smem_base + st * Cfg::kStageBytes;
                 const uint32_t xq = sa + Cfg::kWBytes;
                 const uint32_t xr = xq + Cfg::kXqBytes;
-                for (int i = member * 32 + lane; i < items; i += 32 * Cfg::kTeam) {
+                for (int i = member * 32 + lane; i < items; i += 32 * team_sz) {
                     const int m = i >> 3, c = i & 7;
                     uint4 a, b;
                     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w)
@@ -280,48 +312,61 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         if (m < p.M) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(fmaf(__uint_as_float(v[m]) * in_scale, ws, bs));
                 }
             } else {
-                const uint32_t dst = smem_base + (uint32_t)(q * 32 + lane) * Cfg::kPartPitch;
+                // (one tile per cluster)  Tell every peer that this CTA's ring is free, wait until all of them are,
+                // then send each channel's partial sums to the CTA that finishes it.
+                cluster_wait();
+                if (q == 0 && lane < sched.splits) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_ready), (uint32_t)lane));
+                if (!mbar_wait(smem_u32(&bar_ready), 0, p.status, kDevTimeoutPeer)) { s_abort = 1; ok = false; break; }
+                const int c = q * 32 + lane;
+                const uint32_t owner = (uint32_t)(c / band);
+                const uint32_t dst = map_to_cta(smem_base + (uint32_t)(split_rank * band + (c - (int)owner * band)) * Cfg::kPartPitch, owner);
+                const uint32_t rbar = map_to_cta(smem_u32(&bar_recv), owner);
 #pragma unroll
                 for (int m = 0; m < MP; m += 4)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + m * 4), "r"(v[m]), "r"(v[m + 1]),
-                                 "r"(v[m + 2]), "r"(v[m + 3]) : "memory");
+                    if (m < p.M) st_async_v4(dst + m * 4, v[m], v[m + 1], v[m + 2], v[m + 3], rbar);
             }
         }
     }
 
-    if (kSplit) {
-        // ---- cluster reduction: CTA r finishes channels [r*band, (r+1)*band) of the tile ----
+    if constexpr (kSplit) {
+        // ---- this CTA finishes its band: slices added in rank order, scaled, stored ----
         __syncwarp();
+        if (warp < 2 + kConvWarps) cluster_wait();           // (the epilogue warps did before their first remote access)
+        if (warp == 1) {                                     // the accumulator has been read by the four epilogue warps
+            mbar_wait(smem_u32(&bar_tempty[0]), 0, p.status, kDevTimeoutTmemEmpty);
+            __syncwarp();
+            tc_fence_after();
+            tmem_dealloc(tmem_base, Cfg::kTmemCols);
+        }
         pdl_wait();
-        cluster_sync_all();
-        const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
-        const int band = (kTileN + sched.splits - 1) / sched.splits;
-        const int r_beg = split_rank * band;
-        const int rows = min(kTileN, r_beg + band) - r_beg;
-        const bool healthy = (s_abort == 0);
+        if ((int)threadIdx.x >= band_rows * m_groups) return;
+        if (s_abort || !mbar_wait(smem_u32(&bar_recv), 0, p.status, kDevTimeoutPeer)) return;
+        const float in_scale = in_scale0;
+        const uint32_t slice = (uint32_t)band * Cfg::kPartPitch;
         // consecutive threads take consecutive channels, so the stores of one token coalesce
-        for (int i = threadIdx.x; i < rows * (MP / 4) && healthy; i += kSwapThreads) {
-            const int rl = i % rows;
-            const int mg = (i / rows) * 4;
-            const int n = first_tile * kTileN + r_beg + rl;
-            if (n >= p.N || mg >= p.M) continue;
-            const uint32_t local = smem_base + (uint32_t)(r_beg + rl) * Cfg::kPartPitch + (uint32_t)mg * 4;
-            // all slices' loads go out before the first add: remote shared memory is a long trip
-            float4 u[8];
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-                u[s] = s < sched.splits ? ld_cluster_f4(map_to_cta(local, (uint32_t)s)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = threadIdx.x; i < band_rows * m_groups; i += kSwapThreads) {
+            const int rl = i % band_rows;
+            const int mg = (i / band_rows) * 4;
+            const int n = first_tile * kTileN + split_rank * band + rl;
+            if (n >= p.N) continue;
+            const uint32_t local = smem_base + (uint32_t)rl * Cfg::kPartPitch + (uint32_t)mg * 4;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int s = 0; s < 8; ++s) { a.x += u[s].x; a.y += u[s].y; a.z += u[s].z; a.w += u[s].w; }
-            const float ws = __ldg(p.w_scale + n);
-            const float bs = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+            for (int sl = 0; sl < 8; ++sl) {
+                if (sl < sched.splits) {
+                    const float4 u = ld_shared_f4(local + (uint32_t)sl * slice);
+                    a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+                }
+            }
+            const bool first = i == (int)threadIdx.x;
+            const float ws = first ? ws0 : __ldg(p.w_scale + n);
+            const float bs = first ? bs0 : (p.bias ? __bfloat162float(p.bias[n]) : 0.f);
             const float o[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 if (mg + j < p.M) p.y[(size_t)(mg + j) * p.ldy + n] = __float2bfloat16_rn(fmaf(o[j] * in_scale, ws, bs));
         }
-        cluster_sync_all();
+        return;
     }
 
     tc_fence_before();

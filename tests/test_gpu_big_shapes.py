@@ -92,6 +92,9 @@ PREFILL = [
     (32640, 3584, 4608, 1, "umma_pair"),           # ragged M on CTA pairs: the last pair has one live CTA row block
     (4096, 3584, 37888, None, "umma_pair"),        # gate_up on CTA pairs (148 column tiles)
     (32640, 18944, 3584, None, "umma_pair"),
+    (16384, 3584, 576, None, "umma_w8a8_128x256"), # qkv and gate_up column shards of 8 ranks (N = 4.5 and 37 tiles of 128)
+    (16384, 3584, 4736, None, "umma_pair"),
+    (16384, 2368, 3584, None, "+half"),            # down's K shard of 8 ranks: 18.5 K blocks
 ]
 
 
@@ -317,3 +320,47 @@ def test_graph_captured_before_the_scratch_grows_still_replays_correctly():
                 raised.append(str(exc))
         assert raised and "capture" in raised[0]
     assert_parity(from_bf16(want), oracle_linear("fp8_w8a8_static", small), "graph replay")
+
+
+# (ranks, rows, K per rank, N): the last two are the 8-rank shards of the 7B down and o_proj layers at 16384 rows
+BANDED = [(3, 1000, 256, 264), (8, 1000, 448, 576), (5, 4100, 1408, 520), (8, 16384, 2368, 3584), (8, 16384, 448, 3584)]
+
+
+@pytest.mark.parametrize("tp,rows,k,n", BANDED)
+def test_row_parallel_bands_of_many_ranks_emulated_on_one_gpu(tp, rows, k, n):
+    """The reduce-scatter epilogue and the slot sum of RowParallelLinear at rank counts no box offered, with every
+    rank's buffer in this GPU's memory and the ranks run one after the other: rank r's GEMM stores band d of its
+    partial result into slot r of rank d's buffer, rank d adds its slots in order and stores the band to every
+    rank's output.  Must equal, bit for bit, the plain GEMMs' bf16 partials added in rank order in fp32."""
+    Kn = kernels()
+    cases = [big_case(31 * r + tp + k, rows, k, n) for r in range(tp)]
+    in_scale = cases[0]["input_scale"]
+    band = -(-(-(-rows // tp)) // 32) * 32                    # rows per band as the layer rounds them
+    slot = band * n
+    bufs = [torch.full((tp * slot + rows * n,), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(tp)]
+    for r, d in enumerate(cases):
+        dst = [bufs[o].data_ptr() + r * slot * 2 for o in range(tp)]
+        Kn.launch_w8a8_reduce_scatter(d["x"], d["w_nk"], in_scale, d["w_scale"], d["bias"] if r == 0 else None, dst, n, band)
+    ys = [b.data_ptr() + tp * slot * 2 for b in bufs]
+    for r in range(tp):
+        mine = max(0, min(band, rows - r * band))
+        Kn.sum_slots_gather(bufs[r].data_ptr(), tp, slot, n, ys, n, r * band, mine, n, torch.device("cuda", 0))
+    torch.cuda.synchronize()
+    want = torch.zeros((rows, n), dtype=torch.float32, device="cuda")
+    for r, d in enumerate(cases):
+        want += Kn.launch_w8a8_gemm(d["x"], d["w_nk"], in_scale, d["w_scale"], d["bias"] if r == 0 else None).float()
+    want = want.to(torch.bfloat16)
+    for r in range(tp):
+        got = bufs[r][tp * slot:].view(rows, n)
+        assert torch.equal(got, want), f"rank {r}: {(got != want).sum().item()} elements differ"
+    # and the sum against the oracle on sampled rows and columns
+    rng = np.random.default_rng(rows + n)
+    ri, ci = sample(rows, 24, rng), sample(n, 96, rng)
+    ref = np.zeros((len(ri), len(ci)), dtype=np.float32)
+    for r, d in enumerate(cases):
+        x = from_bf16(d["x"][torch.from_numpy(ri).cuda()])
+        ct = torch.from_numpy(ci).cuda()
+        b = from_bf16(d["bias"][ct]) if r == 0 else None
+        ref += O.linear_w8a8(x, d["q"][ct].cpu().numpy(), d["w_scale"][ct].cpu().numpy(), np.float32(in_scale.item()), b)
+    got = from_bf16(bufs[0][tp * slot:].view(rows, n)[torch.from_numpy(ri).cuda()][:, torch.from_numpy(ci).cuda()])
+    assert_parity(got, O.bf16_round(ref), f"{tp} ranks {rows}x{k}x{n}", ulps=float(tp))
