@@ -424,14 +424,26 @@ SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq)
             if (preq) slots = pl.mp == 16 ? swap_max_clusters<16, true>(s) : (pl.mp == 32 ? swap_max_clusters<32, true>(s) : swap_max_clusters<64, true>(s));
             else slots = pl.mp == 16 ? swap_max_clusters<16, false>(s) : (pl.mp == 32 ? swap_max_clusters<32, false>(s) : swap_max_clusters<64, false>(s));
         }
+        // The occupancy query answers as if one CTA had an SM to itself (74 clusters of two, 15 of eight) whatever the
+        // kernel's shared memory; two CTAs of the 16-row kernel do share an SM (86 clusters of two run as one wave:
+        // 7.9 us against 10.9 us unsplit on 2048 -> 11008), so for that kernel the figure is doubled.
+        if (s > 1 && pl.mp == 16) slots *= 2;
         if (slots < 1) slots = 1;
-        // with two CTAs per SM a second wave of clusters trickles in as slots free up, so a
-        // fractional wave count models it better than a ceiling (measured on 18944 -> 3584)
-        double waves = (double)pl.n_tiles / slots;
-        if (pl.mp != 16) waves = (pl.n_tiles + slots - 1) / slots;
-        if (waves < 1.0) waves = 1.0;
-        // K blocks per CTA plus a fixed cost (launch, first loads, epilogue; cluster reduction when split)
-        const double cost = waves * kps + (s > 1 ? 8.0 : 6.0);
+        // Time of one wave of clusters, in microseconds: the K blocks of a slice at the rate the resident CTAs share
+        // the HBM stream (a CTA alone is bound by its ring and the MMA issue rate: 0.32 us per 16 KB block, more with
+        // wider token tiles), plus what every wave pays once -- ramp, the hand-over of the partial sums (grows with
+        // rows x slices), drain.  A wave does not overlap the next: 86 tiles x 3 slices of 64-row tiles in two waves
+        // took 19.3 us where one wave of unsplit tiles takes 11.0.  Fitted to a sweep of all slice counts over
+        // 3584 -> 4608 / 3584 / 9472 / 18944, 2048 -> 11008 / 5632, 4736 / 11008 / 18944 -> 2048 or 3584 at 1, 16, 64 rows.
+        const int ctas = pl.n_tiles * s;
+        const int resident = ctas < slots * s ? ctas : slots * s;
+        // (rows converted inside the kernel add to a lone CTA's block time: 0.45 us at 16 rows)
+        const double alone = (pl.mp == 16 ? 0.32 : (pl.mp == 32 ? 0.36 : 0.40)) + (preq ? 0.0 : 0.008 * (double)(M < 16 ? M : 16));
+        const double shared = 16384.0 * resident / 6.5e6;
+        const double t_block = shared > alone ? shared : alone;
+        const int waves = (pl.n_tiles + slots - 1) / slots;
+        const double fixed = 3.5 + (s > 1 ? 0.5 + (0.1 + 0.006 * (double)M) * s : 0.0);
+        const double cost = waves * (kps * t_block + fixed);
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
     // Long K over few channel tiles (18944 -> 3584: 28 tiles x 148 K blocks), two CTAs per SM: measured
