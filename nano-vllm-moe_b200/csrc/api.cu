@@ -72,10 +72,12 @@ int validate_common(const void* x, int64_t ldx, const void* w, const float* w_sc
     return FP8LIN_OK;
 }
 
-bool w8a16_swap_eligible(int64_t M) {
-    // measured: the mma.sync kernel wins up to 32 rows (27 vs 34 us on 3584 -> 37888 at M = 16,
-    // equal at 32), the tcgen05 kernel from 33 rows (39 vs 67 us at M = 64)
-    const int min_m = g_tune.w8a16_swap_min_m >= 0 ? g_tune.w8a16_swap_min_m : 33;
+bool w8a16_swap_eligible(int64_t M, int64_t N) {
+    // measured (us, mma.sync kernel / tcgen05 kernel): at 32 rows 3584 -> 4608 11.4 / 10.4, 3584 -> 3584 11.4 / 9.1,
+    // 18944 -> 3584 29.8 / 23.5, 3584 -> 37888 34.1 / 34.4; at 16 rows 9.5 / 9.7, 9.4 / 8.5, 21.6 / 22.7, 26.8 / 33.6;
+    // at 64 rows on 3584 -> 37888 67 / 38.  So: from 17 rows, from 33 when there is a channel tile for every SM.
+    const int wide = (N + 127) / 128 >= fp8lin::sm_count();
+    const int min_m = g_tune.w8a16_swap_min_m >= 0 ? g_tune.w8a16_swap_min_m : (wide ? 33 : 17);
     return g_tune.w8a16_swap_enable != 0 && M >= min_m && M <= 64;
 }
 
@@ -315,7 +317,7 @@ int fp8lin_w8a16(const void* x, int64_t ldx, const void* w_nk, const float* w_sc
                  void* stream) {
     int rc = validate_common(x, ldx, w_nk, w_scale, bias, y, ldy, M, K, N);
     if (rc != FP8LIN_OK || M == 0) return rc;
-    if (w8a16_swap_eligible(M) && workspace) {
+    if (w8a16_swap_eligible(M, N) && workspace) {
         SwapPlan sp = plan_swap_w8a16(M, K, N, g_tune.swap_splits);
         UmmaArgs a;
         a.xq = nullptr; a.w = (const unsigned char*)w_nk; a.w_scale = w_scale; a.input_scale = nullptr;
@@ -710,7 +712,7 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N) {
         snprintf(buf, sizeof(buf), "umma_w8a16_f16_128x%d_s%d_c%d", pl.bn, pl.splits, (int)c.n_chunks);
         return buf;
     }
-    if (scheme == FP8LIN_W8A16 && w8a16_swap_eligible(M)) {
+    if (scheme == FP8LIN_W8A16 && w8a16_swap_eligible(M, N)) {
         SwapPlan pl = plan_swap_w8a16(M, K, N, g_tune.swap_splits);
         snprintf(buf, sizeof(buf), "umma_swap_w8a16_m%d_s%d", pl.mp, pl.splits);
         return buf;

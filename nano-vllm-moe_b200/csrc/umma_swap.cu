@@ -56,9 +56,9 @@ struct SwapCfg {
     static constexpr int kRingBytes = kStages * kStageBytes;
     static constexpr int kSmemBytes = kRingBytes + 1024;
     static constexpr int kTmemCols = 2 * MP < 32 ? 32 : 2 * MP;
-    static constexpr int kPartPitch = MP * 4 + 16;               // parked fp32 tile row pitch (split-K)
+    static constexpr int kPartPitch = MP * 4 + 16;               // row pitch of the received fp32 partial sums (split-K)
     static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment for the swizzle");
-    static_assert(kTileN * kPartPitch <= kRingBytes, "parked tile must fit in the ring");
+    static_assert((kTileN + 8) * kPartPitch <= kRingBytes, "the received slices of a band must fit in the ring");
 };
 
 struct SwapSched {

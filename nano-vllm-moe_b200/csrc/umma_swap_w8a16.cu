@@ -19,8 +19,9 @@
 //                block, A from TMEM, B from shared memory.
 //   warps 10..13 epilogue: as in the W8A8 kernel, y[m][n] = bf16(acc * w_scale[n] + bias[n]).
 //
-// Persistent over the N/128 channel tiles or cluster split-K over DSMEM, bounded waits,
-// programmatic dependent launch: all as in umma_swap.cu.
+// Persistent over the N/128 channel tiles or cluster split-K with the partial sums pushed to the
+// CTA that finishes a band (st.async, no cluster barrier after set-up), bounded waits, programmatic
+// dependent launch: all as in umma_swap.cu.
 #include "umma_common.cuh"
 
 namespace fp8lin {
@@ -46,7 +47,7 @@ struct Swap16Cfg {
     static constexpr int kPartPitch = MP * 4 + 16;
     static_assert(kAccCols + kStages * kACols <= kTmemCols, "TMEM budget");
     static_assert(kStageBytes % 1024 == 0, "stage alignment");
-    static_assert(kS16Tile * kPartPitch <= kRingBytes, "parked tile must fit in the ring");
+    static_assert((kS16Tile + 8) * kPartPitch <= kRingBytes, "the received slices of a band must fit in the ring");
 };
 
 struct Swap16Sched {
@@ -107,6 +108,8 @@ swap_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     __shared__ __align__(8) uint64_t bar_empty[S];    // MMAs that read the slot are done
     __shared__ __align__(8) uint64_t bar_tfull[2];
     __shared__ __align__(8) uint64_t bar_tempty[2];
+    __shared__ __align__(8) uint64_t bar_ready;       // split-K: every CTA of the cluster is past its MMAs
+    __shared__ __align__(8) uint64_t bar_recv;        // split-K: the partials of this CTA's band have landed
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile int s_abort;
 
@@ -120,6 +123,9 @@ swap_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     const int kb0 = split_rank * sched.kblocks_per_split;
     const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
     const uint32_t x_bytes = (uint32_t)p.M * 256u;
+    const int band = kSplit ? (kS16Tile + sched.splits - 1) / sched.splits : kS16Tile;
+    const int band_rows = kSplit ? min(kS16Tile, (split_rank + 1) * band) - split_rank * band : 0;
+    const int m_groups = (p.M + 3) >> 2;
     constexpr uint32_t kXfOff = Cfg::kWBytes;
     constexpr uint32_t kXrawOff = Cfg::kWBytes + Cfg::kXfBytes;
 
@@ -131,6 +137,11 @@ swap_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         }
         for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bar_tfull[i]), 1); mbar_init(smem_u32(&bar_tempty[i]), 4); }
         s_abort = 0;
+        if (kSplit) {
+            mbar_init(smem_u32(&bar_ready), (uint32_t)sched.splits);
+            mbar_init(smem_u32(&bar_recv), 1);
+            mbar_expect_tx(smem_u32(&bar_recv), (uint32_t)(sched.splits * band_rows * m_groups * 16));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -147,6 +158,18 @@ swap_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     const uint32_t tmem_base = s_tmem_base;
     const uint32_t tmem_a0 = tmem_base + Cfg::kAccCols;            // first widened-weight buffer
     pdl_launch_dependents();
+    if (kSplit) cluster_arrive();                            // (waited for before the first remote access)
+    // scale and bias of the first channel this thread finishes, fetched long before they are needed
+    float ws0 = 0.f, bs0 = 0.f;
+    if constexpr (kSplit) {
+        if (band_rows > 0 && (int)threadIdx.x < band_rows * m_groups) {
+            const int n0 = first_tile * kS16Tile + split_rank * band + (int)threadIdx.x % band_rows;
+            if (n0 < p.N) {
+                ws0 = __ldg(p.w_scale + n0);
+                if (p.bias) bs0 = __bfloat162float(p.bias[n0]);
+            }
+        }
+    }
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -303,44 +326,58 @@ swap_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
                         if (m < p.M) p.y[(size_t)m * p.ldy + n] = __float2bfloat16_rn(fmaf(__uint_as_float(v[m]), ws, bs));
                 }
             } else {
-                const uint32_t dst = smem_base + (uint32_t)(q * 32 + lane) * Cfg::kPartPitch;
+                // this CTA's ring is free: tell every peer, wait for all of them, push each channel's sums to its owner
+                cluster_wait();
+                if (q == 0 && lane < sched.splits) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_ready), (uint32_t)lane));
+                if (!mbar_wait(smem_u32(&bar_ready), 0, p.status, kDevTimeoutPeer)) { s_abort = 1; ok = false; break; }
+                const int c = q * 32 + lane;
+                const uint32_t owner = (uint32_t)(c / band);
+                const uint32_t dst = map_to_cta(smem_base + (uint32_t)(split_rank * band + (c - (int)owner * band)) * Cfg::kPartPitch, owner);
+                const uint32_t rbar = map_to_cta(smem_u32(&bar_recv), owner);
 #pragma unroll
                 for (int m = 0; m < MP; m += 4)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + m * 4), "r"(v[m]), "r"(v[m + 1]),
-                                 "r"(v[m + 2]), "r"(v[m + 3]) : "memory");
+                    if (m < p.M) st_async_v4(dst + m * 4, v[m], v[m + 1], v[m + 2], v[m + 3], rbar);
             }
         }
     }
 
-    if (kSplit) {
+    if constexpr (kSplit) {
+        // ---- this CTA finishes its band: slices added in rank order, scaled, stored ----
         __syncwarp();
+        if (warp < 2 + kS16ConvWarps) cluster_wait();        // (the epilogue warps did before their first remote access)
+        if (warp == 1) {                                     // the accumulator has been read by the four epilogue warps
+            mbar_wait(smem_u32(&bar_tempty[0]), 0, p.status, kDevTimeoutTmemEmpty);
+            __syncwarp();
+            tc_fence_after();
+            tmem_dealloc(tmem_base, Cfg::kTmemCols);
+        }
         pdl_wait();
-        cluster_sync_all();
-        const int band = (kS16Tile + sched.splits - 1) / sched.splits;
-        const int r_beg = split_rank * band;
-        const int rows = min(kS16Tile, r_beg + band) - r_beg;
-        const bool healthy = (s_abort == 0);
-        for (int i = threadIdx.x; i < rows * (MP / 4) && healthy; i += kS16Threads) {
-            const int rl = i % rows;
-            const int mg = (i / rows) * 4;
-            const int n = first_tile * kS16Tile + r_beg + rl;
-            if (n >= p.N || mg >= p.M) continue;
-            const uint32_t local = smem_base + (uint32_t)(r_beg + rl) * Cfg::kPartPitch + (uint32_t)mg * 4;
-            float4 u[8];
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-                u[s] = s < sched.splits ? ld_cluster_f4(map_to_cta(local, (uint32_t)s)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if ((int)threadIdx.x >= band_rows * m_groups) return;
+        if (s_abort || !mbar_wait(smem_u32(&bar_recv), 0, p.status, kDevTimeoutPeer)) return;
+        const uint32_t slice = (uint32_t)band * Cfg::kPartPitch;
+        for (int i = threadIdx.x; i < band_rows * m_groups; i += kS16Threads) {
+            const int rl = i % band_rows;
+            const int mg = (i / band_rows) * 4;
+            const int n = first_tile * kS16Tile + split_rank * band + rl;
+            if (n >= p.N) continue;
+            const uint32_t local = smem_base + (uint32_t)rl * Cfg::kPartPitch + (uint32_t)mg * 4;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int s = 0; s < 8; ++s) { a.x += u[s].x; a.y += u[s].y; a.z += u[s].z; a.w += u[s].w; }
-            const float ws = __ldg(p.w_scale + n);
-            const float bs = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+            for (int sl = 0; sl < 8; ++sl) {
+                if (sl < sched.splits) {
+                    const float4 u = ld_shared_f4(local + (uint32_t)sl * slice);
+                    a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+                }
+            }
+            const bool first = i == (int)threadIdx.x;
+            const float ws = first ? ws0 : __ldg(p.w_scale + n);
+            const float bs = first ? bs0 : (p.bias ? __bfloat162float(p.bias[n]) : 0.f);
             const float o[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 if (mg + j < p.M) p.y[(size_t)(mg + j) * p.ldy + n] = __float2bfloat16_rn(fmaf(o[j], ws, bs));
         }
-        cluster_sync_all();
+        return;
     }
 
     tc_fence_before();
@@ -389,8 +426,15 @@ SwapPlan plan_swap_w8a16(int64_t M, int64_t K, int64_t N, int force_splits) {
         int slots = sm_count();
         if (s > 1) slots = pl.mp == 16 ? swap16_max_clusters<16>(s) : (pl.mp == 32 ? swap16_max_clusters<32>(s) : swap16_max_clusters<64>(s));
         if (slots < 1) slots = 1;
+        // microseconds per wave of clusters, as in plan_swap; a CTA alone is bound by the widening of its weight
+        // tiles (0.52 us per 16 KB block), and waves do not overlap
+        const int ctas = pl.n_tiles * s;
+        const int resident = ctas < slots * s ? ctas : slots * s;
+        const double shared = 16384.0 * resident / 6.5e6;
+        const double t_block = shared > 0.52 ? shared : 0.52;
         const int waves = (pl.n_tiles + slots - 1) / slots;
-        const double cost = (double)waves * kps + (s > 1 ? 8.0 : 6.0);
+        const double fixed = 3.5 + (s > 1 ? 0.5 + (0.1 + 0.006 * (double)M) * s : 0.0);
+        const double cost = waves * (kps * t_block + fixed);
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
     pl.splits = best_s;
