@@ -96,6 +96,9 @@ struct UmmaArgs {
     int q_row_start = 0;
     int q_lead = 0;
     int* q_ctrl = nullptr;
+    // decode gate_up form of the swapped-operand kernel: e4m3 h = silu(gate) * up, [M][N / 2], written instead of y
+    unsigned char* hq = nullptr;
+    const float* h_scale = nullptr;
 };
 
 struct UmmaPlan {
@@ -163,6 +166,8 @@ struct SwapPlan {
 SwapPlan plan_swap(int64_t M, int64_t K, int64_t N, int force_splits, bool preq);
 // `a.partial`, `a.counters` are unused (split-K is reduced through cluster shared memory); `a.xq`
 // only when plan.preq.
+// Up to 16 pre-quantised rows (a.xq) through a gate_up projection with interleaved tile rows: writes a.hq (see UmmaArgs).
+cudaError_t launch_swap_gate_up(const UmmaArgs& a, cudaStream_t stream, const char** why);
 cudaError_t launch_swap_w8a8(const SwapPlan& plan, const UmmaArgs& a, const void* x, int64_t ldx,
                              cudaStream_t stream, const char** why);
 

@@ -43,7 +43,11 @@ constexpr int kKB = 128;      // K elements per block
 // kPreQ: the activations were quantised by a pass before the kernel and arrive as ready MMA "B"
 // tiles by TMA; no raw block, no converter work, so more ring slots fit (used for 33..64 rows,
 // where the raw block would leave only five slots).
-template <int MP, bool kPreQ = false>
+// kGateUp (16-row tiles, pre-quantised rows): the weights are a gate_up projection with its 128-channel tile rows
+// alternating gate / up; a CTA takes tile PAIRS, gate into one accumulator stage and up into the other, and its
+// epilogue writes e4m3 h = silu(gate) * up for the down projection instead of y.  One CTA per SM with a ring twice as
+// deep (the same bytes in flight per SM as two CTAs), because both tiles of a pair must meet in one CTA.
+template <int MP, bool kPreQ = false, bool kGateUp = false>
 struct SwapCfg {
     static constexpr int kWBytes = kTileN * kKB;                 // 16 KB e4m3 weight tile
     static constexpr int kXqBytes = MP * kKB;                    // quantised activation tile (MMA B)
@@ -51,8 +55,9 @@ struct SwapCfg {
     static constexpr int kStageBytes = kWBytes + kXqBytes + kXrawBytes;
     // M <= 16: two CTAs share an SM (5 stages each, 160 KB of weights in flight per SM), so the
     // CTAs of the next kernel can start on an SM while this kernel's other CTA is still draining
-    static constexpr int kCtasPerSm = MP <= 16 ? 2 : 1;
-    static constexpr int kStages = kPreQ ? (MP <= 16 ? 6 : 9) : (MP <= 16 ? 5 : (MP <= 32 ? 7 : 5));
+    static constexpr int kCtasPerSm = (MP <= 16 && !kGateUp) ? 2 : 1;
+    static constexpr int kStages = kGateUp ? 12 : (kPreQ ? (MP <= 16 ? 6 : 9) : (MP <= 16 ? 5 : (MP <= 32 ? 7 : 5)));
+    static_assert(!kGateUp || (kPreQ && MP == 16), "the gate_up form exists for 16-row tiles of pre-quantised rows");
     static constexpr int kRingBytes = kStages * kStageBytes;
     static constexpr int kSmemBytes = kRingBytes + 1024;
     static constexpr int kTmemCols = 2 * MP < 32 ? 32 : 2 * MP;
@@ -86,11 +91,12 @@ __device__ __forceinline__ void tmem_ld_cols<64>(uint32_t taddr, uint32_t* v) {
 // converter warps that share one K block: one lane per (row, 16-element chunk) of the M real rows
 __host__ __device__ inline int conv_team(int m) { return m <= 4 ? 1 : (m <= 8 ? 2 : (m <= 16 ? 4 : 8)); }
 
-template <int MP, bool kSplit, bool kPreQ = false>
-__global__ void __launch_bounds__(kSwapThreads, SwapCfg<MP, kPreQ>::kCtasPerSm)
+template <int MP, bool kSplit, bool kPreQ = false, bool kGateUp = false>
+__global__ void __launch_bounds__(kSwapThreads, SwapCfg<MP, kPreQ, kGateUp>::kCtasPerSm)
 swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  UmmaArgs p, SwapSched sched) {
-    using Cfg = SwapCfg<MP, kPreQ>;
+    static_assert(!(kGateUp && kSplit), "tile pairs are not split along K");
+    using Cfg = SwapCfg<MP, kPreQ, kGateUp>;
     // bytes of activations one K block brings in: M real rows, raw bf16 or ready e4m3
     const uint32_t x_bytes = (uint32_t)p.M * (kPreQ ? 128u : 256u);
     constexpr uint32_t kXDst = Cfg::kWBytes + (kPreQ ? 0 : Cfg::kXqBytes);   // where the TMA puts them
@@ -111,8 +117,12 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const int lane = threadIdx.x & 31;
 
     const int split_rank = kSplit ? (int)cluster_ctarank() : 0;
-    const int first_tile = kSplit ? (int)(blockIdx.x / sched.splits) : (int)blockIdx.x;
+    const int first_tile = kSplit ? (int)(blockIdx.x / sched.splits) : (kGateUp ? 2 * (int)blockIdx.x : (int)blockIdx.x);
     const int tile_step = kSplit ? sched.n_tiles : (int)gridDim.x;
+    // the tl-th tile of this CTA: every gridDim.x-th tile, or (gate_up form) both tiles of every gridDim.x-th pair
+    auto tile_of = [&](int tl) -> int {
+        return kGateUp ? 2 * ((int)blockIdx.x + (tl >> 1) * (int)gridDim.x) + (tl & 1) : first_tile + tl * tile_step;
+    };
     const int kb0 = split_rank * sched.kblocks_per_split;
     const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
     // split-K: CTA r of the cluster finishes channels [r * band, r * band + band_rows) of the tile; a slice's partials
@@ -185,7 +195,9 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     tma_load_2d(smem_base + i * Cfg::kStageBytes + kXDst, &tmap_x,
                                 (kb0 + i) * kKB, 0, smem_u32(&bar_full[i]));
             }
-            for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step) {
+            for (int tl = 0; ok; ++tl) {
+                const int t = tile_of(tl);
+                if (t >= sched.n_tiles) break;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     if (it < (uint32_t)first_kb) continue;                       // issued above
                     const int st = it % S;
@@ -210,9 +222,9 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_mn(kTileN, MP, 0, 0);
             uint32_t it = 0;
-            int tl = 0;
             bool ok = true;
-            for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step, ++tl) {
+            for (int tl = 0; ok; ++tl) {
+                if (tile_of(tl) >= sched.n_tiles) break;
                 const int as = tl & 1;
                 const uint32_t aph = (tl >> 1) & 1;
                 if (s_abort || !mbar_wait(smem_u32(&bar_tempty[as]), aph ^ 1, p.status, kDevTimeoutTmemEmpty)) {
@@ -250,7 +262,8 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int items = p.M * 8;                          // (row, 16-element chunk) pairs of the real rows
         uint32_t it = 0;
         bool ok = true;
-        for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step) {
+        for (int tl = 0; ok; ++tl) {
+            if (tile_of(tl) >= sched.n_tiles) break;
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 // a ring slot always belongs to the same warp, so every warp sees the phases of
                 // the barriers it waits on in order (a parity wait may only look one phase ahead)
@@ -285,9 +298,58 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         pdl_wait();                                          // y may still be read by the predecessor
         const int q = warp & 3;
         const float in_scale = fmaxf(__ldg(p.input_scale), 1e-12f);
-        int tl = 0;
         bool ok = true;
-        for (int t = first_tile; t < sched.n_tiles && ok; t += tile_step, ++tl) {
+        if constexpr (kGateUp) {
+            // ---- pairs of tiles: h = silu(gate) * up, quantised for the down projection ----
+            const ExactDiv div_h(fmaxf(__ldg(p.h_scale), 1e-12f));
+            const int inter = p.N >> 1;
+            for (int tl = 0; ok; tl += 2) {
+                const int t = tile_of(tl);
+                if (t >= sched.n_tiles) break;
+                const uint32_t aph = (tl >> 1) & 1;
+                const int ng = t * kTileN + q * 32 + lane, nu = ng + kTileN;     // (N is a multiple of 256: both in range)
+                const float wg = __ldg(p.w_scale + ng), wu = __ldg(p.w_scale + nu);
+                const float bg = p.bias ? __bfloat162float(p.bias[ng]) : 0.f, bu = p.bias ? __bfloat162float(p.bias[nu]) : 0.f;
+                uint32_t vg[MP], vu[MP];
+                if (!mbar_wait(smem_u32(&bar_tfull[0]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
+                tc_fence_after();
+                __syncwarp();
+                tmem_ld_cols<MP>(tmem_base + ((uint32_t)(q * 32) << 16), vg);
+                tmem_ld_wait();
+                if (!mbar_wait(smem_u32(&bar_tfull[1]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
+                tc_fence_after();
+                __syncwarp();
+                tmem_ld_cols<MP>(tmem_base + ((uint32_t)(q * 32) << 16) + MP, vu);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(smem_u32(&bar_tempty[0])); mbar_arrive(smem_u32(&bar_tempty[1])); }
+                // the values and roundings of the two-step form: gate and up rounded to bf16, then bf16(silu(g) * u)
+                unsigned char* hcol = p.hq + (size_t)(t >> 1) * kTileN + q * 32 + lane;
+#pragma unroll
+                for (int m0 = 0; m0 < MP; m0 += 8) {
+                    if (m0 >= p.M) break;
+                    uint4 hv;
+                    uint32_t* hw = reinterpret_cast<uint32_t*>(&hv);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int m = m0 + 2 * j;
+                        const uint32_t gp = pack_bf16x2(fmaf(__uint_as_float(vg[m]) * in_scale, wg, bg), fmaf(__uint_as_float(vg[m + 1]) * in_scale, wg, bg));
+                        const uint32_t up = pack_bf16x2(fmaf(__uint_as_float(vu[m]) * in_scale, wu, bu), fmaf(__uint_as_float(vu[m + 1]) * in_scale, wu, bu));
+                        const float g0 = bf16_lo(gp), g1 = bf16_hi(gp);
+                        const float s0 = g0 / (1.f + expf(-g0)), s1 = g1 / (1.f + expf(-g1));
+                        hw[j] = pack_bf16x2(s0 * bf16_lo(up), s1 * bf16_hi(up));
+                    }
+                    const uint2 qd = quant8_e4m3(hv, div_h);
+#pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        if (m0 + r < p.M) hcol[(size_t)(m0 + r) * inter] = (unsigned char)(((r < 4 ? qd.x : qd.y) >> (8 * (r & 3))) & 0xffu);
+                }
+            }
+        } else
+        for (int tl = 0; ok; ++tl) {
+            const int t = tile_of(tl);
+            if (t >= sched.n_tiles) break;
             const int as = tl & 1;
             const uint32_t aph = (tl >> 1) & 1;
             const int n = t * kTileN + q * 32 + lane;
@@ -492,6 +554,40 @@ static cudaError_t launch_swap(const SwapPlan& pl, const UmmaArgs& a, const CUte
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
+    return counted(cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s));
+}
+
+cudaError_t launch_swap_gate_up(const UmmaArgs& a, cudaStream_t stream, const char** why) {
+    using Cfg = SwapCfg<16, true, true>;
+    if (a.M < 1 || a.M > 16 || a.N % 256 != 0 || !a.hq || !a.h_scale || !a.xq) {
+        if (why) *why = "the gate_up form takes 1..16 pre-quantised rows and an even number of 128-channel tiles";
+        return cudaErrorInvalidValue;
+    }
+    CUtensorMap tw, tx;
+    bool ok = encode_u8_2d(&tw, a.w, (uint64_t)(pack_ntiles(a.N) * pack_kblocks(a.K) * 128), 128, kTileN);
+    ok = ok && encode_u8_2d(&tx, a.xq, (uint64_t)a.M, (uint64_t)a.K, (uint32_t)a.M);
+    if (!ok) {
+        if (why) *why = "cuTensorMapEncodeTiled failed";
+        return cudaErrorInvalidValue;
+    }
+    auto kern = swap_w8a8_kernel<16, false, true, true>;
+    static SmemOptIn opted;
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kSmemBytes, opted);
+        if (e != cudaSuccess) return e;
+    }
+    SwapSched s;
+    s.n_tiles = (int)pack_ntiles(a.N); s.splits = 1;
+    s.kblocks_total = (a.K + kKB - 1) / kKB; s.kblocks_per_split = s.kblocks_total;
+    const int pairs = s.n_tiles / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(pairs < sm_count() ? pairs : sm_count()));
+    cfg.blockDim = dim3(kSwapThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    cfg.numAttrs = pdl_attribute(attr);
+    cfg.attrs = attr;
     return counted(cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s));
 }
 

@@ -138,3 +138,26 @@ def test_fused_mlp_layer_matches_separate_layers():
                      down["wq"], down["w_scale"], down["input_scale"], down["bias"])
     assert_parity(y, ref, "fused mlp layer", ulps=3.0, min_cos=0.9999)
     assert_parity(y, sep, "fused mlp layer vs separate layers", ulps=3.0, min_cos=0.9999)
+
+
+@pytest.mark.parametrize("m,h,inter,n", [(1, 512, 384, 512), (5, 448, 256, 264), (16, 512, 1408, 520), (3, 3584, 18944, 3584)])
+def test_fused_mlp_from_codes_on_decode_rows(m, h, inter, n):
+    """Up to 16 pre-quantised rows, with and without the opt-in form in which the decode kernel takes (gate, up)
+    tile pairs and writes e4m3 h itself: same bits as the default (a separate silu-multiply-quantise pass), and
+    parity with the oracle."""
+    Kn = kernels()
+    gu, down = make_mlp_case(8200 + m + h + inter, m, h, inter, n)
+    d = upload_mlp(gu, down, inter)
+    codes = Kn.quantize_activation(d["x"], d["in_gu"])
+    args = (codes, d["w_il"], d["s_il"], d["in_gu"], d["b_il"], d["w_d"], d["s_d"], d["in_d"], d["b_d"])
+    y = Kn.launch_mlp_w8a8(*args)
+    Kn.set_tuning("mlp_decode_fused", 1)
+    try:
+        y_one = Kn.launch_mlp_w8a8(*args)
+    finally:
+        Kn.set_tuning("mlp_decode_fused", -1)
+    assert torch.equal(y, y_one)
+    assert torch.equal(y, Kn.launch_mlp_w8a8(*args))
+    ref = O.mlp_w8a8(gu["x"], gu["wq"], gu["w_scale"], gu["input_scale"], gu["bias"],
+                     down["wq"], down["w_scale"], down["input_scale"], down["bias"])
+    assert_parity(from_bf16(y), ref, f"decode mlp from codes {m}x{h}x{inter}x{n}", ulps=3.0, min_cos=0.9999)
