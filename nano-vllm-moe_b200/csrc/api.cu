@@ -542,11 +542,12 @@ static int mlp_w8a8_impl(const void* x, int64_t ldx, bool x_is_e4m3, const void*
     cudaStream_t st = (cudaStream_t)stream;
     unsigned char* hq = ws.body + l.hq_off;
     if (x_is_e4m3 && M <= 16 && g_tune.mlp_decode_fused > 0) {
-        // Opt-in: up to 16 pre-quantised rows, the decode kernel takes gate and up tile pairs and writes e4m3 h itself
-        // (one launch fewer, no bf16 gate_up round trip, same bits).  Off by default: both tiles of a pair must meet in
-        // one CTA, so the kernel runs one CTA per SM with a ring twice as deep, and that streams the 136 MB gate_up
-        // weights of a 7B layer slower than two independent CTAs per SM do -- measured 58.6 us per decoder layer
-        // against 55.5 us with the separate 3 us activation pass (one row, 28 layers under one CUDA graph).
+        // Opt-in: up to 16 pre-quantised rows, clusters of two CTAs of the decode kernel take (gate, up) tile pairs, the
+        // up CTA hands its values to the gate CTA, which writes e4m3 h itself (one launch fewer, no bf16 gate_up round
+        // trip, same bits).  Off by default, it buys nothing: 55.9 us per 7B decoder layer at one row against 55.5 us
+        // with the separate 3 us activation pass (58.7 against 58.3 at 16 rows; 28 layers under one CUDA graph) -- the
+        // hand-over buffer costs the ring its sixth slot and the hand-over sits on the kernel's tail.  A first form
+        // (both tiles in one CTA with a 12-slot ring, one CTA per SM) was slower still: 58.6 us.
         UmmaArgs a;
         a.xq = (const unsigned char*)x; a.w = (const unsigned char*)w_gate_up; a.w_scale = gate_up_scale; a.input_scale = gate_up_input_scale;
         a.bias = (const __nv_bfloat16*)gate_up_bias; a.y = nullptr; a.partial = nullptr; a.counters = nullptr;

@@ -44,9 +44,10 @@ constexpr int kKB = 128;      // K elements per block
 // tiles by TMA; no raw block, no converter work, so more ring slots fit (used for 33..64 rows,
 // where the raw block would leave only five slots).
 // kGateUp (16-row tiles, pre-quantised rows): the weights are a gate_up projection with its 128-channel tile rows
-// alternating gate / up; a CTA takes tile PAIRS, gate into one accumulator stage and up into the other, and its
-// epilogue writes e4m3 h = silu(gate) * up for the down projection instead of y.  One CTA per SM with a ring twice as
-// deep (the same bytes in flight per SM as two CTAs), because both tiles of a pair must meet in one CTA.
+// alternating gate / up.  Clusters of two CTAs take tile PAIRS: CTA 0 the gate tile, CTA 1 the up tile.  The up CTA's
+// epilogue sends its bf16 results to the gate CTA (st.async into a 4 KB buffer behind the ring, counted on a barrier
+// of the gate CTA, one barrier per epilogue warp), and the gate CTA writes e4m3 h = silu(gate) * up for the down
+// projection instead of y.  Still two CTAs per SM: the ring is one slot shorter to make room for the buffer.
 template <int MP, bool kPreQ = false, bool kGateUp = false>
 struct SwapCfg {
     static constexpr int kWBytes = kTileN * kKB;                 // 16 KB e4m3 weight tile
@@ -55,11 +56,12 @@ struct SwapCfg {
     static constexpr int kStageBytes = kWBytes + kXqBytes + kXrawBytes;
     // M <= 16: two CTAs share an SM (5 stages each, 160 KB of weights in flight per SM), so the
     // CTAs of the next kernel can start on an SM while this kernel's other CTA is still draining
-    static constexpr int kCtasPerSm = (MP <= 16 && !kGateUp) ? 2 : 1;
-    static constexpr int kStages = kGateUp ? 12 : (kPreQ ? (MP <= 16 ? 6 : 9) : (MP <= 16 ? 5 : (MP <= 32 ? 7 : 5)));
+    static constexpr int kCtasPerSm = MP <= 16 ? 2 : 1;
+    static constexpr int kStages = kGateUp ? 5 : (kPreQ ? (MP <= 16 ? 6 : 9) : (MP <= 16 ? 5 : (MP <= 32 ? 7 : 5)));
+    static constexpr int kRecvBytes = kGateUp ? kTileN * MP * 2 : 0;   // bf16 [channel][row] from the up CTA
     static_assert(!kGateUp || (kPreQ && MP == 16), "the gate_up form exists for 16-row tiles of pre-quantised rows");
     static constexpr int kRingBytes = kStages * kStageBytes;
-    static constexpr int kSmemBytes = kRingBytes + 1024;
+    static constexpr int kSmemBytes = kRingBytes + 1024 + kRecvBytes;
     static constexpr int kTmemCols = 2 * MP < 32 ? 32 : 2 * MP;
     static constexpr int kPartPitch = MP * 4 + 16;               // row pitch of the received fp32 partial sums (split-K)
     static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment for the swizzle");
@@ -96,6 +98,8 @@ __global__ void __launch_bounds__(kSwapThreads, SwapCfg<MP, kPreQ, kGateUp>::kCt
 swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  UmmaArgs p, SwapSched sched) {
     static_assert(!(kGateUp && kSplit), "tile pairs are not split along K");
+    __shared__ __align__(8) uint64_t bar_up[4];       // gate CTA: the up values of epilogue warp q's channels have landed
+    __shared__ __align__(8) uint64_t bar_free[4];     // up CTA: the gate CTA has read warp q's values (buffer reusable)
     using Cfg = SwapCfg<MP, kPreQ, kGateUp>;
     // bytes of activations one K block brings in: M real rows, raw bf16 or ready e4m3
     const uint32_t x_bytes = (uint32_t)p.M * (kPreQ ? 128u : 256u);
@@ -117,12 +121,12 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const int lane = threadIdx.x & 31;
 
     const int split_rank = kSplit ? (int)cluster_ctarank() : 0;
-    const int first_tile = kSplit ? (int)(blockIdx.x / sched.splits) : (kGateUp ? 2 * (int)blockIdx.x : (int)blockIdx.x);
+    const int pair_rank = kGateUp ? (int)cluster_ctarank() : 0;                  // gate_up form: 0 = gate tile, 1 = up tile
+    const int first_tile = kSplit ? (int)(blockIdx.x / sched.splits) : (kGateUp ? (int)(blockIdx.x & ~1u) + pair_rank : (int)blockIdx.x);
     const int tile_step = kSplit ? sched.n_tiles : (int)gridDim.x;
-    // the tl-th tile of this CTA: every gridDim.x-th tile, or (gate_up form) both tiles of every gridDim.x-th pair
-    auto tile_of = [&](int tl) -> int {
-        return kGateUp ? 2 * ((int)blockIdx.x + (tl >> 1) * (int)gridDim.x) + (tl & 1) : first_tile + tl * tile_step;
-    };
+    // the tl-th tile of this CTA: every gridDim.x-th tile (gate_up form: this CTA's half of every (gridDim.x / 2)-th pair)
+    auto tile_of = [&](int tl) -> int { return first_tile + tl * tile_step; };
+    const uint32_t recv_bytes_warp = 32u * (uint32_t)((p.M + 7) >> 3) * 16u;      // what one up warp sends per pair
     const int kb0 = split_rank * sched.kblocks_per_split;
     const int kb1 = kSplit ? min(sched.kblocks_total, kb0 + sched.kblocks_per_split) : sched.kblocks_total;
     // split-K: CTA r of the cluster finishes channels [r * band, r * band + band_rows) of the tile; a slice's partials
@@ -139,6 +143,13 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
         for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bar_tfull[i]), 1); mbar_init(smem_u32(&bar_tempty[i]), 4); }
         s_abort = 0;
+        if (kGateUp) {
+            for (int i = 0; i < 4; ++i) {
+                mbar_init(smem_u32(&bar_up[i]), 1);
+                mbar_init(smem_u32(&bar_free[i]), 1);
+                if (pair_rank == 0) mbar_expect_tx(smem_u32(&bar_up[i]), recv_bytes_warp);
+            }
+        }
         if (kSplit) {
             mbar_init(smem_u32(&bar_ready), (uint32_t)sched.splits);
             mbar_init(smem_u32(&bar_recv), 1);
@@ -159,7 +170,7 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     pdl_launch_dependents();
-    if (kSplit) cluster_arrive();                            // (waited for before the first remote access: the peers' barriers exist)
+    if (kSplit || kGateUp) cluster_arrive();                 // (waited for before the first remote access: the peers' barriers exist)
     // scale and bias of the first channel this thread finishes, fetched long before they are needed
     float ws0 = 0.f, bs0 = 0.f, in_scale0 = 0.f;
     if constexpr (kSplit) {
@@ -303,47 +314,74 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             // ---- pairs of tiles: h = silu(gate) * up, quantised for the down projection ----
             const ExactDiv div_h(fmaxf(__ldg(p.h_scale), 1e-12f));
             const int inter = p.N >> 1;
-            for (int tl = 0; ok; tl += 2) {
+            const int groups = (p.M + 7) >> 3;                                     // rows travel in groups of eight bf16
+            const uint32_t recv = smem_base + Cfg::kRingBytes + (uint32_t)(q * 32 + lane) * (MP * 2);
+            cluster_wait();
+            for (int tl = 0; ok; ++tl) {
                 const int t = tile_of(tl);
                 if (t >= sched.n_tiles) break;
+                const bool more = tile_of(tl + 1) < sched.n_tiles;
+                const int as = tl & 1;
                 const uint32_t aph = (tl >> 1) & 1;
-                const int ng = t * kTileN + q * 32 + lane, nu = ng + kTileN;     // (N is a multiple of 256: both in range)
-                const float wg = __ldg(p.w_scale + ng), wu = __ldg(p.w_scale + nu);
-                const float bg = p.bias ? __bfloat162float(p.bias[ng]) : 0.f, bu = p.bias ? __bfloat162float(p.bias[nu]) : 0.f;
-                uint32_t vg[MP], vu[MP];
-                if (!mbar_wait(smem_u32(&bar_tfull[0]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
+                const int n = t * kTileN + q * 32 + lane;                           // (N is a multiple of 256: in range)
+                const float ws = __ldg(p.w_scale + n);
+                const float bs = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+                uint32_t v[MP];
+                if (!mbar_wait(smem_u32(&bar_tfull[as]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
                 tc_fence_after();
                 __syncwarp();
-                tmem_ld_cols<MP>(tmem_base + ((uint32_t)(q * 32) << 16), vg);
-                tmem_ld_wait();
-                if (!mbar_wait(smem_u32(&bar_tfull[1]), aph, p.status, kDevTimeoutTmemFull)) { s_abort = 1; ok = false; break; }
-                tc_fence_after();
-                __syncwarp();
-                tmem_ld_cols<MP>(tmem_base + ((uint32_t)(q * 32) << 16) + MP, vu);
+                tmem_ld_cols<MP>(tmem_base + ((uint32_t)(q * 32) << 16) + as * MP, v);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(smem_u32(&bar_tempty[0])); mbar_arrive(smem_u32(&bar_tempty[1])); }
-                // the values and roundings of the two-step form: gate and up rounded to bf16, then bf16(silu(g) * u)
-                unsigned char* hcol = p.hq + (size_t)(t >> 1) * kTileN + q * 32 + lane;
+                if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[as]));
+                // this tile's values rounded to bf16, as the two-step form stores them
+                uint32_t r[MP / 2];
 #pragma unroll
-                for (int m0 = 0; m0 < MP; m0 += 8) {
-                    if (m0 >= p.M) break;
-                    uint4 hv;
-                    uint32_t* hw = reinterpret_cast<uint32_t*>(&hv);
+                for (int m = 0; m < MP; m += 2)
+                    r[m >> 1] = pack_bf16x2(fmaf(__uint_as_float(v[m]) * in_scale, ws, bs), fmaf(__uint_as_float(v[m + 1]) * in_scale, ws, bs));
+                if (pair_rank == 1) {
+                    // up tile: hand the values to the gate CTA (after it has read the previous pair's)
+                    if (tl > 0 && !mbar_wait(smem_u32(&bar_free[q]), (uint32_t)((tl - 1) & 1), p.status, kDevTimeoutPeer)) { s_abort = 1; ok = false; break; }
+                    const uint32_t dst = map_to_cta(recv, 0);
+                    const uint32_t rbar = map_to_cta(smem_u32(&bar_up[q]), 0);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int m = m0 + 2 * j;
-                        const uint32_t gp = pack_bf16x2(fmaf(__uint_as_float(vg[m]) * in_scale, wg, bg), fmaf(__uint_as_float(vg[m + 1]) * in_scale, wg, bg));
-                        const uint32_t up = pack_bf16x2(fmaf(__uint_as_float(vu[m]) * in_scale, wu, bu), fmaf(__uint_as_float(vu[m + 1]) * in_scale, wu, bu));
-                        const float g0 = bf16_lo(gp), g1 = bf16_hi(gp);
-                        const float s0 = g0 / (1.f + expf(-g0)), s1 = g1 / (1.f + expf(-g1));
-                        hw[j] = pack_bf16x2(s0 * bf16_lo(up), s1 * bf16_hi(up));
+                    for (int gI = 0; gI < MP / 8; ++gI)
+                        if (gI < groups) st_async_v4(dst + gI * 16, r[4 * gI], r[4 * gI + 1], r[4 * gI + 2], r[4 * gI + 3], rbar);
+                } else {
+                    if (!mbar_wait(smem_u32(&bar_up[q]), (uint32_t)(tl & 1), p.status, kDevTimeoutPeer)) { s_abort = 1; ok = false; break; }
+                    uint32_t u[MP / 2];
+#pragma unroll
+                    for (int gI = 0; gI < MP / 8; ++gI) {
+                        if (gI < groups)
+                            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(u[4 * gI]), "=r"(u[4 * gI + 1]), "=r"(u[4 * gI + 2]), "=r"(u[4 * gI + 3])
+                                         : "r"(recv + gI * 16));
+                        else u[4 * gI] = u[4 * gI + 1] = u[4 * gI + 2] = u[4 * gI + 3] = 0u;
                     }
-                    const uint2 qd = quant8_e4m3(hv, div_h);
+                    __syncwarp();
+                    if (more && lane == 0) {                                        // (no signal after the last pair: the up CTA may be gone)
+                        mbar_expect_tx(smem_u32(&bar_up[q]), recv_bytes_warp);
+                        mbar_arrive_cluster(map_to_cta(smem_u32(&bar_free[q]), 1));
+                    }
+                    // the values and roundings of the two-step form: bf16(silu(g) * u) from bf16 g and u, then the quantiser
+                    unsigned char* hcol = p.hq + (size_t)(t >> 1) * kTileN + q * 32 + lane;
 #pragma unroll
-                    for (int r = 0; r < 8; ++r)
-                        if (m0 + r < p.M) hcol[(size_t)(m0 + r) * inter] = (unsigned char)(((r < 4 ? qd.x : qd.y) >> (8 * (r & 3))) & 0xffu);
+                    for (int gI = 0; gI < MP / 8; ++gI) {
+                        if (gI >= groups) break;
+                        uint4 hv;
+                        uint32_t* hw = reinterpret_cast<uint32_t*>(&hv);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t gp = r[4 * gI + j], up = u[4 * gI + j];
+                            const float g0 = bf16_lo(gp), g1 = bf16_hi(gp);
+                            const float s0 = g0 / (1.f + expf(-g0)), s1 = g1 / (1.f + expf(-g1));
+                            hw[j] = pack_bf16x2(s0 * bf16_lo(up), s1 * bf16_hi(up));
+                        }
+                        const uint2 qd = quant8_e4m3(hv, div_h);
+#pragma unroll
+                        for (int rr = 0; rr < 8; ++rr)
+                            if (gI * 8 + rr < p.M) hcol[(size_t)(gI * 8 + rr) * inter] = (unsigned char)(((rr < 4 ? qd.x : qd.y) >> (8 * (rr & 3))) & 0xffu);
+                    }
                 }
             }
         } else
@@ -431,6 +469,10 @@ swap_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         return;
     }
 
+    if constexpr (kGateUp) {
+        __syncwarp();
+        if (warp < 2 + kConvWarps) cluster_wait();           // (the epilogue warps did before their first remote access)
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -581,13 +623,19 @@ cudaError_t launch_swap_gate_up(const UmmaArgs& a, cudaStream_t stream, const ch
     s.kblocks_total = (a.K + kKB - 1) / kKB; s.kblocks_per_split = s.kblocks_total;
     const int pairs = s.n_tiles / 2;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(pairs < sm_count() ? pairs : sm_count()));
+    cfg.gridDim = dim3((unsigned)(2 * (pairs < sm_count() ? pairs : sm_count())));     // two CTAs per SM, one pair per cluster
     cfg.blockDim = dim3(kSwapThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    cfg.numAttrs = pdl_attribute(attr);
+    cudaLaunchAttribute attr[2];
+    int na = pdl_attribute(attr);
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
     cfg.attrs = attr;
+    cfg.numAttrs = na;
     return counted(cudaLaunchKernelEx(&cfg, kern, tw, tx, a, s));
 }
 

@@ -142,8 +142,8 @@ def test_fused_mlp_layer_matches_separate_layers():
 
 @pytest.mark.parametrize("m,h,inter,n", [(1, 512, 384, 512), (5, 448, 256, 264), (16, 512, 1408, 520), (3, 3584, 18944, 3584)])
 def test_fused_mlp_from_codes_on_decode_rows(m, h, inter, n):
-    """Up to 16 pre-quantised rows, with and without the opt-in form in which the decode kernel takes (gate, up)
-    tile pairs and writes e4m3 h itself: same bits as the default (a separate silu-multiply-quantise pass), and
+    """Up to 16 pre-quantised rows, with and without the opt-in form in which CTA pairs of the decode kernel take (gate,
+    up) tile pairs and write e4m3 h themselves: same bits as the default (a separate silu-multiply-quantise pass), and
     parity with the oracle."""
     Kn = kernels()
     gu, down = make_mlp_case(8200 + m + h + inter, m, h, inter, n)
