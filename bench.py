@@ -931,8 +931,16 @@ def main():
                     help="row-parallel layers: every rank's epilogue stores its partial into every rank (on), reduce-scatter "
                          "in the epilogue + sum + all-gather by peer stores (rs), NCCL all-reduce after the GEMM (off), or "
                          "by shape and rank count (auto, the layer default)")
+    ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
+                    help="study runs: force a tuning knob of the library (fp8lin_set_tuning) before anything is launched; "
+                         "the knobs are echoed under run.tune")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.tune and args.impl == "ours":
+        kn = importlib.import_module("nano-vllm-moe_b200.quantization.kernels")
+        for kv in args.tune:
+            knob, _, val = kv.partition("=")
+            kn.set_tuning(knob, int(val))
 
     if args.workload.startswith("c5"):
         return bench_moe(args, WORKLOADS[args.workload][1])
@@ -1332,7 +1340,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 -> bf16"
             if scheme == "fp8_w8a8_static" else "fp8_e4m3 weights, f16 MMA -> fp32 -> bf16",
             "data": "synthetic", "config": config,
-            "run": {"parallelism": f"tp{tp}" if tp > 1 else "single",
+            "run": {"parallelism": f"tp{tp}" if tp > 1 else "single", "tune": args.tune or None,
                     "row_parallel_reduction": None if tp == 1 else (
                         f"peer_reduce={args.peer_reduce}; " + ("each layer's reduction finished before the next linear starts"
                                                                if args.no_overlap_reduce else

@@ -293,7 +293,10 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);
 int fp8lin_set_tuning(const char* knob, int value);
 
 /* Blocking: copies the device status word out of `workspace` (after syncing
- * `stream`) and clears it.  0 = no kernel gave up a bounded wait. */
+ * `stream`) and clears it.  0 = no kernel gave up a bounded wait.  Otherwise the code of the wait
+ * that ran out (about a second): 0x101 operand tile never landed, 0x102 ring slot never freed, 0x103 /
+ * 0x104 accumulator never filled / never drained, 0x105 in-kernel activation quantiser, 0x106 a peer
+ * CTA of the cluster (split-K hand-over) never answered. */
 int fp8lin_read_status(void* workspace, void* stream, int* status_out);
 
 /* Exercises the give-up path of the kernels' bounded waits without a fault (no counterpart in the
