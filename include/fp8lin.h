@@ -287,6 +287,7 @@ const char* fp8lin_variant_name(int scheme, int64_t M, int64_t K, int64_t N);
  * "swap_splits", "swap_enable", "swap_min_m", "swap_preq_min_m", "w8a16_swap_enable", "w8a16_swap_min_m", "fuse_quant" (1 = large-M W8A8 quantises most rows with warps of the GEMM
  * itself instead of a pass in front of it; n > 1 = the pass takes the first n rows), "quant_lead",
  * "w8a16_umma_min_m" (rows from which W8A16 takes the f16 GEMM route; 0 = never), "w8a16_chunk_mb", "pdl",
+ * "stream_push" (0 = split-K of the mma.sync streaming kernel always through global scratch instead of a cluster),
  * "mlp_decode_fused" (1 = the fused MLP on up to 16 pre-quantised rows computes silu * up inside the gate_up kernel),
  * "moe_fused" (0 = the expert FFN keeps a separate activation pass), "moe_rows_major" (0 = prefill-sized expert
  * batches stay on the channel-major grouped kernel), "pair_stages" (4 or 5 ring slots in the CTA-pair GEMM). */

@@ -152,15 +152,15 @@ bool pair_eligible(int64_t M, int64_t N) {
 }
 
 bool swap_eligible(int64_t M, int64_t K, int64_t N) {
-    (void)K; (void)N;
     const int max_m = g_tune.stream_max_m >= 0 ? g_tune.stream_max_m : kDefaultStreamMaxM;
-    // The tcgen05 kernel from the first row on.  Since its split-K slices push their partial sums to the CTA that
-    // finishes a band (no cluster barrier, no remote loads) it beats the mma.sync streaming kernel at every size
-    // measured, e.g. at one row / eight rows: 3584 -> 4608 6.8 / 7.1 us against 7.8 / 8.2, 3584 -> 3584 6.0 / 6.3
-    // against 7.5 / 8.0, 2048 -> 11008 7.3 / 7.5 against 8.3 / 9.0, 11008 -> 2048 8.6 / 8.8 against 10.1 / 10.6,
-    // 1408 -> 2048 3.7 / 4.1 against 5.6 / 6.2, 3584 -> 37888 21.9 / 22.8 against 23.8 / 27.1 (3584 -> 9472: equal).
-    // The streaming kernel stays for W8A16 up to 32 rows and for the no-allocation entry point.
-    const int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 1;
+    // The tcgen05 kernel from the first row on, except on layers of up to ~17 MB with a short K (qkv, o_proj), where up to
+    // 8 rows the mma.sync streaming kernel -- many small CTAs, its split-K slices handing their sums over inside a
+    // cluster -- starts and drains faster.  Measured at one row / eight rows, us, tcgen05 against streaming kernel:
+    // 3584 -> 4608 6.8 / 7.1 against 6.0 / 6.5, 3584 -> 3584 5.8 / 6.3 against 5.1 / 5.5, 4736 -> 3584 6.9 against 6.5
+    // (four rows), 2048 -> 2048 4.1 against 4.0; but 2048 -> 11008 7.2 / 7.4 against 9.1 / 9.7, 11008 -> 2048 8.3 against
+    // 9.6, 18944 -> 3584 14.9 / 15.2 against 16.6 / 19.0, 3584 -> 37888 21.7 against 24.0.
+    int min_m = g_tune.swap_min_m >= 0 ? g_tune.swap_min_m : 1;
+    if (g_tune.swap_min_m < 0 && K <= 8192 && N <= 4736) min_m = 9;
     return g_tune.swap_enable != 0 && M >= min_m && M <= 64 && M <= max_m;
 }
 
@@ -307,6 +307,7 @@ static int run_stream(int scheme, const void* x, int64_t ldx, const void* w, con
     a.x = (const __nv_bfloat16*)x; a.w = (const unsigned char*)w; a.w_scale = w_scale; a.input_scale = input_scale;
     a.bias = (const __nv_bfloat16*)bias; a.y = (__nv_bfloat16*)y;
     a.partial = workspace ? (float*)ws.body : nullptr; a.counters = workspace ? ws.counters : nullptr;
+    a.status = workspace ? ws.status : nullptr;
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.ldx = (int)ldx; a.ldy = (int)ldy; a.k_per_split = pl.k_per_split;
     cudaError_t e = launch_stream(scheme, pl, a, stream);
     if (e != cudaSuccess) return fail(FP8LIN_ERR_LAUNCH, "stream kernel launch: %s", cudaGetErrorString(e));
@@ -755,6 +756,7 @@ int fp8lin_set_tuning(const char* knob, int value) {
     else if (!strcmp(knob, "umma_pair")) g_tune.umma_pair = value;
     else if (!strcmp(knob, "fuse_quant")) g_tune.fuse_quant = value;
     else if (!strcmp(knob, "quant_lead")) g_tune.quant_lead = value;
+    else if (!strcmp(knob, "stream_push")) set_stream_push(value != 0);
     else if (!strcmp(knob, "mlp_decode_fused")) g_tune.mlp_decode_fused = value;
     else if (!strcmp(knob, "moe_fused")) g_tune.moe_fused = value;
     else if (!strcmp(knob, "moe_rows_major")) g_tune.moe_rows_major = value;

@@ -43,6 +43,11 @@ struct StreamArgs {
     int M, K, N;
     int ldx, ldy;
     int k_per_split;
+    // Split-K of up to eight slices and at most 16 rows, when a status word is given: the slices of a channel tile form
+    // a cluster and push their partial sums into slice 0's shared memory (no scratch, no counters, no second
+    // global round trip); set by launch_stream.
+    int* status = nullptr;
+    int cluster_push = 0;
 };
 
 struct StreamPlan {
@@ -56,6 +61,7 @@ struct StreamPlan {
 };
 
 StreamPlan plan_stream(int scheme, int64_t M, int64_t K, int64_t N, int force_splits);
+void set_stream_push(int on);      // study knob: 0 = split-K of the streaming kernel always through global scratch
 cudaError_t launch_stream(int scheme, const StreamPlan& plan, StreamArgs args, cudaStream_t stream);
 
 // ---- elementwise helpers (elementwise.cu) ------------------------------------

@@ -184,8 +184,12 @@ def test_routing_of_large_shapes(pkg):
     assert name(L.W8A16, 4096, 3584, 37888).endswith("_c5")                            # five chunks of <= 64 MB of f16
     assert name(L.W8A16, 40, 3584, 4608).startswith("umma_swap_w8a16_m64")
     # a 4 MB layer at one row: eight cluster slices of the swapped tcgen05 kernel, all resident at once
-    assert name(L.W8A8_STATIC, 1, 2048, 2048) == "umma_swap_w8a8_m16_s8"
-    assert name(L.W8A8_STATIC, 1, 3584, 3584).startswith("umma_swap_w8a8_m16_s")     # tcgen05 from the first row on
+    # up to 8 rows on layers of a few MB with a short K: the streaming kernel (cluster hand-over of its split-K sums)
+    assert name(L.W8A8_STATIC, 1, 2048, 2048).startswith("stream_mma_w8a8_m8")
+    assert name(L.W8A8_STATIC, 8, 3584, 3584).startswith("stream_mma_w8a8_m8")
+    assert name(L.W8A8_STATIC, 9, 3584, 3584).startswith("umma_swap_w8a8_m16_s")
+    assert name(L.W8A8_STATIC, 1, 2048, 11008).startswith("umma_swap_w8a8_m16_s")    # tcgen05 from the first row elsewhere
+    assert name(L.W8A8_STATIC, 1, 18944, 3584) == "umma_swap_w8a8_m16_s8"
     assert name(L.W8A8_STATIC, 1, 3584, 37888) == "umma_swap_w8a8_m16_s1"          # a channel tile for every SM: no split-K
     # W8A16 from 256 rows needs the f16 scratch: activations + one chunk
     need = lib.fp8lin_workspace_bytes(L.W8A16, 4096, 3584, 37888)
