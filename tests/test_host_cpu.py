@@ -241,3 +241,31 @@ def test_kernels_refuse_cpu_tensors(pkg):
         K.launch_w8a16_gemm(x, w, s)
     with pytest.raises(ValueError, match="CUDA"):
         K.launch_w8a8_gemm(x, w, torch.ones(()), s)
+
+
+def test_decode_planners_give_well_formed_plans(pkg):
+    """The slice planners of the decode kernels are pure host functions: over a grid of shapes every plan names a
+    kernel, its split factor is 1..8 (cluster size) and never larger than the number of 128-element K blocks, and the
+    workspace it asks for is bounded by the header plus one quantised copy of the activations."""
+    import re
+    lib = pkg._lib.load()
+    L = pkg._lib
+    rng = np.random.default_rng(11)
+    shapes = [(m, k, n) for m in (1, 3, 8, 9, 16, 17, 32, 33, 64)
+              for k, n in ((16, 8), (448, 576), (1408, 2048), (2048, 2048), (2048, 11008), (3584, 4608), (3584, 37888), (18944, 3584))]
+    shapes += [(int(rng.integers(1, 65)), 16 * int(rng.integers(1, 1200)), int(rng.integers(1, 40000))) for _ in range(200)]
+    for scheme in (L.W8A16, L.W8A8_STATIC):
+        for m, k, n in shapes:
+            name = lib.fp8lin_variant_name(scheme, m, k, n).decode()
+            assert name.startswith(("stream_mma_", "umma_swap_")), (scheme, m, k, n, name)
+            s = int(re.search(r"_s(\d+)", name).group(1))
+            kblocks = -(-k // 128)
+            if name.startswith("umma_swap_"):
+                assert 1 <= s <= 8 and s <= kblocks, (m, k, n, name)
+                assert f"_m{16 if m <= 16 else 32 if m <= 32 else 64}_" in name, (m, k, n, name)
+            else:
+                assert 1 <= s <= max(1, -(-k // 256)), (m, k, n, name)
+                if m <= 16:
+                    assert s <= 8, (m, k, n, name)          # up to 16 rows the slices form a cluster
+            need = lib.fp8lin_workspace_bytes(scheme, m, k, n)
+            assert L.WS_HEADER_BYTES <= need <= L.WS_HEADER_BYTES + max(m * k + 256, 8 * m * n * 4 * 8 + 4096), (m, k, n, need)
