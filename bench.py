@@ -509,9 +509,11 @@ def bench_moe(args, T):
     el = cfg.local_num_experts
     # the ranks of a TP group hold the same experts (each its slice of the intermediate dimension) and the same tokens
     q13, s13, q2, s2 = make_expert_weights(el, H, I, SEED + 7919 * cfg.ep_rank, dev)
-    g = torch.Generator(device=dev).manual_seed(SEED + cfg.ep_rank)
-    calib = torch.randn((4096, H), generator=g, device=dev).to(torch.bfloat16)
+    # one static activation scale per layer, the same on every rank (as a checkpoint holds it)
+    gc = torch.Generator(device=dev).manual_seed(SEED)
+    calib = torch.randn((4096, H), generator=gc, device=dev).to(torch.bfloat16)
     in13 = (calib.float().abs().amax() / 448.0).reshape(())
+    g = torch.Generator(device=dev).manual_seed(SEED + 1 + cfg.ep_rank)
     wts = moe.Fp8ExpertWeights.from_checkpoint_layout(q13, s13, in13, q2, s2, torch.tensor(4.0 / 448.0),
                                                       tp_rank=cfg.tp_rank, tp_size=cfg.tp_size)
     del q13, q2
@@ -534,6 +536,42 @@ def bench_moe(args, T):
     for i in range(sets):
         run(i)
     torch.cuda.synchronize()
+
+    # ---- parity (outside every timed region): rank 0's sampled tokens of batch 0 against the CPU oracle, with the
+    # expert weights of every rank regenerated from their seeds for the experts those tokens were routed to ----------
+    parity = None
+    if not args.no_parity:
+        y0 = run(0)                              # every rank takes part in the exchange
+        torch.cuda.synchronize()
+        if rank == 0:
+            from oracle import fp8_oracle as O
+            rng = np.random.default_rng(SEED)
+            idx = np.unique(np.concatenate([[0, T - 1], rng.integers(0, T, size=min(T, 6))]))
+            w_all, ids_all = router.select_experts(None, logits[0])
+            it = torch.from_numpy(idx).to(dev)
+            ids_s = ids_all[it].cpu().numpy()
+            w_s = w_all[it].float().cpu().numpy()
+            need = np.unique(ids_s)
+            remap = {int(e): j for j, e in enumerate(need)}
+            w13_q, w13_s, w2_q, w2_s = [], [], [], []
+            el_all = E // cfg.ep_size
+            for e in need:
+                owner, le = int(e) // el_all, int(e) % el_all
+                q, sc = make_weights(H, 2 * I, SEED + 7919 * owner + 2 * le, dev); w13_q.append(q.cpu().numpy()); w13_s.append(sc.cpu().numpy())
+                q, sc = make_weights(I, H, SEED + 7919 * owner + 2 * le + 1, dev); w2_q.append(q.cpu().numpy()); w2_s.append(sc.cpu().numpy())
+            ref = O.moe_experts_w8a8(xs[0][it].float().cpu().numpy(), np.vectorize(remap.get)(ids_s), w_s,
+                                     np.stack(w13_q), np.stack(w13_s), np.float32(in13.item()),
+                                     np.stack(w2_q), np.stack(w2_s), np.float32(4.0 / 448.0))
+            got = y0[it].float().cpu().numpy()
+            ulps = 3.0 * cfg.tp_size
+            ok, worst = O.check_close(got, ref, ulps=ulps)
+            cos = O.cosine(got, ref)
+            parity = {"worst_ratio": float(worst), "cosine": float(cos), "ranks": world, "tokens_checked": int(len(idx)),
+                      "experts_involved": int(len(need)),
+                      "tolerance": f"|y - oracle| <= {ulps:g} * 2^-7 (|oracle| + rms(oracle)): three roundings on the way (gate_up, h, "
+                                   "e4m3 of h), times the ranks that share an expert's intermediate dimension; cosine >= 0.9999",
+                      "ok": bool(ok and cos >= 0.9999)}
+        del y0
     graphs, use_graph = [], (not args.no_graph and pf.supports_cuda_graph)
     if use_graph:
         side = torch.cuda.Stream(dev)
@@ -544,6 +582,11 @@ def bench_moe(args, T):
                 with torch.cuda.graph(gph, stream=side):
                     run(i)
                 graphs.append(gph)
+
+    n0 = Kn.launch_count()
+    run(0)
+    launches_per_step = Kn.launch_count() - n0          # this library's kernels in one step, counted while they were enqueued
+    torch.cuda.synchronize()
 
     def step(i):
         graphs[i % sets].replay() if use_graph else run(i)
@@ -623,7 +666,12 @@ def bench_moe(args, T):
                          "peak_source": f"{peaks['source']}"},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
-            "gpu_launches": 6 * args.steps, "device_status": status}), flush=True)
+            "parity": parity,
+            "gpu_launches": launches_per_step * args.steps, "kernels_per_step": launches_per_step, "device_status": status}), flush=True)
+        if parity is not None and not parity["ok"]:
+            print(f"[bench] parity check failed: {parity}", file=sys.stderr)
+            sys.stdout.flush()
+            os._exit(1)
     if world > 1:
         graphs.clear()               # captured graphs hold NCCL work
         torch.cuda.synchronize()
